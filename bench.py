@@ -1,0 +1,458 @@
+"""Benchmark of the LOCKS decode hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+                    [--workload c1|c0|c4] [--ctx TOKENS] [--no-cpu-baseline]
+
+One "step" = the attention hot path of one decode step over all layers of the
+workload: per layer  page score -> GQA combine + top-b select -> split-K sparse
+paged decode -> merge, replayed as one CUDA graph.  The default workload is the
+Llama-3.1-8B-shaped single-sequence decode at 131072 tokens of context
+(32 layers, 32 q / 8 kv heads, d 128, page 16, budget 128 + 1 sink + 8 recent
+pages).  Inputs are seeded synthetic KV caches of that shape, resident in HBM.
+One JSON line is printed by rank 0.
+
+With N > 1 every rank decodes its own sequence of the same shape (sequence
+sharding, no data-path collective): weak scaling, value = N sequences' tokens/s.
+
+`--impl reference` times the CPU restatement of the reference's own path
+(oracle/locks_oracle.py, numpy, all host threads) on a bounded sample of the
+same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (os.path.join(ROOT, "locks-kv_b200"), os.path.join(ROOT, "oracle")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+REC_ALGO_BYTES = 818           # summary bytes per (page, kv-head) the scorer needs
+PAGE_KV_BYTES = 16 * 128 * 2 * 2   # K + V bytes of one attended (page, kv-head)
+
+
+def workload(name: str, ctx: int | None):
+    from locks import synth
+    if name == "c0":
+        sh, c = synth.CONFIG0, 4096
+    elif name == "c1":
+        sh, c = synth.CONFIG1, 131072
+    elif name == "c4":
+        sh, c = synth.CONFIG4, 1048576
+    else:
+        raise SystemExit(f"unknown workload {name}")
+    return sh, (ctx or c)
+
+
+def algo_bytes(sh, seq_len):
+    """Algorithmic bytes of one step: summaries scanned + selected K/V pages."""
+    npg = -(-seq_len // sh.page)
+    nsh = npg - sh.window_pages
+    A = min(sh.budget_pages, nsh - sh.sink_pages) + sh.sink_pages + sh.window_pages
+    score = sh.n_layers * sh.n_kv * nsh * REC_ALGO_BYTES
+    dec = sh.n_layers * sh.n_kv * A * PAGE_KV_BYTES
+    dense = sh.n_layers * sh.n_kv * npg * PAGE_KV_BYTES
+    return score, dec, dense, nsh, A
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason sampler running beside the timed
+    region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.idx}", f"--query-gpu={self.Q}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                 "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- #
+# CPU arm: the oracle restatement of the reference path                        #
+# --------------------------------------------------------------------------- #
+class CpuArm:
+    """The oracle restatement of the reference path on the host cores, on a
+    bounded sample of the workload: ONE layer, at 1/4 of the context when the
+    context exceeds 32K tokens.  Page scoring and selection are linear in the
+    number of pages, so their time is scaled by the page ratio; the decode
+    attends the same number of pages at any context, so its time is not.
+    Summaries are built once, untimed."""
+
+    def __init__(self, sh, seq_len, seed=1234):
+        import locks_oracle as orc
+        from locks import synth
+        self.orc, self.sh = orc, sh
+        ctx = seq_len - 1
+        self.ctx_s = ctx // 4 if ctx > 32768 else ctx
+        self.page_ratio = (ctx / self.ctx_s)
+        case = synth.make_gqa_case(seed, sh, [self.ctx_s + 1], device="cpu",
+                                   n_layers=1)
+        f = lambda t: t.float().numpy()
+        self.bt, self.sl = case.block_table.numpy(), case.seq_lens.numpy()
+        self.Kc, self.Vc = f(case.kv_caches[0][:, 0]), f(case.kv_caches[0][:, 1])
+        self.q = f(case.q[0])
+        self.scale = case.scale
+        self.MP = case.max_pages
+        self.slabs = orc.rki4_build_pages(self.Kc)
+        self.sample = (f"1 of {sh.n_layers} layers at ctx {self.ctx_s} "
+                       f"(score+select time x{self.page_ratio:g}, decode x1), "
+                       f"scaled x{sh.n_layers}; numpy oracle, summaries prebuilt")
+
+    def step(self):
+        """Seconds one full decode step would take (all layers, full ctx)."""
+        orc, sh = self.orc, self.sh
+        t0 = time.perf_counter()
+        npg, nsh, b = orc.derive_page_params(self.sl, sh.page, sh.window_pages,
+                                             sh.sink_pages, sh.budget_pages)
+        score_h = orc.rki4_score(self.slabs, self.q, self.bt, nsh, self.scale,
+                                 sh.n_kv, sh.G, self.MP)
+        score = orc.nrm_combine(score_h, nsh)
+        tab, cnt = orc.topb_select(score, npg, nsh, b, sh.sink_pages)
+        t1 = time.perf_counter()
+        m, l, acc = orc.sparse_decode_split(self.q, self.Kc, self.Vc, self.bt,
+                                            tab, cnt, self.sl, self.scale,
+                                            sh.n_kv, sh.G, 64, 2)
+        orc.merge_splits(m, l, acc, cnt, 64, 2)
+        t2 = time.perf_counter()
+        return sh.n_layers * ((t1 - t0) * self.page_ratio + (t2 - t1))
+
+
+def run_reference(args, sh, seq_len):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    arm = CpuArm(sh, seq_len)
+    for _ in range(args.warmup):
+        arm.step()
+    per_step = [arm.step() for _ in range(args.steps)]
+    tpot = float(np.mean(per_step))
+    return {
+        "impl": "reference", "metric": "sparse_decode_tokens_per_s",
+        "value": 1.0 / tpot, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": tpot * 1e3, "tpot_ms": tpot * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload_name, "ctx": seq_len - 1},
+        "cpu_baseline": {"value": 1.0 / tpot, "unit": "tokens/s",
+                         "cores": cores, "kind": "port", "sample": arm.sample},
+        "e2e": {"value": 1.0 / tpot, "unit": "tokens/s",
+                "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+
+
+# --------------------------------------------------------------------------- #
+# GPU arm                                                                      #
+# --------------------------------------------------------------------------- #
+def make_device_case(sh, seq_len, dev, seed):
+    """Paged caches for ONE sequence of `seq_len` tokens, generated on the
+    device layer by layer (the full-size cache does not fit a CPU round trip)."""
+    from locks import synth
+    page = sh.page
+    npg = -(-seq_len // page)
+    NB = npg + 3
+    g = torch.Generator().manual_seed(seed * 7 + 3)
+    perm = torch.randperm(NB, generator=g)
+    bt = perm[:npg].to(torch.int32)[None].contiguous().to(dev)
+    caches, qs = [], []
+    blocks = bt[0].long()
+    pad = npg * page - seq_len
+    for l in range(sh.n_layers):
+        K, V, q, _ = synth.gqa_tokens(seed, l, 0, seq_len, sh, dev)
+        kvc = torch.zeros(NB, 2, page, sh.n_kv, sh.d, device=dev,
+                          dtype=torch.bfloat16)
+        if pad:
+            z = torch.zeros(pad, sh.n_kv, sh.d, device=dev, dtype=torch.bfloat16)
+            K, V = torch.cat([K, z]), torch.cat([V, z])
+        kvc[blocks, 0] = K.view(npg, page, sh.n_kv, sh.d)
+        kvc[blocks, 1] = V.view(npg, page, sh.n_kv, sh.d)
+        del K, V
+        caches.append(kvc)
+        qs.append(q[None])
+    sl = torch.tensor([seq_len], dtype=torch.int32, device=dev)
+    return caches, torch.stack(qs), bt, sl
+
+
+def timed(fn, iters, stream=None):
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters          # ms per call
+
+
+def run_gpu(args, sh, seq_len):
+    import torch.distributed as dist
+    from locks import LocksConfig, _cabi
+    from locks.attention import DenseDecodeBuffers, dense_paged_decode
+    from locks.hotpath import HotPath
+    from locks.selection import rki4_score_only, rki4_select_only
+    from locks.attention import sparse_paged_decode_batched
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    # ---- set-up (untimed): caches, summaries, page parameters -----------------
+    caches, q, bt, sl = make_device_case(sh, seq_len, dev, seed=1234 + rank)
+    cfg = LocksConfig(budget_pages=sh.budget_pages, sink_pages=sh.sink_pages,
+                      window_pages=sh.window_pages)
+    hp = HotPath(caches, bt, sl, n_kv=sh.n_kv, G=sh.G,
+                 scale=1.0 / math.sqrt(sh.d), cfg=cfg)
+    t_build = timed(lambda: hp.build_all(), 1)
+    hp.derive()
+    hp.q.copy_(q)
+    t_tail = timed(lambda: hp.build_tail(), 3)
+    hp.capture()
+    torch.cuda.synchronize()
+    hp.st.check_status()
+
+    # ---- timed region: K graph replays ---------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        hp.step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        hp.step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms_total = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+        dist.barrier()
+    ms_step = ms_total / args.steps
+    hp.st.check_status()
+
+    # ---- per-stage kernel times (CUDA events, same stream, same inputs) -------
+    st, R = hp.st, hp.n_req
+    L = sh.n_layers
+    it = max(args.steps // 8, 4)
+
+    def all_layers(fn):
+        def run():
+            for l in range(L):
+                fn(l)
+        return run
+
+    ms_score = timed(all_layers(lambda l: rki4_score_only(
+        st, l, hp.q[l, :R], bt, sl, R, hp.scale)), it) / L
+    ms_select = timed(all_layers(lambda l: rki4_select_only(st, R)), it) / L
+    ms_decode = timed(all_layers(lambda l: sparse_paged_decode_batched(
+        hp.q[l, :R], caches[l], bt, sl, st, hp.out[l], hp.vsources[l],
+        scale=hp.scale)), it) / L
+    # restore a consistent selection for whatever follows
+    hp.step()
+
+    # ---- dense full-KV baseline on the same caches ----------------------------
+    dsplit = max(1, min(512, (4 * 148) // (sh.n_kv * R)))
+    dbuf = DenseDecodeBuffers(dev, R, sh.n_kv, sh.G, sh.d, dsplit)
+    dout = torch.empty_like(hp.out[0])
+    ms_dense = timed(all_layers(lambda l: dense_paged_decode(
+        hp.q[l, :R], caches[l], bt, sl, dbuf, dout, n_kv=sh.n_kv, G=sh.G,
+        scale=hp.scale, status=st.status)), max(it // 4, 2))
+
+    # ---- end to end through the public API with HOST buffers -------------------
+    q_host = q.cpu().pin_memory()
+    out_host = torch.empty(hp.out[:, :R].shape, dtype=torch.bfloat16).pin_memory()
+    sl_host = sl.cpu().pin_memory()
+    bt_host = bt.cpu().pin_memory()
+
+    def e2e_step():
+        hp.q[:, :R].copy_(q_host, non_blocking=True)
+        hp.seq_lens.copy_(sl_host, non_blocking=True)
+        hp.block_table.copy_(bt_host, non_blocking=True)
+        hp.step()
+        out_host.copy_(hp.out[:, :R], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    t0 = time.perf_counter()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms_e2e = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms_e2e], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_e2e = float(t.item())
+    h2d = q_host.numel() * 2 + sl_host.numel() * 4 + bt_host.numel() * 4
+    d2h = out_host.numel() * 2
+
+    clocks = sampler.stop() if rank == 0 else None
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return None
+
+    # ---- roofline of the dominant kernel (the scorer) --------------------------
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak = float(json.load(open(peaks_path))["hbm_gbs"])
+        peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    b_score, b_dec, b_dense, nsh, A = algo_bytes(sh, seq_len)
+    score_launch_bytes = b_score / L
+    achieved = score_launch_bytes / (ms_score * 1e-3) / 1e9
+    step_bytes = b_score + b_dec
+
+    cpu = None
+    if not args.no_cpu_baseline and world == 1:
+        try:
+            cores = os.cpu_count() or 1
+            arm = CpuArm(sh, seq_len)
+            arm.step()
+            t_cpu = float(np.mean([arm.step() for _ in range(10)]))
+            cpu = {"value": 1.0 / t_cpu, "unit": "tokens/s", "cores": cores,
+                   "kind": "port", "sample": arm.sample + "; mean of 10",
+                   "tpot_ms": t_cpu * 1e3}
+        except Exception as e:   # the baseline must not sink the GPU number
+            cpu = {"value": None, "unit": "tokens/s", "cores": os.cpu_count(),
+                   "kind": "port", "sample": f"failed: {type(e).__name__}: {e}"}
+
+    line = {
+        "metric": "sparse_decode_tokens_per_s",
+        "value": world * R / (ms_step * 1e-3),
+        "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+        "tpot_ms": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.workload_name}: {L} layers, "
+                               f"{sh.n_kv * sh.G}q/{sh.n_kv}kv, d{sh.d}, page "
+                               f"{sh.page}, bs1 per GPU, ctx {seq_len - 1}, "
+                               f"budget {sh.budget_pages}+{sh.sink_pages} sink+"
+                               f"{sh.window_pages} recent = {A} pages attended",
+                   "l2_policy": "inputs larger than L2 "
+                                f"({step_bytes / 1e9:.2f} GB touched per step)",
+                   "sharding": "one sequence per GPU, no collective"},
+        "clocks": clocks,
+        "e2e": {"value": world * R / (ms_e2e * 1e-3), "unit": "tokens/s",
+                "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": hp.launches_per_step * args.steps,
+        "roofline": {"kernel": "rki4_score_kernel", "bound": "hbm",
+                     "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": None,
+                     "peak_source": peak_src,
+                     "bytes_per_launch": score_launch_bytes,
+                     "us_per_launch": ms_score * 1e3},
+        "step_roofline": {"algorithmic_bytes": step_bytes,
+                          "achieved_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
+                          "frac_of_measured_peak":
+                              step_bytes / (ms_step * 1e-3) / 1e9 / peak,
+                          "frac_of_8tbs": step_bytes / (ms_step * 1e-3) / 8e12},
+        "stages_us_per_layer": {"score": ms_score * 1e3,
+                                "select": ms_select * 1e3,
+                                "decode_split_merge": ms_decode * 1e3},
+        "dense": {"ms_per_step": ms_dense, "bytes": b_dense,
+                  "gbs": b_dense / (ms_dense * 1e-3) / 1e9,
+                  "speedup_sparse_over_dense": ms_dense / ms_step},
+        "build": {"bulk_ms": t_build, "tail_ms_per_finalize": t_tail,
+                  "tail_ms_amortised_per_step": t_tail / sh.page},
+        "cpu_baseline": cpu,
+    }
+    if world > 1:
+        dist.destroy_process_group()
+    return line
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=16)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", dest="workload_name", default="c1")
+    ap.add_argument("--ctx", type=int, default=None)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    sh, ctx = workload(args.workload_name, args.ctx)
+    seq_len = ctx + 1
+    rank = int(os.environ.get("RANK", "0"))
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        print(json.dumps(run_reference(args, sh, seq_len)), flush=True)
+        return
+    line = run_gpu(args, sh, seq_len)
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

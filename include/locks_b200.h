@@ -1,0 +1,198 @@
+/*
+ * liblocks_b200 -- C ABI of the B200 (sm_100a) LOCKS decode hot path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream, and
+ * returns 0 on success or a negative LOCKS_ERR_* code (message available from
+ * locks_last_error()).  Unless stated otherwise an entry point only enqueues
+ * work on `stream`: it never allocates, never synchronises and never throws,
+ * so every call is legal inside CUDA-graph capture.  The caller owns every
+ * buffer.  Strides are in ELEMENTS of the pointed-to type.
+ *
+ * Each declaration names the reference interface it replaces (paths relative to
+ * the reference's src/locks/).  The reference binds its kernels with pybind11
+ * modules that take torch::Tensor (e.g. selection/rki4_score_cuda.py:2518-2619);
+ * the raw-pointer argument lists below carry the same information.
+ *
+ * Geometry supported by this build: head_dim 128, page 16, summary rank 8,
+ * int4 basis, 1 <= G <= 16 query heads per KV head.
+ */
+#ifndef LOCKS_B200_H_
+#define LOCKS_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LOCKS_ABI_VERSION 1
+
+/* One summary record per (physical block, kv-head):
+ *   [0,512)   V basis, 8 columns x 64 B, int4 (low nibble = even d row)
+ *   [512,640) page centroid mu, int8 x 128
+ *   [640,768) coefficients C, int8, 16 tokens x 8
+ *   [768,800) per-token C scales, bf16 x 16
+ *   [800,816) per-column V scales, bf16 x 8
+ *   [816,818) mu scale, bf16          [818,832) zero padding
+ * Same fields as the reference's six slabs (selection/rki4_state.py:7-22), laid
+ * out as its 832-byte "AoS" record (selection/rki4_state.py:93-102,198-220). */
+#define LOCKS_REC_BYTES 832
+#define LOCKS_TAG_WIDTH 8
+
+#define LOCKS_OK             0
+#define LOCKS_ERR_ARG       (-1)  /* null pointer, negative size, bad stride  */
+#define LOCKS_ERR_GEOMETRY  (-2)  /* head_dim/page/G outside the supported set */
+#define LOCKS_ERR_LAUNCH    (-3)  /* CUDA reported an error at launch          */
+#define LOCKS_ERR_SIZE      (-4)  /* size beyond a stated maximum              */
+
+/* values a kernel may leave in a caller-provided device `status` word */
+#define LOCKS_ST_OK            0
+#define LOCKS_ST_WAIT_TIMEOUT  1  /* a bounded on-chip wait ran out            */
+
+#define LOCKS_COMBINE_NONE 0      /* `score` already holds the combined score  */
+#define LOCKS_COMBINE_NRM  1      /* sum_g exp(S[g,p] - max_p S[g,p])          */
+#define LOCKS_COMBINE_MAX  2      /* max_g S[g,p]                              */
+
+typedef void* locks_stream_t;     /* a cudaStream_t */
+
+int locks_version(void);
+const char* locks_last_error(void);
+/* Bytes of one summary record (without the tag).  Replaces
+ * selection/rki4_state.py:124-141 record_bytes() for the supported geometry;
+ * returns LOCKS_ERR_GEOMETRY otherwise. */
+int locks_record_bytes(int head_dim, int page);
+
+/* ---- Stage A.0: rki4 summary build ---------------------------------------
+ * For every layer in [layer0, layer0+n_layers) and every block id in
+ * blocks[0..n_blocks): read the 16 x head_dim bf16 keys of each kv-head, form the
+ * centroid, the centred 16x16 Gram, its eigen-decomposition (Jacobi, fp32), the
+ * rank-8 factors, quantise and write the record + the content tag.  Block ids
+ * outside [0, min(num_blocks_state, num_blocks_cache)) are skipped.
+ * k_layers: DEVICE array of n_total_layers pointers to each layer's K plane.
+ * records: (n_total_layers, num_blocks_state, n_kv, 832) bytes; tags: same
+ * leading dims x 8 bf16.
+ * Replaces selection/rki4_build.py:228-261 (_rki4_write: _write_pre, eigh,
+ * _write_post) and the (layer, block) pair expansion of selection/build.py:388-396. */
+int locks_rki4_build(const void* const* k_layers, int64_t k_stride_block,
+                     int64_t k_stride_tok, int64_t k_stride_head,
+                     void* records, void* tags, const int32_t* blocks,
+                     int n_blocks, int layer0, int n_layers,
+                     int num_blocks_state, int num_blocks_cache, int n_kv,
+                     int head_dim, int page, locks_stream_t stream);
+
+/* Content-tag staleness scan: stale[i] = 1 when valid[i] != 0 and the stored
+ * tag of blocks[i] differs from the live keys in ANY layer (NaN never equals).
+ * Replaces selection/build.py:475-488 (_delta_select) up to its final boolean
+ * gather, which stays on the host. */
+int locks_rki4_tag_scan(const void* const* k_layers, int64_t k_stride_block,
+                        int64_t k_stride_tok, int64_t k_stride_head,
+                        const void* tags, const int32_t* blocks,
+                        const uint8_t* valid, uint8_t* stale, int n_blocks,
+                        int n_layers, int num_blocks_state, int n_kv, int page,
+                        locks_stream_t stream);
+
+/* ---- Stage A.1: per-step page parameters ---------------------------------
+ * n_pages = ceil(seq_len/page); n_sel_hi = n_pages - window;
+ * s = n_sel_hi - sink; b = budget_pages > 0 ? max(min(budget_pages, max(s,1)),1)
+ *                        : min(max((int)ceil(s*budget),1), max(s,1)) in fp64.
+ * Replaces selection/select.py:28-58 (derive_page_params). */
+int locks_derive_page_params(const int32_t* seq_lens, int n_req, int page,
+                             int window_pages, int sink_pages, int budget_pages,
+                             double budget, int32_t* n_pages, int32_t* n_sel_hi,
+                             int32_t* b_fix, locks_stream_t stream);
+
+/* ---- Stage A.2: page score ------------------------------------------------
+ * score_h[r,kh,g,p] = logsumexp_t scale*(cs[t]*sum_r C8[t,r]*qt[g,r] + mu.q)
+ * for p < n_sel_hi[r], with q round-tripped through per-head int8 and the page
+ * summary read at block_table[r,p] (clamped into [0,num_blocks)).
+ * q: bf16 (n_req, n_kv*G, head_dim).  score_h: f32 (n_req, n_kv, G, max_pages).
+ * hmax: optional (n_req, n_kv, G) uint32 keys, atomically raised to the
+ * order-preserving key of each head's maximum score (pass NULL to skip).
+ * zsplit <= 0 selects the page split automatically.  status: optional device int.
+ * Replaces selection/rki4_score_cuda.py:2518-2619 (rki4_score_bt) /
+ * :3263-3448 (rki4_score_only); CPU twin selection/rki4_score_torch.py:111-160. */
+int locks_rki4_score_bt(const void* q, int64_t q_stride_req,
+                        const void* records_layer, const int32_t* block_table,
+                        int64_t bt_stride, const int32_t* n_sel_hi,
+                        float* score_h, uint32_t* hmax, int n_req, int n_kv,
+                        int G, int head_dim, int page, int max_pages,
+                        int bt_width, int num_blocks, float scale, int zsplit,
+                        int* status, locks_stream_t stream);
+
+/* ---- Stage A.3: GQA combine + exact top-b ---------------------------------
+ * combine: LOCKS_COMBINE_*.  For NRM/MAX the combined score of pages
+ * [0, n_sel_hi) is also written to `score` (n_req, n_kv, max_pages).
+ * tau = b-th largest score over [sink, n_sel_hi); keep {> tau}, then {== tau}
+ * in ascending page order until exactly b are kept, plus [0,sink) and
+ * [n_sel_hi, n_pages); keep everything if n_sel_hi - sink <= 1.  page_table
+ * (n_req, n_kv, max_pages) gets ascending page ids, -1 padded; page_cnt the count.
+ * hmax: optional keys published by locks_rki4_score_bt (read, then reset to 0).
+ * Replaces selection/select_cuda.py:492-938 (nrmtopb_select_kernel),
+ * :162-449 (topb_select_kernel) and the long-context chain :1786-3249;
+ * goldens selection/select.py:65-117 and :123-180. */
+int locks_topb_select(int combine, const float* score_h, float* score,
+                      uint32_t* hmax, const int32_t* n_pages,
+                      const int32_t* n_sel_hi, const int32_t* b_fix,
+                      int32_t* page_table, int32_t* page_cnt, int n_req,
+                      int n_kv, int G, int max_pages, int sink_pages,
+                      locks_stream_t stream);
+
+/* ---- Stage B: sparse paged decode -----------------------------------------
+ * Split-K flash decode over the selected pages.  k_cache/v_cache: bf16 planes
+ * addressed [block*stride_block + tok*stride_tok + head*stride_head + d].
+ * pps = max(ceil(cnt/split), pps_min); split sp covers table entries
+ * [sp*pps, min((sp+1)*pps, cnt)); inactive splits store nothing.
+ * m_part, l_part: f32 (n_req, n_kv, split, G); acc_part: (.., G, head_dim).
+ * Replaces attention/decode.py:209-322 (sparse_decode_split_kernel) and
+ * attention/decode_cuda.py:269-547 (locks_decode_split). */
+int locks_decode_split(const void* q, int64_t q_stride_req, const void* k_cache,
+                       const void* v_cache, int64_t kv_stride_block,
+                       int64_t kv_stride_tok, int64_t kv_stride_head,
+                       const int32_t* block_table, int64_t bt_stride,
+                       const int32_t* page_table, const int32_t* page_cnt,
+                       const int32_t* seq_lens, float* m_part, float* l_part,
+                       float* acc_part, int n_req, int n_kv, int G,
+                       int head_dim, int page, int max_pages, int split,
+                       int pps_min, float scale, int* status,
+                       locks_stream_t stream);
+
+/* Merge of the active split partials into out (bf16, row stride
+ * out_stride_req, heads contiguous); rows without attended pages become 0.
+ * Replaces attention/merge.py:105-152 (merge_splits_kernel). */
+int locks_merge_splits(const float* m_part, const float* l_part,
+                       const float* acc_part, const int32_t* page_cnt,
+                       void* out, int64_t out_stride_req, int n_req, int n_kv,
+                       int G, int head_dim, int split, int pps_min,
+                       locks_stream_t stream);
+
+/* One-launch decode: a CTA per (kv-head, request) walks all selected pages and
+ * writes the final bf16 output (no partials, no merge launch).
+ * Replaces attention/decode_cuda.py:587-884 (locks_decode_fused). */
+int locks_decode_fused(const void* q, int64_t q_stride_req, const void* k_cache,
+                       const void* v_cache, int64_t kv_stride_block,
+                       int64_t kv_stride_tok, int64_t kv_stride_head,
+                       const int32_t* block_table, int64_t bt_stride,
+                       const int32_t* page_table, const int32_t* page_cnt,
+                       const int32_t* seq_lens, void* out,
+                       int64_t out_stride_req, int n_req, int n_kv, int G,
+                       int head_dim, int page, int max_pages, float scale,
+                       int* status, locks_stream_t stream);
+
+/* Dense full-KV paged decode (every page of every request) with the same
+ * split kernel and merge: the baseline of the sparse/dense crossover curve.
+ * The reference takes its dense baseline from FlashAttention
+ * (backend/attn.py:253-267 delegates there); it has no kernel of its own. */
+int locks_dense_decode(const void* q, int64_t q_stride_req, const void* k_cache,
+                       const void* v_cache, int64_t kv_stride_block,
+                       int64_t kv_stride_tok, int64_t kv_stride_head,
+                       const int32_t* block_table, int64_t bt_stride,
+                       const int32_t* seq_lens, float* m_part, float* l_part,
+                       float* acc_part, void* out, int64_t out_stride_req,
+                       int n_req, int n_kv, int G, int head_dim, int page,
+                       int split, float scale, int* status,
+                       locks_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* LOCKS_B200_H_ */

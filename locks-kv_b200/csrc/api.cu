@@ -1,0 +1,66 @@
+// Library-level entry points and host-side error plumbing.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace locks {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+        return fail(LOCKS_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+    return LOCKS_OK;
+}
+
+// SM count of the current device, cached per device id (read-only after the
+// first query; the only per-device state the library keeps).
+int sm_count() {
+    static int cache[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cache[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) !=
+                cudaSuccess || n <= 0)
+            n = 148;
+        cache[dev] = n;
+    }
+    return cache[dev];
+}
+
+}  // namespace locks
+
+extern "C" {
+
+int locks_version(void) { return LOCKS_ABI_VERSION; }
+
+const char* locks_last_error(void) { return locks::g_err; }
+
+int locks_record_bytes(int head_dim, int page) {
+    if (head_dim != 128 || page != 16)
+        return locks::fail(LOCKS_ERR_GEOMETRY,
+                           "record layout is defined for head_dim 128 / page 16, "
+                           "got %d / %d", head_dim, page);
+    return LOCKS_REC_BYTES;
+}
+
+}  // extern "C"

@@ -1,0 +1,525 @@
+// Sparse paged decode: split-K flash decode over the selected pages, the split
+// merge, the one-launch fused variant and the dense full-KV baseline.
+//
+// One kernel serves all three.  A CTA (4 warps) owns one (request, kv-head) and
+// a contiguous run of page-table entries; its warps take entries round-robin
+// and each warp runs its own 2-stage shared-memory ring: 32 lanes issue 32 bulk
+// async copies (16 key rows + 16 value rows of 256 B, found through the page
+// table and the block table) that complete on the warp's mbarrier.  Rows past
+// seq_len are zero-filled instead of copied, so stale cache bytes cannot leak.
+//
+// Math per page, on warp-level tensor-core fragments whose 16 rows are the
+// query heads of the GQA group:  S = Q K^T (bf16, 16 m16n8k16 steps), online
+// softmax in fp32, O += P V with P split into two bf16 terms (32 steps), i.e.
+// P keeps 16 mantissa bits.  The four warps' (m, l, O) are combined through
+// shared memory; the CTA then stores either one split partial or, in fused
+// mode, the normalised bf16 output row.
+#include "common.cuh"
+
+namespace locks {
+namespace {
+
+constexpr int DW = 4;                 // warps per CTA
+constexpr int DTHREADS = DW * 32;
+constexpr int DSTAGES = 2;
+constexpr int PAGE_T = 16;
+constexpr int HD = 128;
+constexpr int ROWB = HD * 2 + 16;     // 272 B row pitch: conflict-free ldmatrix
+constexpr int ACC_PITCH = HD + 4;     // floats
+
+struct WarpBuf {
+    uint8_t k[DSTAGES][PAGE_T][ROWB];
+    uint8_t v[DSTAGES][PAGE_T][ROWB];
+};
+static_assert(sizeof(WarpBuf) >= 16 * ACC_PITCH * 4, "combine buffer must fit");
+
+struct __align__(128) DecSmem {
+    WarpBuf wb[DW];
+    uint64_t full[DW][DSTAGES];
+    float cm[DW][16];
+    float cl[DW][16];
+};
+
+struct DecParams {
+    const __nv_bfloat16* q;
+    int64_t q_stride_req;
+    const __nv_bfloat16* k_cache;
+    const __nv_bfloat16* v_cache;
+    int64_t stride_block, stride_tok, stride_head;
+    const int32_t* block_table;
+    int64_t bt_stride;
+    const int32_t* page_table;     // nullptr: dense (entry j is page j)
+    const int32_t* page_cnt;       // nullptr in dense mode
+    const int32_t* seq_lens;
+    float* m_part;
+    float* l_part;
+    float* acc_part;
+    __nv_bfloat16* out;            // fused mode only
+    int64_t out_stride_req;
+    int n_kv, G, max_pages, split, pps_min, fused;
+    float scale;
+    int* status;
+};
+
+__device__ __forceinline__ void issue_page(DecSmem& sm, const DecParams& p,
+                                           int warp, int lane, int stage,
+                                           int r, int kh, int64_t row, int j,
+                                           int seq_len, int& n_valid_out) {
+    int pt = p.page_table ? p.page_table[row * p.max_pages + j] : j;
+    int n_valid = (pt >= 0) ? min(max(seq_len - pt * PAGE_T, 0), PAGE_T) : 0;
+    pt = max(pt, 0);
+    const int blk = max(p.block_table[(int64_t)r * p.bt_stride + pt], 0);
+    n_valid_out = n_valid;
+    uint64_t* bar = &sm.full[warp][stage];
+    fence_proxy_async();
+    if (lane == 0) mbar_expect_tx(bar, (uint32_t)n_valid * 2u * (HD * 2));
+    __syncwarp();
+    const int t = lane & 15;
+    const bool is_v = lane >= 16;
+    uint8_t* dst = is_v ? &sm.wb[warp].v[stage][t][0] : &sm.wb[warp].k[stage][t][0];
+    if (t < n_valid) {
+        const __nv_bfloat16* base = is_v ? p.v_cache : p.k_cache;
+        const __nv_bfloat16* src = base + (int64_t)blk * p.stride_block +
+                                   (int64_t)t * p.stride_tok +
+                                   (int64_t)kh * p.stride_head;
+        bulk_g2s(dst, src, HD * 2, bar);
+    } else {
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+        for (int i = 0; i < (HD * 2) / 16; ++i) d4[i] = make_uint4(0, 0, 0, 0);
+    }
+}
+
+template <bool G_HI>
+__global__ void __launch_bounds__(DTHREADS)
+decode_kernel(const DecParams p) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    DecSmem& sm = *reinterpret_cast<DecSmem*>(smem_raw);
+
+    const int sp = blockIdx.x, kh = blockIdx.y, r = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int G = p.G;
+    const int64_t row = (int64_t)r * p.n_kv + kh;
+    const int seq_len = p.seq_lens[r];
+
+    const int cnt = p.page_cnt ? p.page_cnt[row]
+                               : (max(seq_len, 0) + PAGE_T - 1) / PAGE_T;
+    int j0, j1;
+    if (p.fused) {
+        j0 = 0; j1 = cnt;
+    } else {
+        const int pps = max((cnt + p.split - 1) / p.split, p.pps_min);
+        j0 = sp * pps;
+        if (j0 >= cnt) return;                    // inactive split: no store
+        j1 = min(j0 + pps, cnt);
+    }
+
+    if (tid == 0) {
+        for (int w = 0; w < DW; ++w)
+            for (int s = 0; s < DSTAGES; ++s) mbar_init(&sm.full[w][s], 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    // pages of this warp: j0 + warp, j0 + warp + DW, ...
+    const int first = j0 + warp;
+    const int n_mine = (first < j1) ? (j1 - first + DW - 1) / DW : 0;
+    int nv[DSTAGES] = {0, 0};
+    for (int it = 0; it < DSTAGES && it < n_mine; ++it)
+        issue_page(sm, p, warp, lane, it, r, kh, row, first + it * DW, seq_len,
+                   nv[it]);
+
+    // ---- Q fragments (A operand), rows gid and gid+8 -------------------------
+    uint32_t qa[8][4];
+    {
+        const __nv_bfloat16* q0 =
+            p.q + (int64_t)r * p.q_stride_req + (int64_t)(kh * G) * HD;
+        const bool live0 = gid < G, live1 = G_HI && (gid + 8 < G);
+        const uint32_t* r0 = reinterpret_cast<const uint32_t*>(q0 + (int64_t)gid * HD);
+        const uint32_t* r1 =
+            reinterpret_cast<const uint32_t*>(q0 + (int64_t)(gid + 8) * HD);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            qa[ks][0] = live0 ? r0[8 * ks + tig] : 0u;
+            qa[ks][1] = live1 ? r1[8 * ks + tig] : 0u;
+            qa[ks][2] = live0 ? r0[8 * ks + 4 + tig] : 0u;
+            qa[ks][3] = live1 ? r1[8 * ks + 4 + tig] : 0u;
+        }
+    }
+
+    float acc[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+    const float scale = p.scale;
+
+    for (int it = 0; it < n_mine; ++it) {
+        const int stage = it % DSTAGES;
+        mbar_wait(&sm.full[warp][stage], (uint32_t)((it / DSTAGES) & 1), p.status);
+        __syncwarp();
+        const int n_valid = nv[stage];
+        if (n_valid > 0) {
+            const uint32_t kbase = smem_u32(&sm.wb[warp].k[stage][0][0]);
+            const uint32_t vbase = smem_u32(&sm.wb[warp].v[stage][0][0]);
+            // ---- S = Q K^T : two 16x8 token tiles ----------------------------
+            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+            {
+                const int t = (lane & 7) + 8 * ((lane >> 4) & 1);
+                const uint32_t a0 = kbase + t * ROWB + 16 * ((lane >> 3) & 1);
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    uint32_t kb[4];
+                    ldmatrix_x4(kb, a0 + 32 * ks);
+                    mma_bf16_k16(s0, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3],
+                                 kb[0], kb[1]);
+                    mma_bf16_k16(s1, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3],
+                                 kb[2], kb[3]);
+                }
+            }
+            // ---- scale, mask the tail of a partial page -----------------------
+            const int ta = 2 * tig, tb = 2 * tig + 1;
+            float x[8];        // [0..3] row gid: t = ta, tb, ta+8, tb+8; [4..7] row gid+8
+            x[0] = (ta < n_valid) ? s0[0] * scale : -INFINITY;
+            x[1] = (tb < n_valid) ? s0[1] * scale : -INFINITY;
+            x[2] = (ta + 8 < n_valid) ? s1[0] * scale : -INFINITY;
+            x[3] = (tb + 8 < n_valid) ? s1[1] * scale : -INFINITY;
+            x[4] = (ta < n_valid) ? s0[2] * scale : -INFINITY;
+            x[5] = (tb < n_valid) ? s0[3] * scale : -INFINITY;
+            x[6] = (ta + 8 < n_valid) ? s1[2] * scale : -INFINITY;
+            x[7] = (tb + 8 < n_valid) ? s1[3] * scale : -INFINITY;
+            // ---- online softmax ----------------------------------------------
+            float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float mn_lo = fmaxf(m_lo, mx);       // finite: token 0 is valid
+            const float al_lo = __expf(m_lo - mn_lo);
+            float pr[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) pr[i] = __expf(x[i] - mn_lo);
+            l_lo = l_lo * al_lo + (pr[0] + pr[1] + pr[2] + pr[3]);
+            m_lo = mn_lo;
+            float al_hi = 1.f;
+            if (G_HI) {
+                float mh = fmaxf(fmaxf(x[4], x[5]), fmaxf(x[6], x[7]));
+                mh = fmaxf(mh, __shfl_xor_sync(0xffffffffu, mh, 1));
+                mh = fmaxf(mh, __shfl_xor_sync(0xffffffffu, mh, 2));
+                const float mn_hi = fmaxf(m_hi, mh);
+                al_hi = __expf(m_hi - mn_hi);
+#pragma unroll
+                for (int i = 4; i < 8; ++i) pr[i] = __expf(x[i] - mn_hi);
+                l_hi = l_hi * al_hi + (pr[4] + pr[5] + pr[6] + pr[7]);
+                m_hi = mn_hi;
+            } else {
+                pr[4] = pr[5] = pr[6] = pr[7] = 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                acc[i][0] *= al_lo; acc[i][1] *= al_lo;
+                if (G_HI) { acc[i][2] *= al_hi; acc[i][3] *= al_hi; }
+            }
+            // ---- P as hi + lo bf16 (A operand, k = 16 tokens) ------------------
+            uint32_t ph[4], pl[4];
+            {
+                float hi[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    hi[i] = __bfloat162float(__float2bfloat16_rn(pr[i]));
+                ph[0] = pack_bf16x2(hi[0], hi[1]);           // row gid,   t 0-7
+                ph[1] = pack_bf16x2(hi[4], hi[5]);           // row gid+8, t 0-7
+                ph[2] = pack_bf16x2(hi[2], hi[3]);           // row gid,   t 8-15
+                ph[3] = pack_bf16x2(hi[6], hi[7]);           // row gid+8, t 8-15
+                pl[0] = pack_bf16x2(pr[0] - hi[0], pr[1] - hi[1]);
+                pl[1] = pack_bf16x2(pr[4] - hi[4], pr[5] - hi[5]);
+                pl[2] = pack_bf16x2(pr[2] - hi[2], pr[3] - hi[3]);
+                pl[3] = pack_bf16x2(pr[6] - hi[6], pr[7] - hi[7]);
+            }
+            // ---- O += P V ------------------------------------------------------
+            {
+                const int t = (lane & 7) + 8 * ((lane >> 3) & 1);
+                const uint32_t a0 = vbase + t * ROWB + 16 * ((lane >> 4) & 1);
+#pragma unroll
+                for (int dp = 0; dp < 8; ++dp) {
+                    uint32_t vb[4];
+                    ldmatrix_x4_trans(vb, a0 + 32 * dp);
+                    mma_bf16_k16(acc[2 * dp], ph[0], ph[1], ph[2], ph[3], vb[0], vb[1]);
+                    mma_bf16_k16(acc[2 * dp], pl[0], pl[1], pl[2], pl[3], vb[0], vb[1]);
+                    mma_bf16_k16(acc[2 * dp + 1], ph[0], ph[1], ph[2], ph[3], vb[2], vb[3]);
+                    mma_bf16_k16(acc[2 * dp + 1], pl[0], pl[1], pl[2], pl[3], vb[2], vb[3]);
+                }
+            }
+        }
+        __syncwarp();                               // stage fully consumed
+        if (it + DSTAGES < n_mine)
+            issue_page(sm, p, warp, lane, stage, r, kh, row,
+                       first + (it + DSTAGES) * DW, seq_len, nv[stage]);
+    }
+
+    // ---- combine the four warps ------------------------------------------------
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    if (G_HI) {
+        l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+        l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    }
+    __syncthreads();           // every warp's ring is idle: reuse it as fp32 scratch
+    float* wacc = reinterpret_cast<float*>(&sm.wb[warp]);
+    if (tig == 0) {
+        sm.cm[warp][gid] = m_lo; sm.cl[warp][gid] = l_lo;
+        sm.cm[warp][gid + 8] = G_HI ? m_hi : -INFINITY;
+        sm.cl[warp][gid + 8] = G_HI ? l_hi : 0.f;
+    }
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+        *reinterpret_cast<float2*>(&wacc[gid * ACC_PITCH + 8 * nt + 2 * tig]) =
+            make_float2(acc[nt][0], acc[nt][1]);
+        if (G_HI)
+            *reinterpret_cast<float2*>(
+                &wacc[(gid + 8) * ACC_PITCH + 8 * nt + 2 * tig]) =
+                make_float2(acc[nt][2], acc[nt][3]);
+    }
+    __syncthreads();
+
+    const int d = tid;                            // 128 threads = 128 channels
+    for (int g = 0; g < G; ++g) {
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DW; ++w) M = fmaxf(M, sm.cm[w][g]);
+        float Lsum = 0.f, o = 0.f;
+#pragma unroll
+        for (int w = 0; w < DW; ++w) {
+            const float lw = sm.cl[w][g];
+            const float wt = (lw > 0.f) ? __expf(sm.cm[w][g] - M) : 0.f;
+            Lsum += wt * lw;
+            o += wt * reinterpret_cast<const float*>(&sm.wb[w])[g * ACC_PITCH + d];
+        }
+        if (p.fused) {
+            const float val = (Lsum > 0.f) ? o / Lsum : 0.f;
+            p.out[(int64_t)r * p.out_stride_req + (int64_t)(kh * G + g) * HD + d] =
+                __float2bfloat16_rn(val);
+        } else {
+            const int64_t base = (row * p.split + sp) * G + g;
+            p.acc_part[base * HD + d] = o;
+            if (d == 0) { p.m_part[base] = M; p.l_part[base] = Lsum; }
+        }
+    }
+}
+
+struct MergeParams {
+    const float* m_part;
+    const float* l_part;
+    const float* acc_part;
+    const int32_t* page_cnt;       // or nullptr with seq_lens set (dense)
+    const int32_t* seq_lens;
+    __nv_bfloat16* out;
+    int64_t out_stride_req;
+    int n_kv, G, split, pps_min;
+};
+
+// grid (n_kv*G, n_req), 128 threads: thread d owns one output channel.
+__global__ void __launch_bounds__(HD) merge_kernel(const MergeParams p) {
+    const int h = blockIdx.x, r = blockIdx.y, d = threadIdx.x;
+    const int kh = h / p.G, g = h % p.G;
+    const int64_t row = (int64_t)r * p.n_kv + kh;
+    const int cnt = p.page_cnt ? p.page_cnt[row]
+                               : (max(p.seq_lens[r], 0) + PAGE_T - 1) / PAGE_T;
+    const int pps = max((cnt + p.split - 1) / p.split, p.pps_min);
+    const int n_act = (cnt + pps - 1) / pps;
+    const int64_t base = row * p.split * p.G + g;
+    float M = -INFINITY;
+    for (int s = 0; s < n_act; ++s) M = fmaxf(M, p.m_part[base + (int64_t)s * p.G]);
+    float Lsum = 0.f, o = 0.f;
+    for (int s = 0; s < n_act; ++s) {
+        const int64_t i = base + (int64_t)s * p.G;
+        const float l = p.l_part[i];
+        const float w = (l > 0.f) ? __expf(p.m_part[i] - M) : 0.f;
+        Lsum += w * l;
+        o += w * p.acc_part[i * HD + d];
+    }
+    const float val = (Lsum > 0.f) ? o / Lsum : 0.f;
+    p.out[(int64_t)r * p.out_stride_req + (int64_t)h * HD + d] =
+        __float2bfloat16_rn(val);
+}
+
+int check_geometry(const char* who, int G, int head_dim, int page) {
+    LOCKS_REQUIRE(head_dim == HD && page == PAGE_T, LOCKS_ERR_GEOMETRY,
+                  "%s: supports head_dim 128 / page 16, got %d / %d", who,
+                  head_dim, page);
+    LOCKS_REQUIRE(G >= 1 && G <= 16, LOCKS_ERR_GEOMETRY,
+                  "%s: supports 1 <= G <= 16, got %d", who, G);
+    return LOCKS_OK;
+}
+
+int launch_decode(const char* who, const DecParams& p, int n_req, int grid_x,
+                  cudaStream_t s) {
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int smem = (int)sizeof(DecSmem);
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        cudaFuncSetAttribute(decode_kernel<false>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaFuncSetAttribute(decode_kernel<true>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        attr_done[dev] = true;
+    }
+    dim3 grid(grid_x, p.n_kv, n_req);
+    if (p.G > 8)
+        decode_kernel<true><<<grid, DTHREADS, smem, s>>>(p);
+    else
+        decode_kernel<false><<<grid, DTHREADS, smem, s>>>(p);
+    return check_launch(who);
+}
+
+int check_kv(const char* who, const void* q, const void* k, const void* v,
+             int64_t q_stride_req, int64_t sb, int64_t st, int64_t sh) {
+    LOCKS_REQUIRE((reinterpret_cast<uintptr_t>(k) & 15) == 0 &&
+                      (reinterpret_cast<uintptr_t>(v) & 15) == 0 &&
+                      (reinterpret_cast<uintptr_t>(q) & 3) == 0,
+                  LOCKS_ERR_ARG, "%s: k/v caches must be 16-byte aligned", who);
+    LOCKS_REQUIRE(sb % 8 == 0 && st % 8 == 0 && sh % 8 == 0 &&
+                      q_stride_req % 2 == 0,
+                  LOCKS_ERR_ARG,
+                  "%s: cache strides must be multiples of 8 elements (16 bytes)",
+                  who);
+    return LOCKS_OK;
+}
+
+}  // namespace
+}  // namespace locks
+
+using namespace locks;
+
+extern "C" int locks_decode_split(
+    const void* q, int64_t q_stride_req, const void* k_cache,
+    const void* v_cache, int64_t kv_stride_block, int64_t kv_stride_tok,
+    int64_t kv_stride_head, const int32_t* block_table, int64_t bt_stride,
+    const int32_t* page_table, const int32_t* page_cnt, const int32_t* seq_lens,
+    float* m_part, float* l_part, float* acc_part, int n_req, int n_kv, int G,
+    int head_dim, int page, int max_pages, int split, int pps_min, float scale,
+    int* status, locks_stream_t stream) {
+    LOCKS_REQUIRE(q && k_cache && v_cache && block_table && page_table &&
+                      page_cnt && seq_lens && m_part && l_part && acc_part,
+                  LOCKS_ERR_ARG, "locks_decode_split: null pointer argument");
+    int rc = check_geometry("locks_decode_split", G, head_dim, page);
+    if (rc) return rc;
+    rc = check_kv("locks_decode_split", q, k_cache, v_cache, q_stride_req,
+                  kv_stride_block, kv_stride_tok, kv_stride_head);
+    if (rc) return rc;
+    LOCKS_REQUIRE(n_req >= 0 && n_req <= 65535 && n_kv >= 1 && n_kv <= 65535 &&
+                      split >= 1 && pps_min >= 1 && max_pages >= 1,
+                  LOCKS_ERR_ARG, "locks_decode_split: bad size argument");
+    if (n_req == 0) return LOCKS_OK;
+    DecParams p{};
+    p.q = static_cast<const __nv_bfloat16*>(q); p.q_stride_req = q_stride_req;
+    p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
+    p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
+    p.stride_block = kv_stride_block; p.stride_tok = kv_stride_tok;
+    p.stride_head = kv_stride_head;
+    p.block_table = block_table; p.bt_stride = bt_stride;
+    p.page_table = page_table; p.page_cnt = page_cnt; p.seq_lens = seq_lens;
+    p.m_part = m_part; p.l_part = l_part; p.acc_part = acc_part;
+    p.n_kv = n_kv; p.G = G; p.max_pages = max_pages; p.split = split;
+    p.pps_min = pps_min; p.fused = 0; p.scale = scale; p.status = status;
+    return launch_decode("locks_decode_split", p, n_req, split,
+                         static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int locks_merge_splits(
+    const float* m_part, const float* l_part, const float* acc_part,
+    const int32_t* page_cnt, void* out, int64_t out_stride_req, int n_req,
+    int n_kv, int G, int head_dim, int split, int pps_min,
+    locks_stream_t stream) {
+    LOCKS_REQUIRE(m_part && l_part && acc_part && page_cnt && out, LOCKS_ERR_ARG,
+                  "locks_merge_splits: null pointer argument");
+    LOCKS_REQUIRE(head_dim == HD, LOCKS_ERR_GEOMETRY,
+                  "locks_merge_splits: supports head_dim 128, got %d", head_dim);
+    LOCKS_REQUIRE(n_req >= 0 && n_req <= 65535 && n_kv >= 1 && G >= 1 &&
+                      split >= 1 && pps_min >= 1,
+                  LOCKS_ERR_ARG, "locks_merge_splits: bad size argument");
+    if (n_req == 0) return LOCKS_OK;
+    MergeParams p{};
+    p.m_part = m_part; p.l_part = l_part; p.acc_part = acc_part;
+    p.page_cnt = page_cnt; p.seq_lens = nullptr;
+    p.out = static_cast<__nv_bfloat16*>(out); p.out_stride_req = out_stride_req;
+    p.n_kv = n_kv; p.G = G; p.split = split; p.pps_min = pps_min;
+    merge_kernel<<<dim3(n_kv * G, n_req), HD, 0,
+                   static_cast<cudaStream_t>(stream)>>>(p);
+    return check_launch("locks_merge_splits");
+}
+
+extern "C" int locks_decode_fused(
+    const void* q, int64_t q_stride_req, const void* k_cache,
+    const void* v_cache, int64_t kv_stride_block, int64_t kv_stride_tok,
+    int64_t kv_stride_head, const int32_t* block_table, int64_t bt_stride,
+    const int32_t* page_table, const int32_t* page_cnt, const int32_t* seq_lens,
+    void* out, int64_t out_stride_req, int n_req, int n_kv, int G, int head_dim,
+    int page, int max_pages, float scale, int* status, locks_stream_t stream) {
+    LOCKS_REQUIRE(q && k_cache && v_cache && block_table && page_table &&
+                      page_cnt && seq_lens && out,
+                  LOCKS_ERR_ARG, "locks_decode_fused: null pointer argument");
+    int rc = check_geometry("locks_decode_fused", G, head_dim, page);
+    if (rc) return rc;
+    rc = check_kv("locks_decode_fused", q, k_cache, v_cache, q_stride_req,
+                  kv_stride_block, kv_stride_tok, kv_stride_head);
+    if (rc) return rc;
+    LOCKS_REQUIRE(n_req >= 0 && n_req <= 65535 && n_kv >= 1 && n_kv <= 65535 &&
+                      max_pages >= 1,
+                  LOCKS_ERR_ARG, "locks_decode_fused: bad size argument");
+    if (n_req == 0) return LOCKS_OK;
+    DecParams p{};
+    p.q = static_cast<const __nv_bfloat16*>(q); p.q_stride_req = q_stride_req;
+    p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
+    p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
+    p.stride_block = kv_stride_block; p.stride_tok = kv_stride_tok;
+    p.stride_head = kv_stride_head;
+    p.block_table = block_table; p.bt_stride = bt_stride;
+    p.page_table = page_table; p.page_cnt = page_cnt; p.seq_lens = seq_lens;
+    p.out = static_cast<__nv_bfloat16*>(out); p.out_stride_req = out_stride_req;
+    p.n_kv = n_kv; p.G = G; p.max_pages = max_pages; p.split = 1;
+    p.pps_min = 1; p.fused = 1; p.scale = scale; p.status = status;
+    return launch_decode("locks_decode_fused", p, n_req, 1,
+                         static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int locks_dense_decode(
+    const void* q, int64_t q_stride_req, const void* k_cache,
+    const void* v_cache, int64_t kv_stride_block, int64_t kv_stride_tok,
+    int64_t kv_stride_head, const int32_t* block_table, int64_t bt_stride,
+    const int32_t* seq_lens, float* m_part, float* l_part, float* acc_part,
+    void* out, int64_t out_stride_req, int n_req, int n_kv, int G, int head_dim,
+    int page, int split, float scale, int* status, locks_stream_t stream) {
+    LOCKS_REQUIRE(q && k_cache && v_cache && block_table && seq_lens && m_part &&
+                      l_part && acc_part && out,
+                  LOCKS_ERR_ARG, "locks_dense_decode: null pointer argument");
+    int rc = check_geometry("locks_dense_decode", G, head_dim, page);
+    if (rc) return rc;
+    rc = check_kv("locks_dense_decode", q, k_cache, v_cache, q_stride_req,
+                  kv_stride_block, kv_stride_tok, kv_stride_head);
+    if (rc) return rc;
+    LOCKS_REQUIRE(n_req >= 0 && n_req <= 65535 && n_kv >= 1 && n_kv <= 65535 &&
+                      split >= 1 && split <= 65535,
+                  LOCKS_ERR_ARG, "locks_dense_decode: bad size argument");
+    if (n_req == 0) return LOCKS_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    DecParams p{};
+    p.q = static_cast<const __nv_bfloat16*>(q); p.q_stride_req = q_stride_req;
+    p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
+    p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
+    p.stride_block = kv_stride_block; p.stride_tok = kv_stride_tok;
+    p.stride_head = kv_stride_head;
+    p.block_table = block_table; p.bt_stride = bt_stride;
+    p.page_table = nullptr; p.page_cnt = nullptr; p.seq_lens = seq_lens;
+    p.m_part = m_part; p.l_part = l_part; p.acc_part = acc_part;
+    p.n_kv = n_kv; p.G = G; p.max_pages = 0; p.split = split; p.pps_min = 1;
+    p.fused = 0; p.scale = scale; p.status = status;
+    rc = launch_decode("locks_dense_decode", p, n_req, split, s);
+    if (rc) return rc;
+    MergeParams m{};
+    m.m_part = m_part; m.l_part = l_part; m.acc_part = acc_part;
+    m.page_cnt = nullptr; m.seq_lens = seq_lens;
+    m.out = static_cast<__nv_bfloat16*>(out); m.out_stride_req = out_stride_req;
+    m.n_kv = n_kv; m.G = G; m.split = split; m.pps_min = 1;
+    merge_kernel<<<dim3(n_kv * G, n_req), HD, 0, s>>>(m);
+    return check_launch("locks_dense_decode(merge)");
+}

@@ -1,0 +1,102 @@
+"""ctypes binding of ``liblocks_b200.so`` (the C ABI of include/locks_b200.h).
+
+This is the only way the Python host code reaches a kernel.  There is no
+fallback: if the library has not been built, or a call reports an error, a
+``RuntimeError`` is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import (POINTER, c_char_p, c_double, c_float, c_int, c_int64,
+                    c_void_p)
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "_lib", "liblocks_b200.so")
+
+_P, _I, _L, _F, _D = c_void_p, c_int, c_int64, c_float, c_double
+
+# name -> (argtypes, kernel launches per call)
+_SIGNATURES = {
+    "locks_version": ([], 0),
+    "locks_record_bytes": ([_I, _I], 0),
+    "locks_rki4_build": ([_P, _L, _L, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I,
+                          _I, _I, _P], 1),
+    "locks_rki4_tag_scan": ([_P, _L, _L, _L, _P, _P, _P, _P, _I, _I, _I, _I,
+                             _I, _P], 1),
+    "locks_derive_page_params": ([_P, _I, _I, _I, _I, _I, _D, _P, _P, _P, _P], 1),
+    "locks_rki4_score_bt": ([_P, _L, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I,
+                             _I, _I, _I, _I, _F, _I, _P, _P], 1),
+    "locks_topb_select": ([_I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I,
+                           _I, _P], 1),
+    "locks_decode_split": ([_P, _L, _P, _P, _L, _L, _L, _P, _L, _P, _P, _P, _P,
+                            _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P,
+                            _P], 1),
+    "locks_merge_splits": ([_P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I,
+                            _P], 1),
+    "locks_decode_fused": ([_P, _L, _P, _P, _L, _L, _L, _P, _L, _P, _P, _P, _P,
+                            _L, _I, _I, _I, _I, _I, _I, _F, _P, _P], 1),
+    "locks_dense_decode": ([_P, _L, _P, _P, _L, _L, _L, _P, _L, _P, _P, _P, _P,
+                            _P, _L, _I, _I, _I, _I, _I, _I, _F, _P, _P], 2),
+}
+
+_lib = None
+launches = 0          # kernels launched through this binding (bench evidence)
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library; raises if it is missing (no CPU fallback exists)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with "
+                "`python -m locks._build` (needs nvcc); the LOCKS B200 ops "
+                "have no other implementation")
+        L = ctypes.CDLL(LIB_PATH)
+        L.locks_last_error.restype = c_char_p
+        L.locks_last_error.argtypes = []
+        for name, (args, _) in _SIGNATURES.items():
+            if not hasattr(L, name):
+                continue                       # optional entry points
+            fn = getattr(L, name)
+            fn.argtypes = args
+            fn.restype = c_int
+        _lib = L
+    return _lib
+
+
+def register_signature(name, argtypes, n_launch=1):
+    """Declare an additional entry point (used by optional modules)."""
+    _SIGNATURES[name] = (argtypes, n_launch)
+    if _lib is not None and hasattr(_lib, name):
+        fn = getattr(_lib, name)
+        fn.argtypes = argtypes
+        fn.restype = c_int
+
+
+def call(name: str, *args) -> None:
+    """Invoke an entry point; non-zero return codes become RuntimeError."""
+    global launches
+    L = lib()
+    rc = getattr(L, name)(*args)
+    if rc != 0:
+        raise RuntimeError(
+            f"{name} failed ({rc}): {L.locks_last_error().decode()}")
+    launches += _SIGNATURES[name][1]
+
+
+def ptr(t) -> c_void_p:
+    """Device pointer of a CUDA tensor (None -> NULL)."""
+    if t is None:
+        return c_void_p(0)
+    if not t.is_cuda:
+        raise RuntimeError("LOCKS B200 kernels need CUDA tensors, got "
+                           f"{t.device} (there is no CPU path)")
+    return c_void_p(t.data_ptr())
+
+
+def stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)

@@ -1,0 +1,112 @@
+"""Attention-only driver of the decode hot path (what a model runner does
+around the kernels, without the model).
+
+``HotPath`` owns an :class:`Rki4State` for a set of per-layer paged KV caches,
+keeps the summaries valid (bulk build at start, tail build when a page
+finalises) and runs one decode step -- for every layer: score, select, sparse
+decode, merge -- as a single CUDA-graph replay.  It calls exactly the functions
+the vLLM hooks call (``backend/_runtime.py``).  Used by the benchmark, the
+smoke test and the end-to-end tests.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from . import _cabi
+from .attention import ResidentVSource, ensure_stage_b_buffers
+from .backend import _runtime
+from .config import LocksConfig
+from .selection import (Rki4State, derive_page_params, rki4_build_bulk,
+                        rki4_build_tail)
+
+
+class HotPath:
+    def __init__(self, kv_caches: List[torch.Tensor], block_table: torch.Tensor,
+                 seq_lens: torch.Tensor, *, n_kv: int, G: int, scale: float,
+                 cfg: LocksConfig, max_reqs: Optional[int] = None,
+                 split_cap: int = 128):
+        dev = kv_caches[0].device
+        self.device = dev
+        self.cfg = cfg
+        self.kv_caches = kv_caches
+        self.block_table = block_table
+        self.seq_lens = seq_lens
+        self.n_req = int(seq_lens.shape[0])
+        self.n_kv, self.G, self.scale = n_kv, G, float(scale)
+        NB, _, page, _, d = kv_caches[0].shape
+        self.page, self.d = int(page), int(d)
+        L = len(kv_caches)
+        st = Rki4State(dev, num_layers=L, num_blocks=int(NB), n_kv=n_kv, G=G,
+                       head_dim=int(d), page=int(page),
+                       max_reqs=max_reqs or self.n_req,
+                       max_pages=int(block_table.shape[1]),
+                       budget=cfg.budget if cfg.budget is not None else 0.1,
+                       budget_pages=cfg.budget_pages,
+                       sink_pages=cfg.sink_pages,
+                       window_pages=cfg.window_pages,
+                       combine=cfg.quad_combine, zsplit=cfg.rki4_zsplit)
+        st.scale = self.scale
+        st._layer_of = {int(c.data_ptr()): i for i, c in enumerate(kv_caches)}
+        ensure_stage_b_buffers(st, dev, split_cap)
+        self.st = st
+        self.K_layers = [c[:, 0] for c in kv_caches]
+        self.vsources = [ResidentVSource(c) for c in kv_caches]
+        H = n_kv * G
+        self.q = torch.zeros(L, st.max_reqs, H, d, device=dev, dtype=torch.bfloat16)
+        self.out = torch.zeros(L, st.max_reqs, H, d, device=dev, dtype=torch.bfloat16)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.launches_per_step = 0
+
+    # ---- summaries ---------------------------------------------------------
+    def build_all(self) -> int:
+        settled = self.seq_lens - 1
+        max_fin = int((settled.max().item()) // self.page)
+        return rki4_build_bulk(self.st, self.K_layers, self.block_table, settled,
+                               self.n_req, max_fin)
+
+    def build_tail(self, rows=None) -> int:
+        return rki4_build_tail(self.st, self.K_layers, self.block_table,
+                               self.seq_lens - 1, self.n_req, rows)
+
+    def derive(self) -> None:
+        derive_page_params(self.st, self.seq_lens, self.n_req)
+
+    # ---- one decode step ---------------------------------------------------
+    def _layers(self) -> None:
+        st, R = self.st, self.n_req
+        for l, kvc in enumerate(self.kv_caches):
+            q = self.q[l, :R]
+            _runtime._rki4_select_adapter(q, kvc, self.block_table,
+                                          self.seq_lens, st, R, self.scale,
+                                          self.cfg)
+            _runtime.decode_dispatch(q, kvc, self.block_table, self.seq_lens, st,
+                                     self.out[l], self.vsources[l], self.scale,
+                                     self.cfg)
+
+    def step_eager(self) -> torch.Tensor:
+        self._layers()
+        return self.out
+
+    def capture(self) -> None:
+        """Warm up (first-launch attribute set-up must happen outside capture)
+        and record the whole L-layer step into one CUDA graph."""
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self._layers()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        n0 = _cabi.launches
+        with torch.cuda.graph(g):
+            self._layers()
+        self.launches_per_step = _cabi.launches - n0
+        self.graph = g
+
+    def step(self) -> torch.Tensor:
+        if self.graph is None:
+            self.capture()
+        self.graph.replay()
+        return self.out

@@ -1,0 +1,23 @@
+"""Stage A -- decode-time page selection.
+
+  rki4_build_*(st, K_layers, block_table, settled_lens, ...)   page finalize
+  derive_page_params(st, seq_lens, n_req)                      once per step
+  rki4_score_state(st, layer, q, block_table, seq_lens, n_req, scale)
+        -> st.score_h -> st.score -> st.page_table / st.page_cnt
+
+All persistent state lives in :class:`Rki4State`.  Same surface as the
+reference's ``selection/__init__.py``.
+"""
+from __future__ import annotations
+
+from .rki4_build import (rki4_build_bulk, rki4_build_delta,
+                         rki4_build_refresh, rki4_build_tail)
+from .rki4_score import rki4_score_only, rki4_score_state, rki4_select_only
+from .rki4_state import TAGW, Rki4State
+from .select import derive_page_params, nrmtopb_select, topb_select
+
+__all__ = [
+    "Rki4State", "TAGW", "rki4_build_refresh", "rki4_build_tail",
+    "rki4_build_bulk", "rki4_build_delta", "derive_page_params", "topb_select",
+    "nrmtopb_select", "rki4_score_only", "rki4_select_only", "rki4_score_state",
+]

@@ -1,0 +1,44 @@
+"""Per-step page parameters and exact top-b page selection (host wrappers).
+
+``derive_page_params`` and ``topb_select`` keep the reference signatures
+(``selection/select.py:51-58`` and ``:183-222``); each is one kernel launch,
+fixed-shape, allocation-free and sync-free.
+"""
+from __future__ import annotations
+
+from .. import _cabi
+
+COMBINE_NONE, COMBINE_NRM, COMBINE_MAX = 0, 1, 2
+
+
+def derive_page_params(st, seq_lens, n_req: int) -> None:
+    """Refresh ``st.n_pages / n_sel_hi / b_fix`` for this decode step."""
+    assert n_req <= st.max_reqs
+    _cabi.call("locks_derive_page_params", _cabi.ptr(seq_lens), int(n_req),
+               int(st.page), int(st.window_pages), int(st.sink_pages),
+               int(getattr(st, "budget_abs", 0)), float(st.budget),
+               _cabi.ptr(st.n_pages), _cabi.ptr(st.n_sel_hi),
+               _cabi.ptr(st.b_fix), _cabi.stream())
+
+
+def _select(st, n_req: int, combine: int, use_hmax: bool) -> None:
+    _cabi.call("locks_topb_select", int(combine), _cabi.ptr(st.score_h),
+               _cabi.ptr(st.score),
+               _cabi.ptr(st.hmax if (use_hmax and st.hmax is not None) else None),
+               _cabi.ptr(st.n_pages), _cabi.ptr(st.n_sel_hi),
+               _cabi.ptr(st.b_fix), _cabi.ptr(st.page_table),
+               _cabi.ptr(st.page_cnt), int(n_req), int(st.n_kv), int(st.G),
+               int(st.max_pages), int(st.sink_pages), _cabi.stream())
+
+
+def topb_select(st, n_req: int) -> None:
+    """Top-b on an already combined ``st.score`` -> ``st.page_table`` /
+    ``st.page_cnt`` (static budget ``st.b_fix``)."""
+    _select(st, n_req, COMBINE_NONE, False)
+
+
+def nrmtopb_select(st, n_req: int, has_hmax: bool = False) -> None:
+    """Fused GQA combine + top-b from ``st.score_h`` using the state's combine
+    mode (reference ``selection/select_cuda.py:3614-3731``)."""
+    _select(st, n_req, COMBINE_NRM if st.combine == "nrm" else COMBINE_MAX,
+            has_hmax and st.combine == "nrm")
