@@ -64,19 +64,25 @@ def _finalized_blocks(cpu_case, page):
     return np.array(sorted(set(out)), dtype=np.int64)
 
 
+def _few(mask, frac):
+    """At most `frac` of the entries (but always allow 2: tiny samples)."""
+    return int(mask.sum()) <= max(2, int(np.ceil(frac * mask.size)))
+
+
 def _check_codes(ref, new, idx):
     """<= 0.1 % of codes differ, each by <= 1 LSB, after sign alignment."""
     Vr, Vn, Cr, Cn = orc.align_signs({k: v[idx] for k, v in ref.items()},
                                      {k: v[idx] for k, v in new.items()})
     dv, dc = np.abs(Vr - Vn), np.abs(Cr - Cn)
-    assert dv.max() <= 1 and (dv > 0).mean() <= 1e-3, ((dv > 0).mean(), dv.max())
-    assert dc.max() <= 1 and (dc > 0).mean() <= 1e-3, ((dc > 0).mean(), dc.max())
+    assert dv.max() <= 1 and _few(dv > 0, 1e-3), ((dv > 0).mean(), dv.max())
+    assert dc.max() <= 1 and _few(dc > 0, 1e-3), ((dc > 0).mean(), dc.max())
     dm = np.abs(ref["mu8"][idx].astype(np.int16) - new["mu8"][idx].astype(np.int16))
-    assert dm.max() <= 1 and (dm > 0).mean() <= 1e-3
+    assert dm.max() <= 1 and _few(dm > 0, 1e-3)
     for k in ("vs", "cs", "mus"):
         a, b = ref[k][idx], new[k][idx]
         rel = np.abs(a - b) / np.maximum(np.abs(a), 1e-12)
-        assert rel.max() <= 2 ** -7 and (rel > 0).mean() <= 5e-3, (k, rel.max())
+        # stored scales are bf16: at most one ulp apart, and rarely
+        assert rel.max() <= 2 ** -7 and _few(rel > 0, 5e-3), (k, rel.max())
 
 
 @pytest.mark.parametrize("name", list(GQA_CASES))
