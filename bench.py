@@ -243,7 +243,8 @@ def run_gpu(args, sh, seq_len):
     from locks.attention import DenseDecodeBuffers, dense_paged_decode
     from locks.hotpath import HotPath
     from locks.selection import rki4_score_only, rki4_select_only
-    from locks.attention import sparse_paged_decode_batched
+    from locks.attention import (sparse_paged_decode_batched,
+                                 sparse_paged_decode_fused)
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -262,7 +263,8 @@ def run_gpu(args, sh, seq_len):
     t_build = timed(lambda: hp.build_all(), 1)
     hp.derive()
     hp.q.copy_(q)
-    t_tail = timed(lambda: hp.build_tail(), 3)
+    hp.build_tail()                                # first call loads kernels
+    t_tail = timed(lambda: hp.build_tail(), 10)
     hp.capture()
     torch.cuda.synchronize()
     hp.st.check_status()
@@ -293,33 +295,46 @@ def run_gpu(args, sh, seq_len):
     ms_step = ms_total / args.steps
     hp.st.check_status()
 
-    # ---- per-stage kernel times (CUDA events, same stream, same inputs) -------
+    # ---- per-stage kernel times: one CUDA graph per stage over all layers, so
+    # that host launch overhead is not part of the number ------------------------
     st, R = hp.st, hp.n_req
     L = sh.n_layers
-    it = max(args.steps // 8, 4)
+    it = max(args.steps // 4, 8)
 
-    def all_layers(fn):
-        def run():
+    def stage_graph(fn):
+        for l in range(L):
+            fn(l)                                  # warm-up outside capture
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
             for l in range(L):
                 fn(l)
-        return run
+        return g
 
-    ms_score = timed(all_layers(lambda l: rki4_score_only(
-        st, l, hp.q[l, :R], bt, sl, R, hp.scale)), it) / L
-    ms_select = timed(all_layers(lambda l: rki4_select_only(st, R)), it) / L
-    ms_decode = timed(all_layers(lambda l: sparse_paged_decode_batched(
+    g_score = stage_graph(lambda l: rki4_score_only(
+        st, l, hp.q[l, :R], bt, sl, R, hp.scale))
+    g_select = stage_graph(lambda l: rki4_select_only(st, R, has_hmax=False))
+    g_decode = stage_graph(lambda l: sparse_paged_decode_fused(
         hp.q[l, :R], caches[l], bt, sl, st, hp.out[l], hp.vsources[l],
-        scale=hp.scale)), it) / L
-    # restore a consistent selection for whatever follows
-    hp.step()
+        scale=hp.scale))
+    g_split = stage_graph(lambda l: sparse_paged_decode_batched(
+        hp.q[l, :R], caches[l], bt, sl, st, hp.out[l], hp.vsources[l],
+        scale=hp.scale))
+    ms_score = timed(g_score.replay, it) / L
+    ms_select = timed(g_select.replay, it) / L
+    ms_decode = timed(g_decode.replay, it) / L
+    ms_split = timed(g_split.replay, it) / L
+    st.hmax.zero_() if st.hmax is not None else None
+    hp.step()                       # leave a consistent selection behind
 
     # ---- dense full-KV baseline on the same caches ----------------------------
     dsplit = max(1, min(512, (4 * 148) // (sh.n_kv * R)))
     dbuf = DenseDecodeBuffers(dev, R, sh.n_kv, sh.G, sh.d, dsplit)
     dout = torch.empty_like(hp.out[0])
-    ms_dense = timed(all_layers(lambda l: dense_paged_decode(
+    g_dense = stage_graph(lambda l: dense_paged_decode(
         hp.q[l, :R], caches[l], bt, sl, dbuf, dout, n_kv=sh.n_kv, G=sh.G,
-        scale=hp.scale, status=st.status)), max(it // 4, 2))
+        scale=hp.scale, status=st.status))
+    ms_dense = timed(g_dense.replay, max(it // 4, 3))
 
     # ---- end to end through the public API with HOST buffers -------------------
     q_host = q.cpu().pin_memory()
@@ -418,7 +433,8 @@ def run_gpu(args, sh, seq_len):
                           "frac_of_8tbs": step_bytes / (ms_step * 1e-3) / 8e12},
         "stages_us_per_layer": {"score": ms_score * 1e3,
                                 "select": ms_select * 1e3,
-                                "decode_split_merge": ms_decode * 1e3},
+                                "decode_fused": ms_decode * 1e3,
+                                "decode_split_plus_merge": ms_split * 1e3},
         "dense": {"ms_per_step": ms_dense, "bytes": b_dense,
                   "gbs": b_dense / (ms_dense * 1e-3) / 1e9,
                   "speedup_sparse_over_dense": ms_dense / ms_step},
@@ -440,8 +456,13 @@ def main():
     ap.add_argument("--workload", dest="workload_name", default="c1")
     ap.add_argument("--ctx", type=int, default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=None,
+                    help="override the layer count (quick experiments only)")
     args = ap.parse_args()
     sh, ctx = workload(args.workload_name, args.ctx)
+    if args.layers:
+        import dataclasses
+        sh = dataclasses.replace(sh, n_layers=args.layers)
     seq_len = ctx + 1
     rank = int(os.environ.get("RANK", "0"))
     if args.impl == "reference":

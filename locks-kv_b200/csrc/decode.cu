@@ -12,9 +12,16 @@
 // query heads of the GQA group:  S = Q K^T (bf16, 16 m16n8k16 steps), online
 // softmax in fp32, O += P V with P split into two bf16 terms (32 steps), i.e.
 // P keeps 16 mantissa bits.  The four warps' (m, l, O) are combined through
-// shared memory; the CTA then stores either one split partial or, in fused
-// mode, the normalised bf16 output row.
+// shared memory; the CTA then stores one split partial (split mode), or, in
+// fused mode, the CTAs of a thread-block cluster -- one cluster per (request,
+// kv-head), each CTA walking its share of the page list -- exchange their
+// (m, l, O) through distributed shared memory and write the normalised bf16
+// output row directly: no partial buffers in HBM and no merge launch.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace locks {
 namespace {
@@ -38,6 +45,8 @@ struct __align__(128) DecSmem {
     uint64_t full[DW][DSTAGES];
     float cm[DW][16];
     float cl[DW][16];
+    float cta_m[16];               // CTA-level (m, l) for the cluster exchange
+    float cta_l[16];
 };
 
 struct DecParams {
@@ -90,7 +99,7 @@ __device__ __forceinline__ void issue_page(DecSmem& sm, const DecParams& p,
     }
 }
 
-template <bool G_HI>
+template <bool G_HI, bool CLUSTER>
 __global__ void __launch_bounds__(DTHREADS)
 decode_kernel(const DecParams p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -106,8 +115,12 @@ decode_kernel(const DecParams p) {
     const int cnt = p.page_cnt ? p.page_cnt[row]
                                : (max(seq_len, 0) + PAGE_T - 1) / PAGE_T;
     int j0, j1;
-    if (p.fused) {
-        j0 = 0; j1 = cnt;
+    if (CLUSTER) {
+        // CTA `sp` of the cluster takes an even share of the list; an empty
+        // share still takes part in the cluster barriers below
+        const int per = (cnt + (int)gridDim.x - 1) / (int)gridDim.x;
+        j0 = min(sp * per, cnt);
+        j1 = min(j0 + per, cnt);
     } else {
         const int pps = max((cnt + p.split - 1) / p.split, p.pps_min);
         j0 = sp * pps;
@@ -281,6 +294,27 @@ decode_kernel(const DecParams p) {
     __syncthreads();
 
     const int d = tid;                            // 128 threads = 128 channels
+    if (!CLUSTER) {
+        for (int g = 0; g < G; ++g) {
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < DW; ++w) M = fmaxf(M, sm.cm[w][g]);
+            float Lsum = 0.f, o = 0.f;
+#pragma unroll
+            for (int w = 0; w < DW; ++w) {
+                const float lw = sm.cl[w][g];
+                const float wt = (lw > 0.f) ? __expf(sm.cm[w][g] - M) : 0.f;
+                Lsum += wt * lw;
+                o += wt * reinterpret_cast<const float*>(&sm.wb[w])[g * ACC_PITCH + d];
+            }
+            const int64_t base = (row * p.split + sp) * G + g;
+            p.acc_part[base * HD + d] = o;
+            if (d == 0) { p.m_part[base] = M; p.l_part[base] = Lsum; }
+        }
+        return;
+    }
+
+    // ---- cluster mode: CTA result into wb[0] (thread d owns column d) --------
     for (int g = 0; g < G; ++g) {
         float M = -INFINITY;
 #pragma unroll
@@ -293,16 +327,37 @@ decode_kernel(const DecParams p) {
             Lsum += wt * lw;
             o += wt * reinterpret_cast<const float*>(&sm.wb[w])[g * ACC_PITCH + d];
         }
-        if (p.fused) {
+        reinterpret_cast<float*>(&sm.wb[0])[g * ACC_PITCH + d] = o;
+        if (d == 0) { sm.cta_m[g] = M; sm.cta_l[g] = Lsum; }
+    }
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();                               // every CTA's result is visible
+    {
+        const int CL = (int)gridDim.x;
+        const int n_el = G * HD;
+        const int per_e = (n_el + CL - 1) / CL;   // output elements of this CTA
+        for (int e = sp * per_e + tid; e < min((sp + 1) * per_e, n_el);
+             e += DTHREADS) {
+            const int g = e / HD, dd = e % HD;
+            float M = -INFINITY;
+            for (int c = 0; c < CL; ++c)
+                M = fmaxf(M, *cluster.map_shared_rank(&sm.cta_m[g], c));
+            float Lsum = 0.f, o = 0.f;
+            for (int c = 0; c < CL; ++c) {
+                const float lw = *cluster.map_shared_rank(&sm.cta_l[g], c);
+                const float mw = *cluster.map_shared_rank(&sm.cta_m[g], c);
+                const float wt = (lw > 0.f) ? __expf(mw - M) : 0.f;
+                const float* racc = cluster.map_shared_rank(
+                    reinterpret_cast<const float*>(&sm.wb[0]), c);
+                Lsum += wt * lw;
+                o += wt * racc[g * ACC_PITCH + dd];
+            }
             const float val = (Lsum > 0.f) ? o / Lsum : 0.f;
-            p.out[(int64_t)r * p.out_stride_req + (int64_t)(kh * G + g) * HD + d] =
+            p.out[(int64_t)r * p.out_stride_req + (int64_t)(kh * G + g) * HD + dd] =
                 __float2bfloat16_rn(val);
-        } else {
-            const int64_t base = (row * p.split + sp) * G + g;
-            p.acc_part[base * HD + d] = o;
-            if (d == 0) { p.m_part[base] = M; p.l_part[base] = Lsum; }
         }
     }
+    cluster.sync();                  // keep shared memory alive for remote readers
 }
 
 struct MergeParams {
@@ -316,9 +371,14 @@ struct MergeParams {
     int n_kv, G, split, pps_min;
 };
 
-// grid (n_kv*G, n_req), 128 threads: thread d owns one output channel.
+// grid (n_kv*G, n_req), 128 threads.  Warp w merges splits w, w+4, ... online
+// (lane l owns channels 4l..4l+3, float4 loads); the 4 warps meet in shared
+// memory.  Only the ACTIVE splits are read.
 __global__ void __launch_bounds__(HD) merge_kernel(const MergeParams p) {
-    const int h = blockIdx.x, r = blockIdx.y, d = threadIdx.x;
+    __shared__ float sM[4], sL[4];
+    __shared__ __align__(16) float sO[4][HD];
+    const int h = blockIdx.x, r = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int kh = h / p.G, g = h % p.G;
     const int64_t row = (int64_t)r * p.n_kv + kh;
     const int cnt = p.page_cnt ? p.page_cnt[row]
@@ -326,18 +386,36 @@ __global__ void __launch_bounds__(HD) merge_kernel(const MergeParams p) {
     const int pps = max((cnt + p.split - 1) / p.split, p.pps_min);
     const int n_act = (cnt + pps - 1) / pps;
     const int64_t base = row * p.split * p.G + g;
-    float M = -INFINITY;
-    for (int s = 0; s < n_act; ++s) M = fmaxf(M, p.m_part[base + (int64_t)s * p.G]);
-    float Lsum = 0.f, o = 0.f;
-    for (int s = 0; s < n_act; ++s) {
+    float M = -INFINITY, Ls = 0.f;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int s = warp; s < n_act; s += 4) {
         const int64_t i = base + (int64_t)s * p.G;
-        const float l = p.l_part[i];
-        const float w = (l > 0.f) ? __expf(p.m_part[i] - M) : 0.f;
-        Lsum += w * l;
-        o += w * p.acc_part[i * HD + d];
+        const float m = p.m_part[i], l = p.l_part[i];
+        const float4 a =
+            *reinterpret_cast<const float4*>(&p.acc_part[i * HD + 4 * lane]);
+        if (l > 0.f) {
+            const float Mn = fmaxf(M, m);
+            const float ao = __expf(M - Mn), w = __expf(m - Mn);
+            Ls = Ls * ao + w * l;
+            o.x = o.x * ao + w * a.x; o.y = o.y * ao + w * a.y;
+            o.z = o.z * ao + w * a.z; o.w = o.w * ao + w * a.w;
+            M = Mn;
+        }
     }
-    const float val = (Lsum > 0.f) ? o / Lsum : 0.f;
-    p.out[(int64_t)r * p.out_stride_req + (int64_t)h * HD + d] =
+    if (lane == 0) { sM[warp] = M; sL[warp] = Ls; }
+    *reinterpret_cast<float4*>(&sO[warp][4 * lane]) = o;
+    __syncthreads();
+    float Mt = fmaxf(fmaxf(sM[0], sM[1]), fmaxf(sM[2], sM[3]));
+    float Lt = 0.f, ot = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        const float wt = (sL[w] > 0.f) ? __expf(sM[w] - Mt) : 0.f;
+        Lt += wt * sL[w];
+        ot += wt * sO[w][tid];
+    }
+    const float val = (Lt > 0.f) ? ot / Lt : 0.f;
+    p.out[(int64_t)r * p.out_stride_req + (int64_t)h * HD + tid] =
         __float2bfloat16_rn(val);
 }
 
@@ -350,6 +428,15 @@ int check_geometry(const char* who, int G, int head_dim, int page) {
     return LOCKS_OK;
 }
 
+// cluster size of the fused decode: enough CTAs to cover the SMs about twice,
+// a power of two, at most 8 (the portable cluster limit)
+int fused_cluster_size(int n_req, int n_kv) {
+    const int want = (2 * sm_count()) / max(1, n_req * n_kv);
+    int cl = 1;
+    while (cl * 2 <= want && cl < 8) cl *= 2;
+    return cl;
+}
+
 int launch_decode(const char* who, const DecParams& p, int n_req, int grid_x,
                   cudaStream_t s) {
     static bool attr_done[64] = {false};
@@ -357,17 +444,41 @@ int launch_decode(const char* who, const DecParams& p, int n_req, int grid_x,
     cudaGetDevice(&dev);
     const int smem = (int)sizeof(DecSmem);
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        cudaFuncSetAttribute(decode_kernel<false>,
+        cudaFuncSetAttribute(decode_kernel<false, false>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        cudaFuncSetAttribute(decode_kernel<true>,
+        cudaFuncSetAttribute(decode_kernel<true, false>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaFuncSetAttribute(decode_kernel<false, true>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaFuncSetAttribute(decode_kernel<true, true>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         attr_done[dev] = true;
     }
     dim3 grid(grid_x, p.n_kv, n_req);
-    if (p.G > 8)
-        decode_kernel<true><<<grid, DTHREADS, smem, s>>>(p);
-    else
-        decode_kernel<false><<<grid, DTHREADS, smem, s>>>(p);
+    if (!p.fused) {
+        if (p.G > 8)
+            decode_kernel<true, false><<<grid, DTHREADS, smem, s>>>(p);
+        else
+            decode_kernel<false, false><<<grid, DTHREADS, smem, s>>>(p);
+        return check_launch(who);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(DTHREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = grid_x;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = (p.G > 8)
+        ? cudaLaunchKernelEx(&cfg, decode_kernel<true, true>, p)
+        : cudaLaunchKernelEx(&cfg, decode_kernel<false, true>, p);
+    if (e != cudaSuccess)
+        return fail(LOCKS_ERR_LAUNCH, "%s: %s", who, cudaGetErrorString(e));
     return check_launch(who);
 }
 
@@ -478,7 +589,8 @@ extern "C" int locks_decode_fused(
     p.out = static_cast<__nv_bfloat16*>(out); p.out_stride_req = out_stride_req;
     p.n_kv = n_kv; p.G = G; p.max_pages = max_pages; p.split = 1;
     p.pps_min = 1; p.fused = 1; p.scale = scale; p.status = status;
-    return launch_decode("locks_decode_fused", p, n_req, 1,
+    return launch_decode("locks_decode_fused", p, n_req,
+                         fused_cluster_size(n_req, n_kv),
                          static_cast<cudaStream_t>(stream));
 }
 

@@ -1,39 +1,47 @@
 // Page scorer: per-head page log-sum-exp from the packed rki4 summary records.
 //
-// Grid (zsplit, n_kv, n_req), 128 threads.  A CTA owns one (request, kv-head)
-// and every zsplit-th tile of 32 consecutive logical pages.  For each tile one
-// warp turns the block table into 32 record addresses and issues 32 bulk async
-// copies of 832 B (the whole record is one contiguous burst) into a 3-stage
-// shared-memory ring, completion tracked by one mbarrier per stage.  Each of
-// the 4 warps then scores 8 pages of the tile with warp-level tensor-core
-// fragments whose 16 rows are the query heads of the GQA group:
+// Grid (zsplit, n_kv, n_req), 128 threads, 4 CTAs per SM.  A CTA owns one
+// (request, kv-head) and a contiguous, evenly sized range of logical pages; its
+// four warps split that range again and run INDEPENDENTLY: each warp walks its
+// pages in chunks of 8 through a private 2-stage shared-memory ring.  Eight
+// lanes turn block-table entries into record addresses and issue one 832-byte
+// bulk async copy each (a record is one contiguous burst); completion is
+// tracked by the warp's own mbarrier, so the main loop has no CTA-wide barrier.
 //
-//   mu.q     s8 x s8  m16n8k32, the 8 pages of the warp as the 8 columns
-//   V^T q    s8 x u8  m16n8k32, 4 k-steps; the int4 codes are used biased by
-//            +8 (one XOR per 8 nibbles) and 8*sum(q8) is subtracted afterwards
-//   C qt     bf16     m16n8k16 with qt split into three bf16 terms (hi, mid in
-//            one k=16 step, lo in a second), i.e. fp32-accurate products
-//   LSE      4 tokens per lane, two shuffle steps for max and for the sum
+// A chunk is scored with warp-level tensor-core fragments whose rows are the
+// query heads of the GQA group:
+//
+//   mu.q     s8 x s8  m16n8k32, the 8 pages of the chunk as the 8 columns
+//   V^T q    s8 x u8  m16n8k32, 4 k-steps per page; the int4 codes are used
+//            biased by +8 (one XOR per 8 nibbles), 8*sum(q8) is subtracted after
+//   C qt     f16      m16n8k16: qt = hi + lo in fp16 (22 significant bits);
+//            C (int8) is exact in fp16
+//   LSE      base-2, 4 tokens per lane, two shuffle steps for max and for sum
+//
+// With G <= 4 the 8 live fragment rows hold the group twice, and two pages are
+// scored per pass: the k dimension of the C product is split between the two
+// pages (block-diagonal A), so rows 0-3 come out as page A and rows 4-7 as page
+// B, and the conversion / LSE / store work is done once per PAIR of pages.
 //
 // The integer dot products are exact, so score_h differs from an fp32
-// evaluation only by summation order and the fast exp/log intrinsics.
+// evaluation only by summation order and the ex2/lg2 approximations.
 #include "common.cuh"
 
 namespace locks {
 namespace {
 
-constexpr int TILE = 32;
-constexpr int STAGES = 3;
+constexpr int CHUNK = 8;                       // pages per ring stage (= mma n)
+constexpr int STAGES = 2;
 constexpr int NWARP = 4;
 constexpr int NTHREADS = NWARP * 32;
-constexpr int PAGES_PER_WARP = TILE / NWARP;   // 8 = n of the mu mma
+constexpr int CTAS_PER_SM = 4;
 
 struct __align__(128) ScoreSmem {
-    uint8_t rec[STAGES][TILE][REC_BYTES];
+    uint8_t rec[NWARP][STAGES][CHUNK][REC_BYTES];
     int8_t q8[16][128];
     float qs[16];
     int qsum[16];
-    uint64_t full[STAGES];
+    uint64_t full[NWARP][STAGES];
 };
 
 struct ScoreParams {
@@ -50,25 +58,80 @@ struct ScoreParams {
     int* status;
 };
 
-__device__ __forceinline__ void issue_tile(ScoreSmem& sm, const ScoreParams& p,
-                                           int r, int kh, int tile, int stage,
-                                           int n_hi, int lane) {
-    const int p0 = tile * TILE;
-    const int n = min(TILE, n_hi - p0);
-    fence_proxy_async();
-    if (lane == 0) mbar_expect_tx(&sm.full[stage], (uint32_t)n * REC_BYTES);
-    __syncwarp();
-    if (lane < n) {
-        int blk = p.block_table[(int64_t)r * p.bt_stride + p0 + lane];
-        blk = min(max(blk, 0), p.num_blocks - 1);
-        const uint8_t* src =
-            p.records + ((int64_t)blk * p.n_kv + kh) * REC_BYTES;
-        bulk_g2s(&sm.rec[stage][lane][0], src, REC_BYTES, &sm.full[stage]);
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float lg2_approx(float x) {
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// D(16x8,f32) = A(16x16,f16,row) * B(16x8,f16,col) + C
+__device__ __forceinline__ void mma_f16_k16(float (&d)[4], uint32_t a0,
+                                            uint32_t a1, uint32_t a2,
+                                            uint32_t a3, uint32_t b0,
+                                            uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// f0, f1 -> packed fp16 (hi parts) and packed fp16 (residuals)
+__device__ __forceinline__ void split_f16x2(float f0, float f1, uint32_t& hi,
+                                            uint32_t& lo) {
+    const __half2 h = __floats2half2_rn(f0, f1);
+    const float2 hf = __half22float2(h);
+    const __half2 l = __floats2half2_rn(f0 - hf.x, f1 - hf.y);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+// two int8 (low 16 bits of cc) -> packed fp16, exactly
+__device__ __forceinline__ uint32_t s8x2_to_f16x2(uint32_t cc) {
+    const uint32_t biased = __byte_perm(cc ^ 0x8080u, 0x64646464u, 0x4140);
+    const __half2 h = __hsub2(*reinterpret_cast<const __half2*>(&biased),
+                              __floats2half2_rn(1152.f, 1152.f));
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// c[row][r] = sum_d q8[row][d] * (code[d][r] + 8) for one page
+template <bool HI>
+__device__ __forceinline__ void project_page(int (&c)[4], const uint8_t* rec,
+                                             int gid, int tig,
+                                             const uint32_t (&qe)[4],
+                                             const uint32_t (&qo)[4],
+                                             const uint32_t (&qe_hi)[4],
+                                             const uint32_t (&qo_hi)[4]) {
+    const uint4 vw =
+        *reinterpret_cast<const uint4*>(rec + RO_V4 + gid * 64 + tig * 16);
+    const uint32_t vword[4] = {vw.x, vw.y, vw.z, vw.w};
+    c[0] = c[1] = c[2] = c[3] = 0;
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+        const uint32_t u = vword[s] ^ 0x88888888u;
+        mma_s8u8_k32(c, qe[s], HI ? qe_hi[s] : 0u, qo[s], HI ? qo_hi[s] : 0u,
+                     u & 0x0F0F0F0Fu, (u >> 4) & 0x0F0F0F0Fu);
     }
 }
 
-template <bool G_HI>
-__global__ void __launch_bounds__(NTHREADS)
+// base-2 log-sum-exp of 4 values per lane over the 4 lanes of a quad
+__device__ __forceinline__ float quad_lse2(float t0, float t1, float t2,
+                                           float t3) {
+    float mx = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    float sum = ex2_approx(t0 - mx) + ex2_approx(t1 - mx) +
+                ex2_approx(t2 - mx) + ex2_approx(t3 - mx);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    return mx + lg2_approx(sum);
+}
+
+// GP = 4 : G <= 4, two pages per pass;  GP = 8 : G <= 8;  GP = 16 : G <= 16
+template <int GP>
+__global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM)
 rki4_score_kernel(const ScoreParams p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     ScoreSmem& sm = *reinterpret_cast<ScoreSmem*>(smem_raw);
@@ -82,19 +145,42 @@ rki4_score_kernel(const ScoreParams p) {
     int n_hi = p.n_sel_hi[r];
     n_hi = min(n_hi, min(p.max_pages, p.bt_width));
     if (n_hi <= 0) return;
-    const int ntiles = (n_hi + TILE - 1) / TILE;
-    if (z >= ntiles) return;
-    const int nt = (ntiles - z + Z - 1) / Z;       // tiles of this CTA
+    // contiguous page range of this CTA, then of this warp
+    const int cg0 = (int)(((int64_t)n_hi * z) / Z);
+    const int cg1 = (int)(((int64_t)n_hi * (z + 1)) / Z);
+    if (cg1 <= cg0) return;
+    const int pg0 = cg0 + (int)(((int64_t)(cg1 - cg0) * warp) / NWARP);
+    const int pg1 = cg0 + (int)(((int64_t)(cg1 - cg0) * (warp + 1)) / NWARP);
+    const int nc = (pg1 - pg0 + CHUNK - 1) / CHUNK;        // chunks of this warp
 
     if (tid == 0) {
-        for (int s = 0; s < STAGES; ++s) mbar_init(&sm.full[s], 1);
+        for (int w = 0; w < NWARP; ++w)
+            for (int s = 0; s < STAGES; ++s) mbar_init(&sm.full[w][s], 1);
         mbar_fence_init();
     }
     __syncthreads();
-    if (warp == 0) {
-        for (int k = 0; k < STAGES && k < nt; ++k)
-            issue_tile(sm, p, r, kh, z + k * Z, k, n_hi, lane);
-    }
+
+    const int32_t* bt = p.block_table + (int64_t)r * p.bt_stride;
+    const uint8_t* recs = p.records + (int64_t)kh * REC_BYTES;
+    const int64_t blk_stride = (int64_t)p.n_kv * REC_BYTES;
+    auto issue = [&](int chunk, int blk) {
+        const int stage = chunk % STAGES;
+        const int n = min(CHUNK, pg1 - pg0 - chunk * CHUNK);
+        fence_proxy_async();
+        if (lane == 0)
+            mbar_expect_tx(&sm.full[warp][stage], (uint32_t)n * REC_BYTES);
+        __syncwarp();
+        if (lane < n) {
+            blk = min(max(blk, 0), p.num_blocks - 1);
+            bulk_g2s(&sm.rec[warp][stage][lane][0], recs + blk * blk_stride,
+                     REC_BYTES, &sm.full[warp][stage]);
+        }
+    };
+    auto bt_of = [&](int chunk) -> int {
+        const int pg = pg0 + chunk * CHUNK + lane;
+        return (lane < CHUNK && pg < pg1) ? bt[pg] : 0;
+    };
+    for (int k = 0; k < STAGES && k < nc; ++k) issue(k, bt_of(k));
 
     // ---- per-head int8 round trip of q (overlaps the first copies) ----------
     for (int g = warp; g < G; g += NWARP) {
@@ -127,14 +213,17 @@ rki4_score_kernel(const ScoreParams p) {
     }
     __syncthreads();
 
-    // ---- A fragments of q: rows gid (and gid+8 when G > 8) ------------------
-    constexpr int NR = G_HI ? 2 : 1;
+    // ---- A fragments of q.  Row gid holds head gid % GP (the group is repeated
+    // when it is shorter than 8 rows); rows 8..15 are used only for GP = 16. ----
+    constexpr int NR = (GP == 16) ? 2 : 1;
+    constexpr bool HI = (GP == 16);
+    constexpr int GROW = (GP < 8) ? GP : 8;
     uint32_t qn[NR][8], qe[NR][4], qo[NR][4];
     float qsc[NR];
     int qsm8[NR];
 #pragma unroll
     for (int h = 0; h < NR; ++h) {
-        const int g = gid + 8 * h;
+        const int g = (gid % GROW) + 8 * h;
         const bool live = g < G;
         const uint32_t* row =
             reinterpret_cast<const uint32_t*>(&sm.q8[live ? g : 0][0]);
@@ -155,146 +244,169 @@ rki4_score_kernel(const ScoreParams p) {
     float run_max[NR];
 #pragma unroll
     for (int h = 0; h < NR; ++h) run_max[h] = -INFINITY;
-    const float scale = p.scale;
+    const float scale2 = p.scale * 1.4426950408889634f;     // base-2 logits
+    constexpr float LN2 = 0.6931471805599453f;
     float* out_base =
         p.score_h + ((int64_t)r * p.n_kv + kh) * (int64_t)G * p.max_pages;
 
-    for (int k = 0; k < nt; ++k) {
+    for (int k = 0; k < nc; ++k) {
         const int stage = k % STAGES;
-        const int tile = z + k * Z;
-        const int p0 = tile * TILE;
-        const int n = min(TILE, n_hi - p0);
-        mbar_wait(&sm.full[stage], (uint32_t)((k / STAGES) & 1), p.status);
+        const int p0 = pg0 + k * CHUNK;
+        const int n = min(CHUNK, pg1 - p0);
+        // block-table entries of the chunk that will reuse this stage
+        const int next_blk = (k + STAGES < nc) ? bt_of(k + STAGES) : 0;
+        mbar_wait(&sm.full[warp][stage], (uint32_t)((k / STAGES) & 1), p.status);
+        const uint8_t* crec = &sm.rec[warp][stage][0][0];
 
-        const uint8_t* wrec = &sm.rec[stage][warp * PAGES_PER_WARP][0];
-
-        // mu . q for the warp's 8 pages: column (n) = page gid of the warp
+        // mu . q for the chunk's 8 pages: column (n) = page slot gid
         int muc[4] = {0, 0, 0, 0};
         {
-            const uint8_t* mrec = wrec + gid * REC_BYTES + RO_MU8 + 32 * tig;
+            const uint8_t* mrec = crec + gid * REC_BYTES + RO_MU8 + 32 * tig;
             const uint4 m0 = *reinterpret_cast<const uint4*>(mrec);
             const uint4 m1 = *reinterpret_cast<const uint4*>(mrec + 16);
             const uint32_t mw[8] = {m0.x, m0.y, m0.z, m0.w,
                                     m1.x, m1.y, m1.z, m1.w};
 #pragma unroll
             for (int s = 0; s < 4; ++s)
-                mma_s8s8_k32(muc, qn[0][2 * s], G_HI ? qn[NR - 1][2 * s] : 0u,
-                             qn[0][2 * s + 1],
-                             G_HI ? qn[NR - 1][2 * s + 1] : 0u, mw[2 * s],
-                             mw[2 * s + 1]);
+                mma_s8s8_k32(muc, qn[0][2 * s], HI ? qn[NR - 1][2 * s] : 0u,
+                             qn[0][2 * s + 1], HI ? qn[NR - 1][2 * s + 1] : 0u,
+                             mw[2 * s], mw[2 * s + 1]);
         }
 
+        if constexpr (GP == 4) {
+            // ---- two pages per pass: rows 0-3 -> slot 2j, rows 4-7 -> 2j+1 ----
+            const int sel = gid >> 2;
 #pragma unroll 2
-        for (int i = 0; i < PAGES_PER_WARP; ++i) {
-            const int li = warp * PAGES_PER_WARP + i;
-            const uint8_t* rec = wrec + i * REC_BYTES;
-
-            // ---- qt_int[g][r] = sum_d q8[g][d] * (code[d][r] + 8) -----------
-            int c1[4] = {0, 0, 0, 0};
-            const uint4 vw =
-                *reinterpret_cast<const uint4*>(rec + RO_V4 + gid * 64 + tig * 16);
-            const uint32_t vword[4] = {vw.x, vw.y, vw.z, vw.w};
+            for (int j = 0; j < CHUNK / 2; ++j) {
+                if (2 * j >= n) break;
+                const uint8_t* recA = crec + (2 * j) * REC_BYTES;
+                const uint8_t* recB = recA + REC_BYTES;
+                const uint8_t* own = sel ? recB : recA;
+                int cA[4], cB[4];
+                project_page<false>(cA, recA, gid, tig, qe[0], qo[0], qe[0], qo[0]);
+                project_page<false>(cB, recB, gid, tig, qe[0], qo[0], qe[0], qo[0]);
+                const int c0 = sel ? cB[0] : cA[0];
+                const int c1 = sel ? cB[1] : cA[1];
+                const uint32_t vs2 =
+                    *reinterpret_cast<const uint32_t*>(own + RO_VS + 4 * tig);
+                const float mus = bf16_bits_to_f32(
+                    *reinterpret_cast<const uint16_t*>(own + RO_MUS));
+                // mu.q of slot 2j+sel: lane (gid, j), register sel
+                const int mq = __shfl_sync(0xffffffffu, sel ? muc[1] : muc[0],
+                                           (lane & ~3) | j);
+                uint32_t a_hi, a_lo;
+                split_f16x2(
+                    (float)(c0 - qsm8[0]) *
+                        (qsc[0] * bf16_bits_to_f32(vs2 & 0xFFFFu)),
+                    (float)(c1 - qsm8[0]) * (qsc[0] * bf16_bits_to_f32(vs2 >> 16)),
+                    a_hi, a_lo);
+                const float mud = (float)mq * (qsc[0] * mus * scale2);
+                // block-diagonal A: k 0-7 multiply page A's C, k 8-15 page B's
+                const uint32_t a0h = sel ? 0u : a_hi, a2h = sel ? a_hi : 0u;
+                const uint32_t a0l = sel ? 0u : a_lo, a2l = sel ? a_lo : 0u;
+                float x[2][4];
 #pragma unroll
-            for (int s = 0; s < 4; ++s) {
-                const uint32_t u = vword[s] ^ 0x88888888u;
-                const uint32_t b0 = u & 0x0F0F0F0Fu;
-                const uint32_t b1 = (u >> 4) & 0x0F0F0F0Fu;
-                mma_s8u8_k32(c1, qe[0][s], G_HI ? qe[NR - 1][s] : 0u, qo[0][s],
-                             G_HI ? qo[NR - 1][s] : 0u, b0, b1);
+                for (int th = 0; th < 2; ++th) {
+                    const int off = RO_C8 + (8 * th + gid) * 8 + 2 * tig;
+                    const uint32_t bA = s8x2_to_f16x2(
+                        *reinterpret_cast<const uint16_t*>(recA + off));
+                    const uint32_t bB = s8x2_to_f16x2(
+                        *reinterpret_cast<const uint16_t*>(recB + off));
+                    x[th][0] = x[th][1] = x[th][2] = x[th][3] = 0.f;
+                    mma_f16_k16(x[th], a0h, 0u, a2h, 0u, bA, bB);
+                    mma_f16_k16(x[th], a0l, 0u, a2l, 0u, bA, bB);
+                }
+                const uint32_t csa =
+                    *reinterpret_cast<const uint32_t*>(own + RO_CS + 4 * tig);
+                const uint32_t csb =
+                    *reinterpret_cast<const uint32_t*>(own + RO_CS + 16 + 4 * tig);
+                const float S = LN2 * quad_lse2(
+                    fmaf(bf16_bits_to_f32(csa & 0xFFFFu) * scale2, x[0][0], mud),
+                    fmaf(bf16_bits_to_f32(csa >> 16) * scale2, x[0][1], mud),
+                    fmaf(bf16_bits_to_f32(csb & 0xFFFFu) * scale2, x[1][0], mud),
+                    fmaf(bf16_bits_to_f32(csb >> 16) * scale2, x[1][1], mud));
+                const int slot = 2 * j + sel;
+                const int g = gid & 3;
+                if (slot < n && g < G) {
+                    if (tig == 0)
+                        out_base[(int64_t)g * p.max_pages + p0 + slot] = S;
+                    run_max[0] = fmaxf(run_max[0], S);
+                }
             }
-            const uint32_t vs2 =
-                *reinterpret_cast<const uint32_t*>(rec + RO_VS + 4 * tig);
-            const float vs0 = bf16_bits_to_f32(vs2 & 0xFFFFu);
-            const float vs1 = bf16_bits_to_f32(vs2 >> 16);
-            const float mus = bf16_bits_to_f32(
-                *reinterpret_cast<const uint16_t*>(rec + RO_MUS));
-
-            // mu.q of page i sits in lane (gid, i/2), register i%2 (+2 for hi)
-            const int src_lane = (lane & ~3) | (i >> 1);
-            const int mlo = __shfl_sync(0xffffffffu, (i & 1) ? muc[1] : muc[0],
-                                        src_lane);
-            int mhi = 0;
-            if (G_HI)
-                mhi = __shfl_sync(0xffffffffu, (i & 1) ? muc[3] : muc[2],
-                                  src_lane);
-
-            // ---- A operand of the C product: qt as hi/mid/lo bf16 -----------
-            uint32_t a_hi[NR], a_mid[NR], a_lo[NR];
-            float mud[NR];
+        } else {
+            // ---- one page per pass, rows = heads (8, or 16 with the hi rows) --
+#pragma unroll 2
+            for (int i = 0; i < CHUNK; ++i) {
+                if (i >= n) break;
+                const uint8_t* rec = crec + i * REC_BYTES;
+                int c1[4];
+                project_page<HI>(c1, rec, gid, tig, qe[0], qo[0], qe[NR - 1],
+                                 qo[NR - 1]);
+                const uint32_t vs2 =
+                    *reinterpret_cast<const uint32_t*>(rec + RO_VS + 4 * tig);
+                const float vs0 = bf16_bits_to_f32(vs2 & 0xFFFFu);
+                const float vs1 = bf16_bits_to_f32(vs2 >> 16);
+                const float mus = bf16_bits_to_f32(
+                    *reinterpret_cast<const uint16_t*>(rec + RO_MUS));
+                const int src_lane = (lane & ~3) | (i >> 1);
+                const int mlo = __shfl_sync(
+                    0xffffffffu, (i & 1) ? muc[1] : muc[0], src_lane);
+                int mhi = 0;
+                if (HI)
+                    mhi = __shfl_sync(0xffffffffu, (i & 1) ? muc[3] : muc[2],
+                                      src_lane);
+                uint32_t a_hi[NR], a_lo[NR];
+                float mud[NR];
 #pragma unroll
-            for (int h = 0; h < NR; ++h) {
-                const float f0 =
-                    (float)(c1[2 * h] - qsm8[h]) * (qsc[h] * vs0);
-                const float f1 =
-                    (float)(c1[2 * h + 1] - qsm8[h]) * (qsc[h] * vs1);
-                const float h0 = __bfloat162float(__float2bfloat16_rn(f0));
-                const float h1 = __bfloat162float(__float2bfloat16_rn(f1));
-                const float r0 = f0 - h0, r1 = f1 - h1;
-                const float m0 = __bfloat162float(__float2bfloat16_rn(r0));
-                const float m1 = __bfloat162float(__float2bfloat16_rn(r1));
-                a_hi[h] = pack_bf16x2(h0, h1);
-                a_mid[h] = pack_bf16x2(m0, m1);
-                a_lo[h] = pack_bf16x2(r0 - m0, r1 - m1);
-                mud[h] = (float)(h == 0 ? mlo : mhi) * (qsc[h] * mus);
-            }
-
-            // ---- X[g][t] = sum_r C8[t][r] * qt[g][r], two halves of 8 tokens
-            float x[2][4];
+                for (int h = 0; h < NR; ++h) {
+                    split_f16x2((float)(c1[2 * h] - qsm8[h]) * (qsc[h] * vs0),
+                                (float)(c1[2 * h + 1] - qsm8[h]) * (qsc[h] * vs1),
+                                a_hi[h], a_lo[h]);
+                    mud[h] = (float)(h == 0 ? mlo : mhi) * (qsc[h] * mus * scale2);
+                }
+                float x[2][4];
 #pragma unroll
-            for (int th = 0; th < 2; ++th) {
-                const uint16_t cc = *reinterpret_cast<const uint16_t*>(
-                    rec + RO_C8 + (8 * th + gid) * 8 + 2 * tig);
-                const uint32_t bC = pack_bf16x2(
-                    (float)(int8_t)(cc & 0xFF), (float)(int8_t)(cc >> 8));
-                x[th][0] = x[th][1] = x[th][2] = x[th][3] = 0.f;
-                mma_bf16_k16(x[th], a_hi[0], G_HI ? a_hi[NR - 1] : 0u, a_mid[0],
-                             G_HI ? a_mid[NR - 1] : 0u, bC, bC);
-                mma_bf16_k16(x[th], a_lo[0], G_HI ? a_lo[NR - 1] : 0u, 0u, 0u,
-                             bC, 0u);
-            }
-
-            // ---- tok = scale * (cs[t] * X + mu.q); LSE over the 16 tokens ---
-            const uint32_t csa =
-                *reinterpret_cast<const uint32_t*>(rec + RO_CS + 4 * tig);
-            const uint32_t csb =
-                *reinterpret_cast<const uint32_t*>(rec + RO_CS + 16 + 4 * tig);
-            const float cs[4] = {bf16_bits_to_f32(csa & 0xFFFFu),
-                                 bf16_bits_to_f32(csa >> 16),
-                                 bf16_bits_to_f32(csb & 0xFFFFu),
-                                 bf16_bits_to_f32(csb >> 16)};
+                for (int th = 0; th < 2; ++th) {
+                    const uint32_t bC =
+                        s8x2_to_f16x2(*reinterpret_cast<const uint16_t*>(
+                            rec + RO_C8 + (8 * th + gid) * 8 + 2 * tig));
+                    x[th][0] = x[th][1] = x[th][2] = x[th][3] = 0.f;
+                    mma_f16_k16(x[th], a_hi[0], HI ? a_hi[NR - 1] : 0u, a_lo[0],
+                                HI ? a_lo[NR - 1] : 0u, bC, bC);
+                }
+                const uint32_t csa =
+                    *reinterpret_cast<const uint32_t*>(rec + RO_CS + 4 * tig);
+                const uint32_t csb =
+                    *reinterpret_cast<const uint32_t*>(rec + RO_CS + 16 + 4 * tig);
+                const float cs0 = bf16_bits_to_f32(csa & 0xFFFFu) * scale2;
+                const float cs1 = bf16_bits_to_f32(csa >> 16) * scale2;
+                const float cs2 = bf16_bits_to_f32(csb & 0xFFFFu) * scale2;
+                const float cs3 = bf16_bits_to_f32(csb >> 16) * scale2;
 #pragma unroll
-            for (int h = 0; h < NR; ++h) {
-                float t[4];
-                t[0] = scale * fmaf(cs[0], x[0][2 * h], mud[h]);
-                t[1] = scale * fmaf(cs[1], x[0][2 * h + 1], mud[h]);
-                t[2] = scale * fmaf(cs[2], x[1][2 * h], mud[h]);
-                t[3] = scale * fmaf(cs[3], x[1][2 * h + 1], mud[h]);
-                float mx = fmaxf(fmaxf(t[0], t[1]), fmaxf(t[2], t[3]));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-                float sum = __expf(t[0] - mx) + __expf(t[1] - mx) +
-                            __expf(t[2] - mx) + __expf(t[3] - mx);
-                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                const float S = mx + __logf(sum);
-                const int g = gid + 8 * h;
-                if (li < n && g < G) {
-                    if (tig == (i & 3))
-                        out_base[(int64_t)g * p.max_pages + p0 + li] = S;
-                    run_max[h] = fmaxf(run_max[h], S);
+                for (int h = 0; h < NR; ++h) {
+                    const float S = LN2 * quad_lse2(
+                        fmaf(cs0, x[0][2 * h], mud[h]),
+                        fmaf(cs1, x[0][2 * h + 1], mud[h]),
+                        fmaf(cs2, x[1][2 * h], mud[h]),
+                        fmaf(cs3, x[1][2 * h + 1], mud[h]));
+                    const int g = gid + 8 * h;
+                    if (g < G) {
+                        if (tig == (i & 3))
+                            out_base[(int64_t)g * p.max_pages + p0 + i] = S;
+                        run_max[h] = fmaxf(run_max[h], S);
+                    }
                 }
             }
         }
 
-        __syncthreads();                      // every warp is done with `stage`
-        if (warp == 0 && k + STAGES < nt)
-            issue_tile(sm, p, r, kh, z + (k + STAGES) * Z, stage, n_hi, lane);
+        __syncwarp();                         // the warp is done with `stage`
+        if (k + STAGES < nc) issue(k + STAGES, next_blk);
     }
 
     if (p.hmax != nullptr && tig == 0) {
 #pragma unroll
         for (int h = 0; h < NR; ++h) {
-            const int g = gid + 8 * h;
+            const int g = (GP == 4 ? (gid & 3) : gid) + 8 * h;
             if (g < G && run_max[h] > -INFINITY)
                 atomicMax(&p.hmax[((int64_t)r * p.n_kv + kh) * G + g],
                           f2key(run_max[h]));
@@ -334,20 +446,23 @@ extern "C" int locks_rki4_score_bt(
     cudaGetDevice(&dev);
     const int smem = (int)sizeof(ScoreSmem);
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        cudaFuncSetAttribute(rki4_score_kernel<false>,
+        cudaFuncSetAttribute(rki4_score_kernel<4>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        cudaFuncSetAttribute(rki4_score_kernel<true>,
+        cudaFuncSetAttribute(rki4_score_kernel<8>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaFuncSetAttribute(rki4_score_kernel<16>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         attr_done[dev] = true;
     }
-    const int max_tiles = (max_pages + TILE - 1) / TILE;
+    // a CTA should own at least one chunk per warp
+    const int max_z = (max_pages + NWARP * CHUNK - 1) / (NWARP * CHUNK);
     int Z = zsplit;
     if (Z <= 0) {
-        // two resident CTAs per SM, spread over the (request, kv-head) grid
+        // fill every resident CTA slot, spread over the (request, kv-head) grid
         const int base = n_req * n_kv;
-        Z = (2 * sm_count() + base - 1) / base;
+        Z = (CTAS_PER_SM * sm_count() + base - 1) / base;
     }
-    Z = max(1, min(Z, min(max_tiles, 65535)));
+    Z = max(1, min(Z, min(max_z, 65535)));
 
     ScoreParams p;
     p.q = static_cast<const __nv_bfloat16*>(q);
@@ -362,9 +477,11 @@ extern "C" int locks_rki4_score_bt(
     p.num_blocks = num_blocks; p.scale = scale; p.status = status;
     dim3 grid(Z, n_kv, n_req);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (G > 8)
-        rki4_score_kernel<true><<<grid, NTHREADS, smem, s>>>(p);
+    if (G <= 4)
+        rki4_score_kernel<4><<<grid, NTHREADS, smem, s>>>(p);
+    else if (G <= 8)
+        rki4_score_kernel<8><<<grid, NTHREADS, smem, s>>>(p);
     else
-        rki4_score_kernel<false><<<grid, NTHREADS, smem, s>>>(p);
+        rki4_score_kernel<16><<<grid, NTHREADS, smem, s>>>(p);
     return check_launch("locks_rki4_score_bt");
 }

@@ -9,6 +9,7 @@ reference are outside this build.
 """
 from __future__ import annotations
 
+import sys
 from typing import Optional
 
 from ..config import LocksConfig
@@ -16,8 +17,9 @@ from ..config import LocksConfig
 _CONFIG: Optional[LocksConfig] = None
 _ANNOUNCED = False
 
-# decode launcher choice: one fused launch at large batch, split + merge below
-FUSED_MIN_REQS = 8
+# decode launcher choice: the one-launch cluster decode from this many requests up
+# (1 = always; the split + merge pair stays available below it)
+FUSED_MIN_REQS = 1
 
 
 def set_config(cfg: Optional[LocksConfig]) -> None:
@@ -52,7 +54,7 @@ def _rki4_select_adapter(q, kv_cache, block_table, seq_lens, st, n_req, scale,
         _ANNOUNCED = True
         print(f"[locks] selection kernels: sm_100a rki4 score (zsplit="
               f"{st.zsplit or 'auto'}, combine={st.combine}) + radix top-b",
-              flush=True)
+              file=sys.stderr, flush=True)
     lidx = _layer_index(st, kv_cache)
     rki4_score_state(st, lidx, q, block_table, seq_lens, n_req, scale)
 
