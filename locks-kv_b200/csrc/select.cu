@@ -1,18 +1,23 @@
 // Per-step page parameters, GQA score combine and exact top-b page selection.
 //
-// topb kernel: one thread-block CLUSTER (1..8 CTAs of 1024 threads) per
-// (request, kv-head); CTA c owns a contiguous slice of the pages.
+// topb kernel: one thread-block CLUSTER (1, 2, 4 or 8 CTAs of 1024 threads) per
+// (request, kv-head); CTA c owns a contiguous slice of the pages and keeps the
+// slice's 32-bit order-preserving score keys in shared memory, so every pass
+// after the first runs out of shared memory.  A single CTA is used whenever the
+// keys of one (request, kv-head) fit (<= 16384 pages); longer contexts spread
+// over a cluster and meet through distributed shared memory.
 //   1. combine the per-head scores of the slice into one score per page (nrm
 //      or max); the per-head maxima come from the scorer's published keys or
-//      from a cluster-wide sweep,
-//   2. find the b-th largest score of the selectable range with a 3-pass MSD
-//      radix select (11/11/10 bits) on order-preserving 32-bit keys: every CTA
-//      histograms its slice in shared memory, the cluster meets at a hardware
-//      barrier, every CTA adds up all slices' histograms through distributed
-//      shared memory and picks the digit with a block-wide suffix scan,
-//   3. keep flags with the exact-b tie rule; tie ranks and output slots come
-//      from block scans plus a cluster exchange of per-CTA totals; ascending
-//      compaction, -1 padding.
+//      from a (cluster-wide) sweep,
+//   2. b-th largest score of the selectable range by a 3-pass MSD radix select
+//      (11/11/10 bits): shared-memory histogram per CTA; in a cluster, CTA c
+//      sums bin slice c of all CTAs (reduce-scatter through DSMEM), the slice
+//      totals locate the slice that holds the digit and that slice alone is
+//      read back,
+//   3. keep flags with the exact-b tie rule; each warp owns consecutive groups
+//      of 32 pages, so ballots give the in-group ranks, and warp / CTA totals
+//      give the tie ranks and the output slots; ascending compaction, -1
+//      padding.
 // No global scratch and a single launch for any page count.
 #include <cooperative_groups.h>
 
@@ -63,53 +68,166 @@ struct SelParams {
     int n_kv, G, max_pages, sink;
 };
 
+#ifdef LOCKS_SEL_TIMING
+__device__ long long g_sel_ts[32];
+#define SEL_TS(i)                                                          \
+    do {                                                                   \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 &&       \
+            threadIdx.x == 0)                                              \
+            g_sel_ts[i] = clock64();                                       \
+    } while (0)
+#else
+#define SEL_TS(i)
+#endif
+
 constexpr int RBITS0 = 11, RBITS1 = 11, RBITS2 = 10;
 constexpr int NBINS = 1 << RBITS0;                // 2048 (largest digit)
 constexpr int MAX_CL = 8;
+constexpr int KEYS_PER_CTA = 16384;               // shared-memory key capacity
 
 struct SelSmem {
-    int hist[2][NBINS];
-    int warp_tot[32];
+    int hist[NBINS];               // this CTA's histogram of the current digit
+    int tot[NBINS];                // cluster: summed bin slice; CL=1: unused
+    int wtot[SEL_WARPS];           // per-warp totals (scans)
+    int wtot2[SEL_WARPS];
     float wmax[SEL_WARPS][MAX_G];
     float xmax[MAX_G];             // this CTA's per-head maxima (cluster sweep)
     float hm_sh[MAX_G];
+    int x_slice_tot;               // cluster exchange: total of my bin slice
+    int x_eq;                      // ... ties in my page slice
+    int x_kept;                    // ... kept pages in my page slice
     uint32_t sh_prefix;
     int sh_k;
-    int x_eq;                      // this CTA's tie count / kept count
-    int x_kept;
+    int sh_i0, sh_i1;
 };
 
-// exclusive prefix sum of one int per thread over the whole CTA;
-// `total` receives the CTA-wide sum.  `warp_tot` is 32 ints of scratch.
-__device__ __forceinline__ int block_exclusive_scan(int v, int* warp_tot,
-                                                    int& total) {
+// inclusive scan of 32 per-warp totals by warp 0 (in place); returns nothing,
+// callers read exclusive bases as (w ? a[w-1] : 0) and the total as a[31]
+__device__ __forceinline__ void scan_warp_totals(int* a) {
+    if (threadIdx.x < 32) {
+        int v = a[threadIdx.x];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, v, o);
+            if ((int)threadIdx.x >= o) v += t;
+        }
+        a[threadIdx.x] = v;
+    }
+}
+
+// Among bins [0, nb) of `h` (nb a multiple of 64, <= 2048) find the largest
+// bin d with  count(bins > d) < k <= count(bins >= d);  `above0` pages already
+// lie above bin nb-1.  Warp w owns the 64 bins just below nb-64w.  On return
+// (after the trailing __syncthreads) sm.sh_i0 = d, sm.sh_i1 = k - count above d.
+__device__ __forceinline__ void find_digit(SelSmem& sm, const int* h, int nb,
+                                           int above0, int k) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    int inc = v;
+    const int hi_bin = nb - 1 - 64 * warp - 2 * lane;      // and hi_bin - 1
+    int ca = 0, cb = 0;
+    if (hi_bin >= 1) { ca = h[hi_bin]; cb = h[hi_bin - 1]; }
+    int inc = ca + cb;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
         const int t = __shfl_up_sync(0xffffffffu, inc, o);
         if (lane >= o) inc += t;
     }
-    __syncthreads();                       // protect warp_tot reuse
-    if (lane == 31) warp_tot[warp] = inc;
+    if (lane == 31) sm.wtot[warp] = inc;
     __syncthreads();
-    int wv = (lane < SEL_WARPS) ? warp_tot[lane] : 0;
-    int winc = wv;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int t = __shfl_up_sync(0xffffffffu, winc, o);
-        if (lane >= o) winc += t;
+    scan_warp_totals(sm.wtot);
+    __syncthreads();
+    const int base = above0 + (warp ? sm.wtot[warp - 1] : 0);
+    const int above = base + inc - (ca + cb);
+    if (above < k && k <= above + ca + cb) {
+        if (k <= above + ca) { sm.sh_i0 = hi_bin; sm.sh_i1 = k - above; }
+        else { sm.sh_i0 = hi_bin - 1; sm.sh_i1 = k - above - ca; }
     }
-    total = __shfl_sync(0xffffffffu, winc, 31);
-    const int wbase = __shfl_sync(0xffffffffu, winc - wv, warp);
-    return wbase + inc - v;
+    __syncthreads();
 }
+
+// nrm combine of the groups [g_beg, g_end) of one warp: score = sum_g
+// exp(S[g] - hm[g]).  GT = G rounded up to a power of two; rows beyond G are
+// read from row G-1 and masked, so the loads are unconditional and all loads
+// of a batch are in flight together.
+template <int GT>
+__device__ __forceinline__ void combine_nrm_groups(
+    const float* __restrict__ sh, float* __restrict__ score, uint32_t* keys,
+    const float* hm_sh, int G, int MP, int s0, int n_loc, int n_comb,
+    int g_beg, int g_end, int lane) {
+    constexpr int CB = (16 / GT > 4) ? 4 : (GT >= 16 ? 1 : 16 / GT);   // <= 16 loads in flight
+    float hm[GT];
+#pragma unroll
+    for (int g = 0; g < GT; ++g) hm[g] = hm_sh[min(g, G - 1)];
+    for (int gb = g_beg; gb < g_end; gb += CB) {
+        float v[CB][GT];
+#pragma unroll
+        for (int u = 0; u < CB; ++u) {
+            const int j = (gb + u) * 32 + lane;
+            const int i = min(s0 + j, n_comb - 1);          // clamped: always valid
+#pragma unroll
+            for (int g = 0; g < GT; ++g)
+                v[u][g] = __ldcg(&sh[(int64_t)min(g, G - 1) * MP + i]);
+        }
+#pragma unroll
+        for (int u = 0; u < CB; ++u) {
+            const int j = (gb + u) * 32 + lane, i = s0 + j;
+            if ((gb + u) < g_end && j < n_loc) {
+                float acc = 0.f;
+#pragma unroll
+                for (int g = 0; g < GT; ++g) {
+                    const float e = __expf(v[u][g] - hm[g]);
+                    acc += (g < G) ? e : 0.f;
+                }
+                if (i < n_comb) score[i] = acc; else acc = 0.f;
+                keys[j] = f2key(acc);
+            }
+        }
+    }
+}
+
+// per-head maxima of the groups of one warp (clamped, unconditional loads)
+template <int GT>
+__device__ __forceinline__ void sweep_max_groups(
+    const float* __restrict__ sh, float* wmax_row, int G, int MP, int s0,
+    int n_loc, int n_comb, int g_beg, int g_end, int lane) {
+    float lmax[GT];
+#pragma unroll
+    for (int g = 0; g < GT; ++g) lmax[g] = -INFINITY;
+    for (int grp = g_beg; grp < g_end; ++grp) {
+        const int j = grp * 32 + lane, i = s0 + j;
+        const int ic = min(i, n_comb - 1);
+        const bool ok = j < n_loc && i < n_comb;
+#pragma unroll
+        for (int g = 0; g < GT; ++g) {
+            const float x = __ldcg(&sh[(int64_t)min(g, G - 1) * MP + ic]);
+            lmax[g] = fmaxf(lmax[g], ok ? x : -INFINITY);
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < GT; ++g) {
+        float m = lmax[g];
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1)
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0 && g < G) wmax_row[g] = m;
+    }
+}
+
+#define LOCKS_DISPATCH_GT(G, CALL)                 \
+    do {                                           \
+        if ((G) <= 1) { constexpr int GT = 1; CALL; }        \
+        else if ((G) <= 2) { constexpr int GT = 2; CALL; }   \
+        else if ((G) <= 4) { constexpr int GT = 4; CALL; }   \
+        else if ((G) <= 8) { constexpr int GT = 8; CALL; }   \
+        else { constexpr int GT = 16; CALL; }                \
+    } while (0)
 
 __global__ void __launch_bounds__(SEL_THREADS)
 topb_kernel(const SelParams p) {
     __shared__ SelSmem sm;
+    extern __shared__ __align__(16) uint32_t keys[];   // keys of my page slice
     cg::cluster_group cluster = cg::this_cluster();
 
+    SEL_TS(0);
     const int c = blockIdx.x, CL = gridDim.x;     // rank / size of the cluster
     const int kh = blockIdx.y, r = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -126,47 +244,34 @@ topb_kernel(const SelParams p) {
     float* score = p.score + row * MP;
     const int n_comb = min(max(nsh, 0), MP);        // pages with a score
 
-    // contiguous page slice of this CTA (covers [0, max(npg, n_comb)))
+    // contiguous page slice of this CTA, a multiple of 32 pages long
     const int span = max(npg, n_comb);
-    const int per_cta = (span + CL - 1) / CL;
+    const int per_cta = (((span + CL - 1) / CL) + 31) & ~31;
     const int s0 = min(c * per_cta, span), s1 = min(s0 + per_cta, span);
+    const int n_loc = s1 - s0;
+    // warp w owns groups [w*gpw, (w+1)*gpw) of 32 consecutive pages
+    const int n_grp = (n_loc + 31) >> 5;
+    const int gpw = (n_grp + SEL_WARPS - 1) / SEL_WARPS;
+    const int g_beg = min(warp * gpw, n_grp), g_end = min(g_beg + gpw, n_grp);
 
-    // ---------------- 1. GQA combine -> score[slice] --------------------------
-    if (p.combine != LOCKS_COMBINE_NONE && n_comb > 0) {
+    // ---------------- 1. GQA combine -> score[slice], keys[slice] --------------
+    if (p.combine == LOCKS_COMBINE_NRM && n_comb > 0) {
         const float* sh = p.score_h + row * (int64_t)G * MP;
-        const int e0 = s0, e1 = min(s1, n_comb);
-        if (p.combine == LOCKS_COMBINE_NRM) {
-            if (p.hmax != nullptr) {
-                if (tid < G) sm.hm_sh[tid] = key2f(p.hmax[row * G + tid]);
-                cluster.sync();                     // everyone has read the keys
-                if (c == 0 && tid < G) p.hmax[row * G + tid] = 0u;
-            } else {
-                float lmax[MAX_G];
-#pragma unroll
-                for (int g = 0; g < MAX_G; ++g) lmax[g] = -INFINITY;
-                for (int i = e0 + tid; i < e1; i += SEL_THREADS) {
-#pragma unroll
-                    for (int g = 0; g < MAX_G; ++g)
-                        if (g < G)
-                            lmax[g] = fmaxf(lmax[g], sh[(int64_t)g * MP + i]);
-                }
-#pragma unroll
-                for (int g = 0; g < MAX_G; ++g) {
-                    if (g < G) {
-                        float m = lmax[g];
-#pragma unroll
-                        for (int o = 16; o >= 1; o >>= 1)
-                            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-                        if (lane == 0) sm.wmax[warp][g] = m;
-                    }
-                }
-                __syncthreads();
-                if (tid < G) {
-                    float m = -INFINITY;
-                    for (int w = 0; w < SEL_WARPS; ++w)
-                        m = fmaxf(m, sm.wmax[w][tid]);
-                    sm.xmax[tid] = m;
-                }
+        if (p.hmax != nullptr) {
+            if (tid < G) sm.hm_sh[tid] = key2f(p.hmax[row * G + tid]);
+            if (CL > 1) cluster.sync();             // everyone has read the keys
+            else __syncthreads();
+            if (c == 0 && tid < G) p.hmax[row * G + tid] = 0u;
+        } else {
+            LOCKS_DISPATCH_GT(G, (sweep_max_groups<GT>(
+                sh, sm.wmax[warp], G, MP, s0, n_loc, n_comb, g_beg, g_end, lane)));
+            __syncthreads();
+            if (tid < G) {
+                float m = -INFINITY;
+                for (int w = 0; w < SEL_WARPS; ++w) m = fmaxf(m, sm.wmax[w][tid]);
+                sm.xmax[tid] = m;
+            }
+            if (CL > 1) {
                 cluster.sync();
                 if (tid < G) {
                     float m = -INFINITY;
@@ -174,31 +279,43 @@ topb_kernel(const SelParams p) {
                         m = fmaxf(m, *cluster.map_shared_rank(&sm.xmax[tid], cc));
                     sm.hm_sh[tid] = m;
                 }
+            } else {
+                __syncthreads();
+                if (tid < G) sm.hm_sh[tid] = sm.xmax[tid];
             }
             __syncthreads();
-            float hm[MAX_G];
-#pragma unroll
-            for (int g = 0; g < MAX_G; ++g) hm[g] = (g < G) ? sm.hm_sh[g] : 0.f;
-            for (int i = e0 + tid; i < e1; i += SEL_THREADS) {
-                float acc = 0.f;
-#pragma unroll
-                for (int g = 0; g < MAX_G; ++g)
-                    if (g < G) acc += __expf(sh[(int64_t)g * MP + i] - hm[g]);
-                score[i] = acc;
-            }
-        } else {                                    // LOCKS_COMBINE_MAX
-            for (int i = e0 + tid; i < e1; i += SEL_THREADS) {
-                float m = -INFINITY;
-                for (int g = 0; g < G; ++g)
-                    m = fmaxf(m, sh[(int64_t)g * MP + i]);
-                score[i] = m;
+        }
+        SEL_TS(20);
+        LOCKS_DISPATCH_GT(G, (combine_nrm_groups<GT>(
+            sh, score, keys, sm.hm_sh, G, MP, s0, n_loc, n_comb, g_beg, g_end,
+            lane)));
+        SEL_TS(21);
+    } else if (p.combine == LOCKS_COMBINE_MAX && n_comb > 0) {
+        const float* sh = p.score_h + row * (int64_t)G * MP;
+        for (int grp = g_beg; grp < g_end; ++grp) {
+            const int j = grp * 32 + lane, i = s0 + j;
+            if (j < n_loc) {
+                float m = 0.f;
+                if (i < n_comb) {
+                    m = -INFINITY;
+                    for (int g = 0; g < G; ++g)
+                        m = fmaxf(m, sh[(int64_t)g * MP + i]);
+                    score[i] = m;
+                }
+                keys[j] = f2key(m);
             }
         }
-        __syncthreads();        // this CTA re-reads only its own slice of score
+    } else {
+        for (int grp = g_beg; grp < g_end; ++grp) {
+            const int j = grp * 32 + lane;
+            if (j < n_loc) keys[j] = f2key(score[s0 + j]);
+        }
     }
+    __syncthreads();
+    SEL_TS(1);
 
-    // selectable part of the slice
-    const int q0 = max(s0, lo), q1 = min(s1, hi);
+    // selectable part of the slice, in local indices
+    const int q0 = max(s0, lo) - s0, q1 = min(s1, hi) - s0;
 
     // ---------------- 2. threshold key (b-th largest of [lo, hi)) -------------
     uint32_t tau_key = 0u;       // below every real key: everything is "> tau"
@@ -211,105 +328,165 @@ topb_kernel(const SelParams p) {
 #pragma unroll 1
         for (int pass = 0; pass < 3; ++pass) {
             const int bits = (pass == 0) ? RBITS0 : (pass == 1) ? RBITS1 : RBITS2;
+            const int nb = 1 << bits;
             shift -= bits;
-            const uint32_t dmask = (1u << bits) - 1u;
-            int* hist = sm.hist[pass & 1];
-            for (int i = tid; i < NBINS; i += SEL_THREADS) hist[i] = 0;
+            const uint32_t dmask = (uint32_t)nb - 1u;
+            for (int i = tid; i < nb; i += SEL_THREADS) { sm.hist[i] = 0; sm.tot[i] = 0; }
             __syncthreads();
-            for (int i = q0 + tid; i < q1; i += SEL_THREADS) {
-                const uint32_t key = f2key(score[i]);
+            for (int j = q0 + tid; j < q1; j += SEL_THREADS) {
+                const uint32_t key = keys[j];
                 if ((key & mask) == prefix)
-                    atomicAdd(&hist[(key >> shift) & dmask], 1);
+                    atomicAdd(&sm.hist[(key >> shift) & dmask], 1);
             }
-            cluster.sync();                 // all slices' histograms are complete
-            // thread t owns bins (NBINS-1-2t) and (NBINS-2-2t): descending order
-            const int bin_a = NBINS - 1 - 2 * tid, bin_b = bin_a - 1;
-            int ca = 0, cb = 0;
-            for (int cc = 0; cc < CL; ++cc) {
-                const int* rh = cluster.map_shared_rank(hist, cc);
-                ca += rh[bin_a];
-                cb += rh[bin_b];
-            }
-            int tot;
-            const int above = block_exclusive_scan(ca + cb, sm.warp_tot, tot);
-            if (above < k && k <= above + ca + cb) {
-                if (k <= above + ca) {
-                    sm.sh_prefix = prefix | ((uint32_t)bin_a << shift);
-                    sm.sh_k = k - above;
-                } else {
-                    sm.sh_prefix = prefix | ((uint32_t)bin_b << shift);
-                    sm.sh_k = k - above - ca;
+            SEL_TS(2 + 4 * pass);
+            if (CL == 1) {
+                __syncthreads();
+                find_digit(sm, sm.hist, nb, 0, k);
+            } else {
+                cluster.sync();             // all slices' histograms are complete
+                // reduce-scatter: CTA c sums bins [c*bs, (c+1)*bs) of every CTA
+                const int bs = nb / CL;
+                for (int e = tid; e < bs * CL; e += SEL_THREADS) {
+                    const int bin = c * bs + (e % bs), src = e / bs;
+                    const int v = cluster.map_shared_rank(sm.hist, src)[bin];
+                    if (v) atomicAdd(&sm.tot[bin], v);
                 }
+                __syncthreads();
+                // total of my bin slice
+                int part = 0;
+                for (int e = tid; e < bs; e += SEL_THREADS) part += sm.tot[c * bs + e];
+#pragma unroll
+                for (int o = 16; o >= 1; o >>= 1)
+                    part += __shfl_xor_sync(0xffffffffu, part, o);
+                if (lane == 0) sm.wtot2[warp] = part;
+                __syncthreads();
+                if (tid == 0) {
+                    int t = 0;
+                    for (int w = 0; w < SEL_WARPS; ++w) t += sm.wtot2[w];
+                    sm.x_slice_tot = t;
+                }
+                cluster.sync();             // slice totals + summed slices ready
+                // locate the slice (from the top) that holds the k-th key
+                int above = 0, sl = CL - 1;
+                for (int cc = CL - 1; cc >= 0; --cc) {
+                    const int t = *cluster.map_shared_rank(&sm.x_slice_tot, cc);
+                    if (k <= above + t) { sl = cc; break; }
+                    above += t;
+                }
+                // copy that summed slice locally (into hist, now free) and search
+                const int* rt = cluster.map_shared_rank(sm.tot, sl);
+                __syncthreads();
+                for (int e = tid; e < nb; e += SEL_THREADS)
+                    sm.hist[e] = (e >= sl * bs && e < (sl + 1) * bs) ? rt[e] : 0;
+                __syncthreads();
+                find_digit(sm, sm.hist, (sl + 1) * bs, above, k);
+                cluster.sync();             // remote reads of tot are finished
             }
-            __syncthreads();
-            prefix = sm.sh_prefix;
-            k = sm.sh_k;
+            prefix |= (uint32_t)sm.sh_i0 << shift;
+            k = sm.sh_i1;
             mask |= dmask << shift;
+            __syncthreads();
+            SEL_TS(5 + 4 * pass);
         }
         tau_key = prefix;
         quota = k;
     }
 
     // ---------------- 3. keep flags + ascending compaction --------------------
-    // thread-contiguous chunks inside the slice [s0, min(s1, npg))
-    const int t1 = min(s1, npg), t0 = min(s0, t1);
-    const int per = (t1 - t0 + SEL_THREADS - 1) / SEL_THREADS;
-    const int c0 = min(t0 + tid * per, t1), c1 = min(c0 + per, t1);
-    int n_eq = 0;
+    // ties in my groups
+    int w_eq = 0;
     if (!keep_all)
-        for (int i = max(c0, lo); i < min(c1, hi); ++i)
-            n_eq += (f2key(score[i]) == tau_key);
-    int tot_eq;
-    int eq_base = block_exclusive_scan(n_eq, sm.warp_tot, tot_eq);
-    if (tid == 0) sm.x_eq = tot_eq;
-    cluster.sync();
-    for (int cc = 0; cc < c; ++cc)
-        eq_base += *cluster.map_shared_rank(&sm.x_eq, cc);
-    int kept = 0;
+        for (int grp = g_beg; grp < g_end; ++grp) {
+            const int j = grp * 32 + lane;
+            const bool eq = j >= q0 && j < q1 && keys[j] == tau_key;
+            w_eq += __popc(__ballot_sync(0xffffffffu, eq));
+        }
+    if (lane == 0) sm.wtot[warp] = w_eq;
+    __syncthreads();
+    scan_warp_totals(sm.wtot);
+    __syncthreads();
+    int eq_base = warp ? sm.wtot[warp - 1] : 0;
+    if (CL > 1) {
+        if (tid == 0) sm.x_eq = sm.wtot[SEL_WARPS - 1];
+        SEL_TS(14);
+        cluster.sync();
+        for (int cc = 0; cc < c; ++cc)
+            eq_base += *cluster.map_shared_rank(&sm.x_eq, cc);
+    }
+    SEL_TS(15);
+    // kept pages in my groups (keep masks are recomputed when writing)
+    const uint32_t lt_mask = (1u << lane) - 1u;
+    int w_kept = 0;
     {
         int eqr = eq_base;
-        for (int i = c0; i < c1; ++i) {
-            bool keep = true;
-            if (!keep_all && i >= lo && i < hi) {
-                const uint32_t key = f2key(score[i]);
-                if (key == tau_key) keep = (++eqr <= quota);
-                else keep = key > tau_key;
-            }
-            kept += keep;
+        for (int grp = g_beg; grp < g_end; ++grp) {
+            const int j = grp * 32 + lane, i = s0 + j;
+            const bool in = j < n_loc && i < npg;
+            const bool selr = !keep_all && j >= q0 && j < q1;
+            const uint32_t key = (j < n_loc) ? keys[j] : 0u;
+            const bool eq = selr && key == tau_key;
+            const uint32_t eqb = __ballot_sync(0xffffffffu, eq);
+            bool keep = in;
+            if (selr) keep = eq ? (eqr + __popc(eqb & lt_mask) + 1 <= quota)
+                                : (key > tau_key);
+            eqr += __popc(eqb);
+            w_kept += __popc(__ballot_sync(0xffffffffu, keep));
         }
     }
-    int tot_kept;
-    int pos = block_exclusive_scan(kept, sm.warp_tot, tot_kept);
-    if (tid == 0) sm.x_kept = tot_kept;
-    cluster.sync();
-    int cnt = 0;
-    for (int cc = 0; cc < CL; ++cc) {
-        const int v = *cluster.map_shared_rank(&sm.x_kept, cc);
-        if (cc < c) pos += v;
-        cnt += v;
+    if (lane == 0) sm.wtot2[warp] = w_kept;
+    __syncthreads();
+    scan_warp_totals(sm.wtot2);
+    __syncthreads();
+    int pos = warp ? sm.wtot2[warp - 1] : 0;
+    int cnt = sm.wtot2[SEL_WARPS - 1];
+    if (CL > 1) {
+        if (tid == 0) sm.x_kept = cnt;
+        SEL_TS(16);
+        cluster.sync();
+        cnt = 0;
+        for (int cc = 0; cc < CL; ++cc) {
+            const int v = *cluster.map_shared_rank(&sm.x_kept, cc);
+            if (cc < c) pos += v;
+            cnt += v;
+        }
     }
+    SEL_TS(17);
     int32_t* tab = p.page_table + row * MP;
     {
         int eqr = eq_base;
-        for (int i = c0; i < c1; ++i) {
-            bool keep = true;
-            if (!keep_all && i >= lo && i < hi) {
-                const uint32_t key = f2key(score[i]);
-                if (key == tau_key) keep = (++eqr <= quota);
-                else keep = key > tau_key;
-            }
-            if (keep) tab[pos++] = i;
+        for (int grp = g_beg; grp < g_end; ++grp) {
+            const int j = grp * 32 + lane, i = s0 + j;
+            const bool in = j < n_loc && i < npg;
+            const bool selr = !keep_all && j >= q0 && j < q1;
+            const uint32_t key = (j < n_loc) ? keys[j] : 0u;
+            const bool eq = selr && key == tau_key;
+            const uint32_t eqb = __ballot_sync(0xffffffffu, eq);
+            bool keep = in;
+            if (selr) keep = eq ? (eqr + __popc(eqb & lt_mask) + 1 <= quota)
+                                : (key > tau_key);
+            eqr += __popc(eqb);
+            const uint32_t kb = __ballot_sync(0xffffffffu, keep);
+            if (keep) tab[pos + __popc(kb & lt_mask)] = i;
+            pos += __popc(kb);
         }
     }
     // -1 padding of [cnt, MP), shared by the cluster
     for (int i = cnt + c * SEL_THREADS + tid; i < MP; i += CL * SEL_THREADS)
         tab[i] = -1;
     if (c == 0 && tid == 0) p.page_cnt[row] = cnt;
-    cluster.sync();              // keep shared memory alive for remote readers
+    SEL_TS(18);
+    if (CL > 1) cluster.sync();  // keep shared memory alive for remote readers
+    SEL_TS(19);
 }
 
 }  // namespace
 }  // namespace locks
+
+#ifdef LOCKS_SEL_TIMING
+extern "C" int locks_debug_sel_timing(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, locks::g_sel_ts, sizeof(long long) * 32);
+}
+#endif
 
 extern "C" int locks_derive_page_params(
     const int32_t* seq_lens, int n_req, int page, int window_pages,
@@ -351,18 +528,28 @@ extern "C" int locks_topb_select(
     p.n_pages = n_pages; p.n_sel_hi = n_sel_hi; p.b_fix = b_fix;
     p.page_table = page_table; p.page_cnt = page_cnt;
     p.n_kv = n_kv; p.G = G; p.max_pages = max_pages; p.sink = sink_pages;
-    // cluster size: spread one (request, kv-head) over up to 8 SMs when the
-    // grid is small; a power of two; never more CTAs than 1024-page slices
+    // cluster size: the smallest power of two whose CTAs can hold the keys of
+    // one (request, kv-head) in shared memory (one CTA up to 16384 pages)
     int cl = 1;
-    {
-        const int want = sm_count() / max(1, n_kv * n_req);
-        const int useful = (max_pages + SEL_THREADS - 1) / SEL_THREADS;
-        while (cl * 2 <= want && cl * 2 <= useful && cl < MAX_CL) cl *= 2;
+    while (cl < MAX_CL && (max_pages + cl - 1) / cl > KEYS_PER_CTA) cl *= 2;
+    LOCKS_REQUIRE((max_pages + cl - 1) / cl <= KEYS_PER_CTA, LOCKS_ERR_SIZE,
+                  "locks_topb_select: max_pages %d beyond the supported %d",
+                  max_pages, MAX_CL * KEYS_PER_CTA);
+    const int per_cta = ((((max_pages + cl - 1) / cl) + 31) & ~31) + 32;
+    const int dyn_smem = per_cta * 4;
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        cudaFuncSetAttribute(topb_kernel,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (KEYS_PER_CTA + 64) * 4);
+        attr_done[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(cl, n_kv, n_req);
     cfg.blockDim = dim3(SEL_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = dyn_smem;
     cfg.stream = static_cast<cudaStream_t>(stream);
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
