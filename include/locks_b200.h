@@ -192,6 +192,64 @@ int locks_dense_decode(const void* q, int64_t q_stride_req, const void* k_cache,
                        int split, float scale, int* status,
                        locks_stream_t stream);
 
+/* ---- MLA (latent KV) path ------------------------------------------------
+ * Geometry: latent width kv_lora_rank 512 + rope 64 = 576, page 16, 16 query
+ * heads sharing one latent head (16 is the fragment height; fewer heads are
+ * padded by the caller with zero rows).
+ *
+ * One factor record per physical block (LOCKS_MLA_REC_BYTES):
+ *   [0,8192)    Rf  fp16 8 x 512   right factors, row r = mode r (descending)
+ *   [8192,8448) Lf  fp16 16 x 8    left factors (token x mode), Lf Rf ~ page
+ * The rope part of the keys is read from the latent cache itself. */
+#define LOCKS_MLA_REC_BYTES 8448
+#define LOCKS_MLA_LKV 512
+#define LOCKS_MLA_ROPE 64
+#define LOCKS_MLA_HEADS 16
+
+/* Rank-8 factors of each listed block's 16 x 512 latent page: Gram (16x16),
+ * Jacobi eigh, top-8 modes in descending order, modes at or below
+ * sigma_1*sqrt(eps) zeroed; Lf = W sigma, Rf = W^T page / sigma.
+ * cache: bf16 (num_blocks, 16, 576) with the given element strides.
+ * Replaces selection/mla_select.py:26-108 (_page_basis, build_page_factors). */
+int locks_mla_build_factors(const void* cache, int64_t stride_block,
+                            int64_t stride_tok, void* records,
+                            const int32_t* blocks, int n_blocks, int num_blocks,
+                            locks_stream_t stream);
+
+/* Per-row page parameters of the MLA keep rule: n_pages = ceil(L/16);
+ * n_sel_hi = n_pages - window; b = n_pages when n_pages <= budget_pages (keep
+ * all), else budget_pages - |sink pages U last window pages| (>= 0).
+ * Replaces the bookkeeping of selection/mla_score_torch.py:51-73 (topb_middle). */
+int locks_mla_derive(const int32_t* seq_lens, int n_rows, int budget_pages,
+                     int sink_pages, int window_pages, int32_t* n_pages,
+                     int32_t* n_sel_hi, int32_t* b_fix, locks_stream_t stream);
+
+/* score[row,p] = scale * max_h max_t ((q_c[h] Rf^T) Lf^T + q_rope[h] k_rope^T)[t]
+ * for p < n_cache[row]; -inf for n_cache[row] <= p < n_pages[row].
+ * q: bf16 (n_rows, 16, 576) = [q_c | q_rope].  score: f32 (n_rows, max_pages).
+ * Replaces selection/mla_score_triton.py:98-151 (factored batched scorer);
+ * CPU twin selection/mla_score_torch.py:27-48.  Selection itself is
+ * locks_topb_select(LOCKS_COMBINE_NONE) with n_kv = 1. */
+int locks_mla_score(const void* q, int64_t q_stride_row, const void* records,
+                    const void* cache, int64_t stride_block, int64_t stride_tok,
+                    const int32_t* block_table, int64_t bt_stride,
+                    const int32_t* n_cache, const int32_t* n_pages, float* score,
+                    int n_rows, int max_pages, int num_blocks, float scale,
+                    int zsplit, int* status, locks_stream_t stream);
+
+/* Attention of every row over its kept pages of the latent cache:
+ * o[row,h,:512] = softmax(scale * q[h] . kv^T) kv[:, :512], lse = logsumexp.
+ * Tokens at or beyond seq_lens[row] are masked.  o: bf16 (n_rows,16,512),
+ * lse: f32 (n_rows,16).  One thread-block cluster per row.
+ * Replaces backend/mla_attn.py:178-201. */
+int locks_mla_decode(const void* q, int64_t q_stride_row, const void* cache,
+                     int64_t stride_block, int64_t stride_tok,
+                     const int32_t* block_table, int64_t bt_stride,
+                     const int32_t* page_table, const int32_t* page_cnt,
+                     const int32_t* seq_lens, void* out, float* lse, int n_rows,
+                     int max_pages, float scale, int* status,
+                     locks_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -13,6 +13,7 @@
 // LAPACK-based build only after the per-column sign is aligned; scales, the
 // centroid and every score computed from the record are sign-free.
 #include "common.cuh"
+#include "jacobi16.cuh"
 
 namespace locks {
 namespace {
@@ -21,7 +22,6 @@ constexpr int BW = 4;                  // warps (jobs) per CTA
 constexpr int PAGE_T = 16;
 constexpr int HD = 128;
 constexpr int DC_PITCH = HD + 4;       // floats, keeps float4 rows conflict-free
-constexpr int MAX_SWEEPS = 14;
 
 struct WarpScratch {
     float dc[PAGE_T][DC_PITCH];
@@ -121,69 +121,7 @@ __global__ void __launch_bounds__(BW * 32) rki4_build_kernel(const BuildParams p
         for (int j = lane + 1; j < PAGE_T; ++j) ws.A[j][lane] = ws.A[lane][j];
     __syncwarp();
 
-    // ---- Jacobi sweeps -----------------------------------------------------------
-    float trace = (lane < PAGE_T) ? ws.A[lane][lane] : 0.f;
-#pragma unroll
-    for (int o = 16; o >= 1; o >>= 1) trace += __shfl_xor_sync(0xffffffffu, trace, o);
-    const float floor_abs = 1e-9f * fabsf(trace);   // below fp32 noise of A
-    for (int sweep = 0; sweep < MAX_SWEEPS; ++sweep) {
-        bool rotated = false;
-        for (int rd = 0; rd < 15; ++rd) {
-            // pair k of this round: (a_k, b_k)
-            int pk, qk;
-            {
-                const int k = lane & 7;
-                int a = (rd + k) % 15;
-                int b = (k == 0) ? 15 : (rd + 15 - k) % 15;
-                pk = min(a, b); qk = max(a, b);
-            }
-            if (lane < 8) {
-                const float app = ws.A[pk][pk], aqq = ws.A[qk][qk];
-                const float apq = ws.A[pk][qk];
-                float c = 1.f, s = 0.f;
-                if (fabsf(apq) > floor_abs &&
-                    fabsf(apq) > 1e-7f * sqrtf(fabsf(app * aqq))) {
-                    const float theta = __fdiv_rn(aqq - app, 2.f * apq);
-                    const float t = __fdiv_rn(
-                        copysignf(1.f, theta),
-                        fabsf(theta) + sqrtf(fmaf(theta, theta, 1.f)));
-                    c = __fdiv_rn(1.f, sqrtf(fmaf(t, t, 1.f)));
-                    s = t * c;
-                    rotated = true;
-                }
-                ws.rc[lane] = c; ws.rs[lane] = s;
-            }
-            __syncwarp();
-            // rows:  A <- J^T A   (pair k, columns 4*(lane/8) .. +3)
-            {
-                const int k = lane & 7, jb = (lane >> 3) * 4;
-                const float c = ws.rc[k], s = ws.rs[k];
-#pragma unroll
-                for (int j = jb; j < jb + 4; ++j) {
-                    const float x = ws.A[pk][j], y = ws.A[qk][j];
-                    ws.A[pk][j] = c * x - s * y;
-                    ws.A[qk][j] = s * x + c * y;
-                }
-            }
-            __syncwarp();
-            // columns:  A <- A J,  U <- U J   (pair k, rows 4*(lane/8) .. +3)
-            {
-                const int k = lane & 7, ib = (lane >> 3) * 4;
-                const float c = ws.rc[k], s = ws.rs[k];
-#pragma unroll
-                for (int i = ib; i < ib + 4; ++i) {
-                    const float x = ws.A[i][pk], y = ws.A[i][qk];
-                    ws.A[i][pk] = c * x - s * y;
-                    ws.A[i][qk] = s * x + c * y;
-                    const float u = ws.U[i][pk], v = ws.U[i][qk];
-                    ws.U[i][pk] = c * u - s * v;
-                    ws.U[i][qk] = s * u + c * v;
-                }
-            }
-            __syncwarp();
-        }
-        if (!__any_sync(0xffffffffu, rotated)) break;
-    }
+    jacobi16_warp(ws.A, ws.U, ws.rc, ws.rs, lane);
 
     // ---- rank the eigenvalues, keep the top 8 in ascending order ----------------
     if (lane < PAGE_T) {

@@ -320,8 +320,9 @@ topb_kernel(const SelParams p) {
     // ---------------- 2. threshold key (b-th largest of [lo, hi)) -------------
     uint32_t tau_key = 0u;       // below every real key: everything is "> tau"
     int quota = 0;
-    if (!keep_all && b < L) {
-        b = max(b, 1);
+    if (!keep_all && b <= 0) {
+        tau_key = 0xFFFFFFFFu;   // above every real key: no selectable page kept
+    } else if (!keep_all && b < L) {
         uint32_t prefix = 0u, mask = 0u;
         int k = b;
         int shift = 32;
