@@ -178,6 +178,35 @@ int locks_decode_fused(const void* q, int64_t q_stride_req, const void* k_cache,
                        int head_dim, int page, int max_pages, float scale,
                        int* status, locks_stream_t stream);
 
+/* Split decode + merge WITHOUT caller-provided partial buffers.  No counterpart
+ * in the reference (its kernels always take caller-allocated partials).
+ * For callers that cannot allocate device memory -- e.g. a host-language
+ * binding that may only forward pointers it was handed, or code running where
+ * cudaMalloc would stall the device -- the (m, l, acc) partials live in a fixed
+ * array inside the library: LOCKS_NOALLOC_MAX_ROWS x 130 floats (about 8.5 MB
+ * that every GPU loading the library keeps until the process exits).
+ * Same arguments and results as locks_decode_split followed by
+ * locks_merge_splits.  Limits and rules:
+ *   - n_req*n_kv*split*G must not exceed LOCKS_NOALLOC_MAX_ROWS, otherwise
+ *     LOCKS_ERR_SIZE is returned and nothing is launched;
+ *   - the first call on a device resolves the array's device address (a CUDA
+ *     runtime query, not a stream operation): make that first call before any
+ *     stream capture begins on that device, with the device current;
+ *   - all calls share the one array and it keeps the previous call's contents;
+ *     nothing in it has to start at zero (only partials written by the current
+ *     call are read back), but two calls whose kernels overlap on the GPU --
+ *     different streams, or graph branches -- race on it: serialise them;
+ *   - it performs no cudaMalloc/cudaFree and calls no allocating library. */
+#define LOCKS_NOALLOC_MAX_ROWS 16384
+int locks_decode_split_noalloc(
+    const void* q, int64_t q_stride_req, const void* k_cache,
+    const void* v_cache, int64_t kv_stride_block, int64_t kv_stride_tok,
+    int64_t kv_stride_head, const int32_t* block_table, int64_t bt_stride,
+    const int32_t* page_table, const int32_t* page_cnt, const int32_t* seq_lens,
+    void* out, int64_t out_stride_req, int n_req, int n_kv, int G, int head_dim,
+    int page, int max_pages, int split, int pps_min, float scale, int* status,
+    locks_stream_t stream);
+
 /* Dense full-KV paged decode (every page of every request) with the same
  * split kernel and merge: the baseline of the sparse/dense crossover curve.
  * The reference takes its dense baseline from FlashAttention

@@ -635,3 +635,92 @@ extern "C" int locks_dense_decode(
     merge_kernel<<<dim3(n_kv * G, n_req), HD, 0, s>>>(m);
     return check_launch("locks_dense_decode(merge)");
 }
+
+// --------------------------------------------------------------------------- //
+// Split decode + merge for callers that must not allocate                      //
+// --------------------------------------------------------------------------- //
+// The split partials (m, l, acc) normally live in buffers the caller allocates
+// once.  Some callers cannot do that: a plugin that is handed a stream inside a
+// memory-pool-managed region where cudaMalloc would synchronise the device, or
+// a host language binding that may only pass pointers it was given.  For them
+// the partials live in the fixed array below.  It is part of the library image:
+// every GPU that loads the library holds these bytes until the process exits.
+namespace locks {
+namespace {
+constexpr int NOALLOC_MAX_ROWS = LOCKS_NOALLOC_MAX_ROWS;   // n_req*n_kv*split*G
+constexpr size_t NOALLOC_FLOATS = (size_t)NOALLOC_MAX_ROWS * (HD + 2);
+static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_FLOATS];
+// device address of the array, per device (the symbol itself is only a
+// host-side handle and must never be passed to a kernel)
+float* g_noalloc_ptr[64] = {nullptr};
+}  // namespace
+}  // namespace locks
+
+extern "C" int locks_decode_split_noalloc(
+    const void* q, int64_t q_stride_req, const void* k_cache,
+    const void* v_cache, int64_t kv_stride_block, int64_t kv_stride_tok,
+    int64_t kv_stride_head, const int32_t* block_table, int64_t bt_stride,
+    const int32_t* page_table, const int32_t* page_cnt, const int32_t* seq_lens,
+    void* out, int64_t out_stride_req, int n_req, int n_kv, int G, int head_dim,
+    int page, int max_pages, int split, int pps_min, float scale, int* status,
+    locks_stream_t stream) {
+    LOCKS_REQUIRE(q && k_cache && v_cache && block_table && page_table &&
+                      page_cnt && seq_lens && out,
+                  LOCKS_ERR_ARG, "locks_decode_split_noalloc: null pointer argument");
+    int rc = check_geometry("locks_decode_split_noalloc", G, head_dim, page);
+    if (rc) return rc;
+    rc = check_kv("locks_decode_split_noalloc", q, k_cache, v_cache, q_stride_req,
+                  kv_stride_block, kv_stride_tok, kv_stride_head);
+    if (rc) return rc;
+    LOCKS_REQUIRE(n_req >= 0 && n_req <= 65535 && n_kv >= 1 && n_kv <= 65535 &&
+                      split >= 1 && pps_min >= 1 && max_pages >= 1,
+                  LOCKS_ERR_ARG, "locks_decode_split_noalloc: bad size argument");
+    const int64_t rows = (int64_t)n_req * n_kv * split * G;
+    LOCKS_REQUIRE(rows <= NOALLOC_MAX_ROWS, LOCKS_ERR_SIZE,
+                  "locks_decode_split_noalloc: n_req*n_kv*split*G = %lld exceeds "
+                  "the built-in scratch of %d partial rows; use locks_decode_split "
+                  "with caller-owned buffers", (long long)rows, NOALLOC_MAX_ROWS);
+    if (n_req == 0) return LOCKS_OK;
+
+    // one-time set-up per device, with that device current: resolve the device
+    // address of the scratch array
+    int dev = -1;
+    cudaError_t ce = cudaGetDevice(&dev);
+    LOCKS_REQUIRE(ce == cudaSuccess && dev >= 0 && dev < 64, LOCKS_ERR_LAUNCH,
+                  "locks_decode_split_noalloc: cudaGetDevice: %s",
+                  cudaGetErrorString(ce));
+    if (g_noalloc_ptr[dev] == nullptr) {
+        float* ptr = nullptr;
+        ce = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
+        LOCKS_REQUIRE(ce == cudaSuccess && ptr != nullptr, LOCKS_ERR_LAUNCH,
+                      "locks_decode_split_noalloc: cudaGetSymbolAddress: %s",
+                      cudaGetErrorString(ce));
+        g_noalloc_ptr[dev] = ptr;
+    }
+    float* base = g_noalloc_ptr[dev];
+    float* m_part = base;
+    float* l_part = base + NOALLOC_MAX_ROWS;
+    float* acc_part = base + 2 * (size_t)NOALLOC_MAX_ROWS;
+
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    DecParams p{};
+    p.q = static_cast<const __nv_bfloat16*>(q); p.q_stride_req = q_stride_req;
+    p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
+    p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
+    p.stride_block = kv_stride_block; p.stride_tok = kv_stride_tok;
+    p.stride_head = kv_stride_head;
+    p.block_table = block_table; p.bt_stride = bt_stride;
+    p.page_table = page_table; p.page_cnt = page_cnt; p.seq_lens = seq_lens;
+    p.m_part = m_part; p.l_part = l_part; p.acc_part = acc_part;
+    p.n_kv = n_kv; p.G = G; p.max_pages = max_pages; p.split = split;
+    p.pps_min = pps_min; p.fused = 0; p.scale = scale; p.status = status;
+    rc = launch_decode("locks_decode_split_noalloc", p, n_req, split, s);
+    if (rc) return rc;
+    MergeParams m{};
+    m.m_part = m_part; m.l_part = l_part; m.acc_part = acc_part;
+    m.page_cnt = page_cnt; m.seq_lens = nullptr;
+    m.out = static_cast<__nv_bfloat16*>(out); m.out_stride_req = out_stride_req;
+    m.n_kv = n_kv; m.G = G; m.split = split; m.pps_min = pps_min;
+    merge_kernel<<<dim3(n_kv * G, n_req), HD, 0, s>>>(m);
+    return check_launch("locks_decode_split_noalloc(merge)");
+}

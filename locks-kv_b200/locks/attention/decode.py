@@ -178,3 +178,33 @@ def dense_paged_decode(q, kv_cache, block_table, seq_lens, buf, out, *, n_kv,
                _cabi.ptr(buf.acc), _cabi.ptr(out), out.stride(0), n_req,
                int(n_kv), int(G), d, page, int(buf.split), float(scale),
                _cabi.ptr(status), _cabi.stream())
+
+
+NOALLOC_MAX_ROWS = 16384
+
+
+def sparse_paged_decode_noalloc(q, kv_cache, block_table, seq_lens, st, out,
+                                vsource, *, split: int, scale: float = None) -> None:
+    """Split decode + merge whose partial buffers live inside the library.
+
+    For integrations that are not allowed to allocate device memory (they can
+    only hand over the tensors they were given): nothing is taken from
+    ``st.m_part / l_part / acc_part``; the partials go to a fixed ~8.5 MB array
+    that is part of the loaded library on every GPU.  Limits: ``n_req * n_kv *
+    split * G <= 16384`` (a ``RuntimeError`` otherwise); make the first call on
+    a device outside stream capture (it looks up the array's address once);
+    calls share the array, so do not let two of them overlap on the GPU.
+    Results equal ``sparse_paged_decode_batched`` with the same ``split``.
+    """
+    if scale is None:
+        scale = st.scale
+    n_req = int(seq_lens.shape[0])
+    k, v = _kv_args(kv_cache, vsource)
+    _cabi.call("locks_decode_split_noalloc", _cabi.ptr(q), q.stride(0),
+               _cabi.ptr(k), _cabi.ptr(v), k.stride(0), k.stride(1), k.stride(2),
+               _cabi.ptr(block_table), block_table.stride(0),
+               _cabi.ptr(st.page_table), _cabi.ptr(st.page_cnt),
+               _cabi.ptr(seq_lens), _cabi.ptr(out), out.stride(0), n_req,
+               int(st.n_kv), int(st.G), int(st.d), int(st.page),
+               int(st.max_pages), int(split), int(_pps_min(n_req, st.n_kv)),
+               float(scale), _cabi.ptr(st.status), _cabi.stream())
