@@ -55,6 +55,15 @@ extern "C" {
 
 typedef void* locks_stream_t;     /* a cudaStream_t */
 
+/* Programmatic dependent launch between score -> select -> fused decode -> next
+ * layer's score (on by default; returns the previous setting).  With it the
+ * scorer prefetches summary records while the previous layer's select / decode
+ * still run.  The reference chains its kernels the same way with
+ * griddepcontrol (selection/select_cuda.py:202-206, attention/decode_cuda.py:
+ * 304-315).  Contract: block tables must not be written by the kernel launched
+ * immediately before a scorer launch on the same stream. */
+int locks_set_pdl(int enable);
+
 int locks_version(void);
 const char* locks_last_error(void);
 /* Bytes of one summary record (without the tag).  Replaces

@@ -47,9 +47,21 @@ int sm_count() {
     return cache[dev];
 }
 
+static int g_pdl = 1;
+bool pdl_enabled() { return g_pdl != 0; }
+static thread_local bool g_pdl_break = true;
+void pdl_break() { g_pdl_break = true; }
+bool pdl_take_break() { const bool b = g_pdl_break; g_pdl_break = false; return b; }
+
 }  // namespace locks
 
 extern "C" {
+
+int locks_set_pdl(int enable) {
+    const int old = locks::g_pdl;
+    locks::g_pdl = enable ? 1 : 0;
+    return old;
+}
 
 int locks_version(void) { return LOCKS_ABI_VERSION; }
 

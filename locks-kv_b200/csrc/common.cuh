@@ -15,6 +15,12 @@ void set_error(const char* fmt, ...);
 int  fail(int code, const char* fmt, ...);
 int  check_launch(const char* what);
 int  sm_count();
+bool pdl_enabled();
+// A launcher that writes what the scorer reads BEFORE its pdl_wait() (summary
+// records, page parameters) calls pdl_break(); the next scorer launch then
+// takes an ordinary full stream dependency instead of a programmatic one.
+void pdl_break();
+bool pdl_take_break();
 
 #define LOCKS_REQUIRE(cond, code, ...)                                        \
     do {                                                                      \
@@ -94,6 +100,37 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src,
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes "
         "[%0], [%1], %2, [%3];"
         ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// Programmatic dependent launch.  A kernel launched with the programmatic
+// stream-serialization attribute may start while its predecessor is still
+// running; pdl_wait() blocks until the predecessor grid has completed and its
+// writes are visible (a no-op without the attribute).  pdl_trigger() lets the
+// successor's CTAs be scheduled once every CTA of this grid has called it.
+__device__ __forceinline__ void pdl_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_trigger() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// L2 eviction policies for data that is read once per step (evict_first) or
+// that later kernels re-read (evict_last)
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+// bulk copy with an L2 cache-policy hint
+__device__ __forceinline__ void bulk_g2s_hint(void* dst, const void* src,
+                                              uint32_t bytes, uint64_t* bar,
+                                              uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes"
+        ".L2::cache_hint [%0], [%1], %2, [%3], %4;"
+        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)),
+          "l"(policy)
         : "memory");
 }
 

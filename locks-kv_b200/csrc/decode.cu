@@ -26,7 +26,7 @@ namespace cg = cooperative_groups;
 namespace locks {
 namespace {
 
-constexpr int DW = 4;                 // warps per CTA
+constexpr int DW = 8;                 // warps per CTA
 constexpr int DTHREADS = DW * 32;
 constexpr int DSTAGES = 2;
 constexpr int PAGE_T = 16;
@@ -72,12 +72,10 @@ struct DecParams {
 
 __device__ __forceinline__ void issue_page(DecSmem& sm, const DecParams& p,
                                            int warp, int lane, int stage,
-                                           int r, int kh, int64_t row, int j,
+                                           int kh, int pt, int blk,
                                            int seq_len, int& n_valid_out) {
-    int pt = p.page_table ? p.page_table[row * p.max_pages + j] : j;
-    int n_valid = (pt >= 0) ? min(max(seq_len - pt * PAGE_T, 0), PAGE_T) : 0;
-    pt = max(pt, 0);
-    const int blk = max(p.block_table[(int64_t)r * p.bt_stride + pt], 0);
+    const int n_valid = (pt >= 0) ? min(max(seq_len - pt * PAGE_T, 0), PAGE_T) : 0;
+    blk = max(blk, 0);
     n_valid_out = n_valid;
     uint64_t* bar = &sm.full[warp][stage];
     fence_proxy_async();
@@ -110,6 +108,8 @@ decode_kernel(const DecParams p) {
     const int gid = lane >> 2, tig = lane & 3;
     const int G = p.G;
     const int64_t row = (int64_t)r * p.n_kv + kh;
+    pdl_trigger();            // the next layer's scorer may start prefetching
+    pdl_wait();               // page tables / counts come from the selector
     const int seq_len = p.seq_lens[r];
 
     const int cnt = p.page_cnt ? p.page_cnt[row]
@@ -139,9 +139,27 @@ decode_kernel(const DecParams p) {
     const int first = j0 + warp;
     const int n_mine = (first < j1) ? (j1 - first + DW - 1) / DW : 0;
     int nv[DSTAGES] = {0, 0};
-    for (int it = 0; it < DSTAGES && it < n_mine; ++it)
-        issue_page(sm, p, warp, lane, it, r, kh, row, first + it * DW, seq_len,
-                   nv[it]);
+    // Page-table entry and physical block of the warp's pages, 32 at a time
+    // (lane i holds entry i of the window), so that the two dependent index
+    // loads are paid once per window instead of once per page.
+    int win_pt = -1, win_blk = 0;
+    auto load_window = [&](int it0) {
+        const int it = it0 + lane;
+        win_pt = -1; win_blk = 0;
+        if (it < n_mine) {
+            const int j = first + it * DW;
+            win_pt = p.page_table ? p.page_table[row * p.max_pages + j] : j;
+            win_blk = p.block_table[(int64_t)r * p.bt_stride + max(win_pt, 0)];
+        }
+    };
+    auto issue_it = [&](int it) {
+        const int pt = __shfl_sync(0xffffffffu, win_pt, it & 31);
+        const int blk = __shfl_sync(0xffffffffu, win_blk, it & 31);
+        issue_page(sm, p, warp, lane, it % DSTAGES, kh, pt, blk, seq_len,
+                   nv[it % DSTAGES]);
+    };
+    load_window(0);
+    for (int it = 0; it < DSTAGES && it < n_mine; ++it) issue_it(it);
 
     // ---- Q fragments (A operand), rows gid and gid+8 -------------------------
     uint32_t qa[8][4];
@@ -263,9 +281,10 @@ decode_kernel(const DecParams p) {
             }
         }
         __syncwarp();                               // stage fully consumed
-        if (it + DSTAGES < n_mine)
-            issue_page(sm, p, warp, lane, stage, r, kh, row,
-                       first + (it + DSTAGES) * DW, seq_len, nv[stage]);
+        if (it + DSTAGES < n_mine) {
+            if (((it + DSTAGES) & 31) == 0) load_window(it + DSTAGES);
+            issue_it(it + DSTAGES);
+        }
     }
 
     // ---- combine the four warps ------------------------------------------------
@@ -293,9 +312,9 @@ decode_kernel(const DecParams p) {
     }
     __syncthreads();
 
-    const int d = tid;                            // 128 threads = 128 channels
     if (!CLUSTER) {
-        for (int g = 0; g < G; ++g) {
+        for (int e = tid; e < G * HD; e += DTHREADS) {
+            const int g = e / HD, d = e % HD;
             float M = -INFINITY;
 #pragma unroll
             for (int w = 0; w < DW; ++w) M = fmaxf(M, sm.cm[w][g]);
@@ -314,8 +333,10 @@ decode_kernel(const DecParams p) {
         return;
     }
 
-    // ---- cluster mode: CTA result into wb[0] (thread d owns column d) --------
-    for (int g = 0; g < G; ++g) {
+    // ---- cluster mode: CTA result into wb[0]; element (g, d) is read from every
+    // warp's buffer and written back by the same thread ---------------------------
+    for (int e = tid; e < G * HD; e += DTHREADS) {
+        const int g = e / HD, d = e % HD;
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < DW; ++w) M = fmaxf(M, sm.cm[w][g]);
@@ -467,13 +488,15 @@ int launch_decode(const char* who, const DecParams& p, int n_req, int grid_x,
     cfg.blockDim = dim3(DTHREADS, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = grid_x;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
     cudaError_t e = (p.G > 8)
         ? cudaLaunchKernelEx(&cfg, decode_kernel<true, true>, p)
         : cudaLaunchKernelEx(&cfg, decode_kernel<false, true>, p);

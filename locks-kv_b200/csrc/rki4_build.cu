@@ -297,6 +297,7 @@ extern "C" int locks_rki4_build(
     p.nb_cache = num_blocks_cache; p.n_kv = n_kv;
     rki4_build_kernel<<<(unsigned)((n_jobs + BW - 1) / BW), BW * 32, 0,
                         static_cast<cudaStream_t>(stream)>>>(p);
+    pdl_break();
     return check_launch("locks_rki4_build");
 }
 

@@ -163,6 +163,9 @@ rki4_score_kernel(const ScoreParams p) {
     const int32_t* bt = p.block_table + (int64_t)r * p.bt_stride;
     const uint8_t* recs = p.records + (int64_t)kh * REC_BYTES;
     const int64_t blk_stride = (int64_t)p.n_kv * REC_BYTES;
+    // summaries are streamed once per step: do not let them push the scores,
+    // page tables and K/V pages of the following kernels out of L2
+    const uint64_t stream_policy = l2_policy_evict_first();
     auto issue = [&](int chunk, int blk) {
         const int stage = chunk % STAGES;
         const int n = min(CHUNK, pg1 - pg0 - chunk * CHUNK);
@@ -172,8 +175,8 @@ rki4_score_kernel(const ScoreParams p) {
         __syncwarp();
         if (lane < n) {
             blk = min(max(blk, 0), p.num_blocks - 1);
-            bulk_g2s(&sm.rec[warp][stage][lane][0], recs + blk * blk_stride,
-                     REC_BYTES, &sm.full[warp][stage]);
+            bulk_g2s_hint(&sm.rec[warp][stage][lane][0], recs + blk * blk_stride,
+                          REC_BYTES, &sm.full[warp][stage], stream_policy);
         }
     };
     auto bt_of = [&](int chunk) -> int {
@@ -181,6 +184,10 @@ rki4_score_kernel(const ScoreParams p) {
         return (lane < CHUNK && pg < pg1) ? bt[pg] : 0;
     };
     for (int k = 0; k < STAGES && k < nc; ++k) issue(k, bt_of(k));
+
+    // Everything above touches only per-step constants (block table, page
+    // counts, summaries); q and the score buffers belong to the kernels before.
+    pdl_wait();
 
     // ---- per-head int8 round trip of q (overlaps the first copies) ----------
     for (int g = warp; g < G; g += NWARP) {
@@ -403,6 +410,7 @@ rki4_score_kernel(const ScoreParams p) {
         if (k + STAGES < nc) issue(k + STAGES, next_blk);
     }
 
+    pdl_trigger();
     if (p.hmax != nullptr && tig == 0) {
 #pragma unroll
         for (int h = 0; h < NR; ++h) {
@@ -475,13 +483,21 @@ extern "C" int locks_rki4_score_bt(
     p.hmax = hmax;
     p.n_kv = n_kv; p.G = G; p.max_pages = max_pages; p.bt_width = bt_width;
     p.num_blocks = num_blocks; p.scale = scale; p.status = status;
-    dim3 grid(Z, n_kv, n_req);
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (G <= 4)
-        rki4_score_kernel<4><<<grid, NTHREADS, smem, s>>>(p);
-    else if (G <= 8)
-        rki4_score_kernel<8><<<grid, NTHREADS, smem, s>>>(p);
-    else
-        rki4_score_kernel<16><<<grid, NTHREADS, smem, s>>>(p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(Z, n_kv, n_req);
+    cfg.blockDim = dim3(NTHREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (pdl_enabled() && !pdl_take_break()) ? 1 : 0;
+    cudaError_t e = (G <= 4)   ? cudaLaunchKernelEx(&cfg, rki4_score_kernel<4>, p)
+                    : (G <= 8) ? cudaLaunchKernelEx(&cfg, rki4_score_kernel<8>, p)
+                               : cudaLaunchKernelEx(&cfg, rki4_score_kernel<16>, p);
+    if (e != cudaSuccess)
+        return fail(LOCKS_ERR_LAUNCH, "locks_rki4_score_bt: %s",
+                    cudaGetErrorString(e));
     return check_launch("locks_rki4_score_bt");
 }

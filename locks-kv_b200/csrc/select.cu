@@ -153,7 +153,7 @@ __device__ __forceinline__ void combine_nrm_groups(
     const float* __restrict__ sh, float* __restrict__ score, uint32_t* keys,
     const float* hm_sh, int G, int MP, int s0, int n_loc, int n_comb,
     int g_beg, int g_end, int lane) {
-    constexpr int CB = (16 / GT > 4) ? 4 : (GT >= 16 ? 1 : 16 / GT);   // <= 16 loads in flight
+    constexpr int CB = (32 / GT > 8) ? 8 : (GT >= 16 ? 1 : 32 / GT);   // <= 32 loads in flight
     float hm[GT];
 #pragma unroll
     for (int g = 0; g < GT; ++g) hm[g] = hm_sh[min(g, G - 1)];
@@ -228,6 +228,7 @@ topb_kernel(const SelParams p) {
     cg::cluster_group cluster = cg::this_cluster();
 
     SEL_TS(0);
+    pdl_trigger();               // the decode may be scheduled; it waits for us
     const int c = blockIdx.x, CL = gridDim.x;     // rank / size of the cluster
     const int kh = blockIdx.y, r = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -253,6 +254,8 @@ topb_kernel(const SelParams p) {
     const int n_grp = (n_loc + 31) >> 5;
     const int gpw = (n_grp + SEL_WARPS - 1) / SEL_WARPS;
     const int g_beg = min(warp * gpw, n_grp), g_end = min(g_beg + gpw, n_grp);
+
+    pdl_wait();                  // score_h / hmax / score come from the scorer
 
     // ---------------- 1. GQA combine -> score[slice], keys[slice] --------------
     if (p.combine == LOCKS_COMBINE_NRM && n_comb > 0) {
@@ -394,14 +397,20 @@ topb_kernel(const SelParams p) {
     }
 
     // ---------------- 3. keep flags + ascending compaction --------------------
-    // ties in my groups
-    int w_eq = 0;
-    if (!keep_all)
-        for (int grp = g_beg; grp < g_end; ++grp) {
-            const int j = grp * 32 + lane;
-            const bool eq = j >= q0 && j < q1 && keys[j] == tau_key;
-            w_eq += __popc(__ballot_sync(0xffffffffu, eq));
-        }
+    // one pass over my groups: pages kept outright (outside the selectable
+    // range, or above the threshold) and pages tied with the threshold
+    const uint32_t lt_mask = (1u << lane) - 1u;
+    int w_eq = 0, w_sure = 0;
+    for (int grp = g_beg; grp < g_end; ++grp) {
+        const int j = grp * 32 + lane, i = s0 + j;
+        const bool in = j < n_loc && i < npg;
+        const bool selr = !keep_all && j >= q0 && j < q1;
+        const uint32_t key = (j < n_loc) ? keys[j] : 0u;
+        const bool eq = selr && key == tau_key;
+        const bool sure = in && (!selr || key > tau_key);
+        w_eq += __popc(__ballot_sync(0xffffffffu, eq));
+        w_sure += __popc(__ballot_sync(0xffffffffu, sure));
+    }
     if (lane == 0) sm.wtot[warp] = w_eq;
     __syncthreads();
     scan_warp_totals(sm.wtot);
@@ -415,25 +424,8 @@ topb_kernel(const SelParams p) {
             eq_base += *cluster.map_shared_rank(&sm.x_eq, cc);
     }
     SEL_TS(15);
-    // kept pages in my groups (keep masks are recomputed when writing)
-    const uint32_t lt_mask = (1u << lane) - 1u;
-    int w_kept = 0;
-    {
-        int eqr = eq_base;
-        for (int grp = g_beg; grp < g_end; ++grp) {
-            const int j = grp * 32 + lane, i = s0 + j;
-            const bool in = j < n_loc && i < npg;
-            const bool selr = !keep_all && j >= q0 && j < q1;
-            const uint32_t key = (j < n_loc) ? keys[j] : 0u;
-            const bool eq = selr && key == tau_key;
-            const uint32_t eqb = __ballot_sync(0xffffffffu, eq);
-            bool keep = in;
-            if (selr) keep = eq ? (eqr + __popc(eqb & lt_mask) + 1 <= quota)
-                                : (key > tau_key);
-            eqr += __popc(eqb);
-            w_kept += __popc(__ballot_sync(0xffffffffu, keep));
-        }
-    }
+    // ties are kept in ascending page order until `quota` of them are taken
+    const int w_kept = w_sure + min(max(quota - eq_base, 0), w_eq);
     if (lane == 0) sm.wtot2[warp] = w_kept;
     __syncthreads();
     scan_warp_totals(sm.wtot2);
@@ -503,6 +495,7 @@ extern "C" int locks_derive_page_params(
                     static_cast<cudaStream_t>(stream)>>>(
         seq_lens, n_req, page, window_pages, sink_pages, budget_pages, budget,
         n_pages, n_sel_hi, b_fix);
+    pdl_break();
     return check_launch("locks_derive_page_params");
 }
 
@@ -552,13 +545,15 @@ extern "C" int locks_topb_select(
     cfg.blockDim = dim3(SEL_THREADS, 1, 1);
     cfg.dynamicSmemBytes = dyn_smem;
     cfg.stream = static_cast<cudaStream_t>(stream);
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = cl;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, topb_kernel, p);
     if (e != cudaSuccess)
         return fail(LOCKS_ERR_LAUNCH, "locks_topb_select: %s",

@@ -21,6 +21,7 @@ _P, _I, _L, _F, _D = c_void_p, c_int, c_int64, c_float, c_double
 # name -> (argtypes, kernel launches per call)
 _SIGNATURES = {
     "locks_version": ([], 0),
+    "locks_set_pdl": ([_I], 0),
     "locks_record_bytes": ([_I, _I], 0),
     "locks_rki4_build": ([_P, _L, _L, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I,
                           _I, _I, _P], 1),
