@@ -39,6 +39,7 @@ import torch  # noqa: E402
 
 REC_ALGO_BYTES = 818           # summary bytes per (page, kv-head) the scorer needs
 PAGE_KV_BYTES = 16 * 128 * 2 * 2   # K + V bytes of one attended (page, kv-head)
+SCORE_TRAFFIC_PER_UNIT = (54556416 + 57344) / 65480.0   # measured DRAM bytes per unit
 
 
 def workload(name: str, ctx: int | None):
@@ -422,7 +423,11 @@ def run_gpu(args, sh, seq_len):
         "gpu_launches": hp.launches_per_step * args.steps,
         "roofline": {"kernel": "rki4_score_kernel", "bound": "hbm",
                      "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": None,
+                     "frac": achieved / peak,
+                     # dram__bytes_read+write of one launch, ncu --set full on the
+                     # same shape (profiles/c1_score_select_decode_ncu_full.md):
+                     # 833.2 B per (page, kv-head), scaled by the units of a launch
+                     "traffic": SCORE_TRAFFIC_PER_UNIT * sh.n_kv * nsh,
                      "peak_source": peak_src,
                      "bytes_per_launch": score_launch_bytes,
                      "us_per_launch": ms_score * 1e3},
