@@ -197,7 +197,7 @@ def run_reference(args, sh, seq_len):
 # --------------------------------------------------------------------------- #
 # GPU arm                                                                      #
 # --------------------------------------------------------------------------- #
-def make_device_case(sh, seq_len, dev, seed):
+def make_device_case(sh, seq_len, dev, seed, return_needles=False):
     """Paged caches for ONE sequence of `seq_len` tokens, generated on the
     device layer by layer (the full-size cache does not fit a CPU round trip)."""
     from locks import synth
@@ -207,11 +207,12 @@ def make_device_case(sh, seq_len, dev, seed):
     g = torch.Generator().manual_seed(seed * 7 + 3)
     perm = torch.randperm(NB, generator=g)
     bt = perm[:npg].to(torch.int32)[None].contiguous().to(dev)
-    caches, qs = [], []
+    caches, qs, needles = [], [], []
     blocks = bt[0].long()
     pad = npg * page - seq_len
     for l in range(sh.n_layers):
-        K, V, q, _ = synth.gqa_tokens(seed, l, 0, seq_len, sh, dev)
+        K, V, q, nd = synth.gqa_tokens(seed, l, 0, seq_len, sh, dev)
+        needles.append(nd)
         kvc = torch.zeros(NB, 2, page, sh.n_kv, sh.d, device=dev,
                           dtype=torch.bfloat16)
         if pad:
@@ -223,6 +224,8 @@ def make_device_case(sh, seq_len, dev, seed):
         caches.append(kvc)
         qs.append(q[None])
     sl = torch.tensor([seq_len], dtype=torch.int32, device=dev)
+    if return_needles:
+        return caches, torch.stack(qs), bt, sl, needles
     return caches, torch.stack(qs), bt, sl
 
 
