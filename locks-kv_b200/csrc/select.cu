@@ -66,6 +66,7 @@ struct SelParams {
     int32_t* page_table;
     int32_t* page_cnt;
     int n_kv, G, max_pages, sink;
+    int owner_mode;     // keys of a whole row fit one CTA: helpers only combine
 };
 
 #ifdef LOCKS_SEL_TIMING
@@ -229,7 +230,7 @@ topb_kernel(const SelParams p) {
 
     SEL_TS(0);
     pdl_trigger();               // the decode may be scheduled; it waits for us
-    const int c = blockIdx.x, CL = gridDim.x;     // rank / size of the cluster
+    const int c_phys = blockIdx.x, CL_phys = gridDim.x;   // rank / size of cluster
     const int kh = blockIdx.y, r = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int MP = p.max_pages, G = p.G;
@@ -244,11 +245,25 @@ topb_kernel(const SelParams p) {
     const int64_t row = (int64_t)r * p.n_kv + kh;
     float* score = p.score + row * MP;
     const int n_comb = min(max(nsh, 0), MP);        // pages with a score
-
-    // contiguous page slice of this CTA, a multiple of 32 pages long
     const int span = max(npg, n_comb);
-    const int per_cta = (((span + CL - 1) / CL) + 31) & ~31;
-    const int s0 = min(c * per_cta, span), s1 = min(s0 + per_cta, span);
+
+    // Owner mode (the keys of the whole row fit one CTA's shared memory): every
+    // CTA of the cluster combines a slice of the scores and pushes the keys into
+    // CTA 0 through distributed shared memory; CTA 0 alone selects, the helpers
+    // write the -1 padding that no selection can reach and leave.
+    // Distributed mode (long contexts): every CTA keeps and selects its slice.
+    const bool owner = p.owner_mode && CL_phys > 1;
+    // slice whose scores this CTA combines
+    const int cper = (((span + CL_phys - 1) / CL_phys) + 31) & ~31;
+    const int cs0 = min(c_phys * cper, span), cs1 = min(cs0 + cper, span);
+    const int cn_loc = cs1 - cs0;
+    const int cn_grp = (cn_loc + 31) >> 5;
+    const int cgpw = (cn_grp + SEL_WARPS - 1) / SEL_WARPS;
+    const int cg_beg = min(warp * cgpw, cn_grp), cg_end = min(cg_beg + cgpw, cn_grp);
+    uint32_t* kdst = owner ? cluster.map_shared_rank(keys, 0) + cs0 : keys;
+    // slice this CTA selects from
+    const int c = owner ? 0 : c_phys, CL = owner ? 1 : CL_phys;
+    const int s0 = owner ? 0 : cs0, s1 = owner ? span : cs1;
     const int n_loc = s1 - s0;
     // warp w owns groups [w*gpw, (w+1)*gpw) of 32 consecutive pages
     const int n_grp = (n_loc + 31) >> 5;
@@ -258,27 +273,30 @@ topb_kernel(const SelParams p) {
     pdl_wait();                  // score_h / hmax / score come from the scorer
 
     // ---------------- 1. GQA combine -> score[slice], keys[slice] --------------
+    // remote shared memory may only be touched once every CTA of the cluster
+    // runs: the nrm branch has a cluster barrier of its own, the others get one
+    if (owner && !(p.combine == LOCKS_COMBINE_NRM && n_comb > 0)) cluster.sync();
     if (p.combine == LOCKS_COMBINE_NRM && n_comb > 0) {
         const float* sh = p.score_h + row * (int64_t)G * MP;
         if (p.hmax != nullptr) {
             if (tid < G) sm.hm_sh[tid] = key2f(p.hmax[row * G + tid]);
-            if (CL > 1) cluster.sync();             // everyone has read the keys
+            if (CL_phys > 1) cluster.sync();        // everyone has read the keys
             else __syncthreads();
-            if (c == 0 && tid < G) p.hmax[row * G + tid] = 0u;
+            if (c_phys == 0 && tid < G) p.hmax[row * G + tid] = 0u;
         } else {
             LOCKS_DISPATCH_GT(G, (sweep_max_groups<GT>(
-                sh, sm.wmax[warp], G, MP, s0, n_loc, n_comb, g_beg, g_end, lane)));
+                sh, sm.wmax[warp], G, MP, cs0, cn_loc, n_comb, cg_beg, cg_end, lane)));
             __syncthreads();
             if (tid < G) {
                 float m = -INFINITY;
                 for (int w = 0; w < SEL_WARPS; ++w) m = fmaxf(m, sm.wmax[w][tid]);
                 sm.xmax[tid] = m;
             }
-            if (CL > 1) {
+            if (CL_phys > 1) {
                 cluster.sync();
                 if (tid < G) {
                     float m = -INFINITY;
-                    for (int cc = 0; cc < CL; ++cc)
+                    for (int cc = 0; cc < CL_phys; ++cc)
                         m = fmaxf(m, *cluster.map_shared_rank(&sm.xmax[tid], cc));
                     sm.hm_sh[tid] = m;
                 }
@@ -290,14 +308,14 @@ topb_kernel(const SelParams p) {
         }
         SEL_TS(20);
         LOCKS_DISPATCH_GT(G, (combine_nrm_groups<GT>(
-            sh, score, keys, sm.hm_sh, G, MP, s0, n_loc, n_comb, g_beg, g_end,
+            sh, score, kdst, sm.hm_sh, G, MP, cs0, cn_loc, n_comb, cg_beg, cg_end,
             lane)));
         SEL_TS(21);
     } else if (p.combine == LOCKS_COMBINE_MAX && n_comb > 0) {
         const float* sh = p.score_h + row * (int64_t)G * MP;
-        for (int grp = g_beg; grp < g_end; ++grp) {
-            const int j = grp * 32 + lane, i = s0 + j;
-            if (j < n_loc) {
+        for (int grp = cg_beg; grp < cg_end; ++grp) {
+            const int j = grp * 32 + lane, i = cs0 + j;
+            if (j < cn_loc) {
                 float m = 0.f;
                 if (i < n_comb) {
                     m = -INFINITY;
@@ -305,16 +323,30 @@ topb_kernel(const SelParams p) {
                         m = fmaxf(m, sh[(int64_t)g * MP + i]);
                     score[i] = m;
                 }
-                keys[j] = f2key(m);
+                kdst[j] = f2key(m);
             }
         }
     } else {
-        for (int grp = g_beg; grp < g_end; ++grp) {
+        for (int grp = cg_beg; grp < cg_end; ++grp) {
             const int j = grp * 32 + lane;
-            if (j < n_loc) keys[j] = f2key(score[s0 + j]);
+            if (j < cn_loc) kdst[j] = f2key(score[cs0 + j]);
         }
     }
-    __syncthreads();
+    if (owner) {
+        cluster.sync();                  // all keys have landed in CTA 0
+        if (c_phys != 0) {
+            // entries no selection can reach: beyond the forced pages + budget
+            const int cnt_max = keep_all ? npg
+                                         : min(npg, (npg - L) + min(max(b, 0), L));
+            int32_t* tabp = p.page_table + row * MP;
+            for (int i = cnt_max + (c_phys - 1) * SEL_THREADS + tid; i < MP;
+                 i += (CL_phys - 1) * SEL_THREADS)
+                tabp[i] = -1;
+            return;
+        }
+    } else {
+        __syncthreads();
+    }
     SEL_TS(1);
 
     // selectable part of the slice, in local indices
@@ -464,8 +496,13 @@ topb_kernel(const SelParams p) {
         }
     }
     // -1 padding of [cnt, MP), shared by the cluster
-    for (int i = cnt + c * SEL_THREADS + tid; i < MP; i += CL * SEL_THREADS)
-        tab[i] = -1;
+    {
+        const int pad_end = owner
+            ? (keep_all ? npg : min(npg, (npg - L) + min(max(b, 0), L)))
+            : MP;
+        for (int i = cnt + c * SEL_THREADS + tid; i < pad_end; i += CL * SEL_THREADS)
+            tab[i] = -1;
+    }
     if (c == 0 && tid == 0) p.page_cnt[row] = cnt;
     SEL_TS(18);
     if (CL > 1) cluster.sync();  // keep shared memory alive for remote readers
@@ -522,14 +559,25 @@ extern "C" int locks_topb_select(
     p.n_pages = n_pages; p.n_sel_hi = n_sel_hi; p.b_fix = b_fix;
     p.page_table = page_table; p.page_cnt = page_cnt;
     p.n_kv = n_kv; p.G = G; p.max_pages = max_pages; p.sink = sink_pages;
-    // cluster size: the smallest power of two whose CTAs can hold the keys of
-    // one (request, kv-head) in shared memory (one CTA up to 16384 pages)
+    // Short rows (keys fit one CTA): owner mode, up to 4 CTAs share the combine.
+    // Long rows: the smallest power-of-two cluster whose CTAs hold the keys.
     int cl = 1;
-    while (cl < MAX_CL && (max_pages + cl - 1) / cl > KEYS_PER_CTA) cl *= 2;
-    LOCKS_REQUIRE((max_pages + cl - 1) / cl <= KEYS_PER_CTA, LOCKS_ERR_SIZE,
+    const bool owner_mode = max_pages <= KEYS_PER_CTA;
+    if (owner_mode) {
+        const int want = sm_count() / max(1, n_kv * n_req);
+        const int useful = (max_pages + 2047) / 2048;
+        while (cl * 2 <= want && cl * 2 <= useful && cl < 4) cl *= 2;
+    } else {
+        while (cl < MAX_CL && (max_pages + cl - 1) / cl > KEYS_PER_CTA) cl *= 2;
+    }
+    LOCKS_REQUIRE(owner_mode || (max_pages + cl - 1) / cl <= KEYS_PER_CTA,
+                  LOCKS_ERR_SIZE,
                   "locks_topb_select: max_pages %d beyond the supported %d",
                   max_pages, MAX_CL * KEYS_PER_CTA);
-    const int per_cta = ((((max_pages + cl - 1) / cl) + 31) & ~31) + 32;
+    p.owner_mode = owner_mode ? 1 : 0;
+    const int per_cta = owner_mode
+        ? ((max_pages + 31) & ~31) + 32 * 4
+        : ((((max_pages + cl - 1) / cl) + 31) & ~31) + 32;
     const int dyn_smem = per_cta * 4;
     static bool attr_done[64] = {false};
     int dev = 0;
