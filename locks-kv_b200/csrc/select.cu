@@ -134,9 +134,15 @@ __device__ __forceinline__ void find_digit(SelSmem& sm, const int* h, int nb,
     }
     if (lane == 31) sm.wtot[warp] = inc;
     __syncthreads();
-    scan_warp_totals(sm.wtot);
-    __syncthreads();
-    const int base = above0 + (warp ? sm.wtot[warp - 1] : 0);
+    // every warp scans the 32 warp totals itself (no second barrier)
+    const int wv = sm.wtot[lane];
+    int winc = wv;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, winc, o);
+        if (lane >= o) winc += t;
+    }
+    const int base = above0 + __shfl_sync(0xffffffffu, winc - wv, warp);
     const int above = base + inc - (ca + cb);
     if (above < k && k <= above + ca + cb) {
         if (k <= above + ca) { sm.sh_i0 = hi_bin; sm.sh_i1 = k - above; }
@@ -270,6 +276,7 @@ topb_kernel(const SelParams p) {
     const int gpw = (n_grp + SEL_WARPS - 1) / SEL_WARPS;
     const int g_beg = min(warp * gpw, n_grp), g_end = min(g_beg + gpw, n_grp);
 
+    for (int i = tid; i < NBINS; i += SEL_THREADS) sm.hist[i] = 0;   // pass-0 bins
     pdl_wait();                  // score_h / hmax / score come from the scorer
 
     // ---------------- 1. GQA combine -> score[slice], keys[slice] --------------
@@ -367,18 +374,28 @@ topb_kernel(const SelParams p) {
             const int nb = 1 << bits;
             shift -= bits;
             const uint32_t dmask = (uint32_t)nb - 1u;
-            for (int i = tid; i < nb; i += SEL_THREADS) { sm.hist[i] = 0; sm.tot[i] = 0; }
-            __syncthreads();
-            for (int j = q0 + tid; j < q1; j += SEL_THREADS) {
-                const uint32_t key = keys[j];
-                if ((key & mask) == prefix)
-                    atomicAdd(&sm.hist[(key >> shift) & dmask], 1);
-            }
-            SEL_TS(2 + 4 * pass);
             if (CL == 1) {
+                // two histogram buffers: this pass counts into one (zeroed
+                // before) while clearing the other for the next pass
+                int* h = (pass & 1) ? sm.tot : sm.hist;
+                int* hn = (pass & 1) ? sm.hist : sm.tot;
+                for (int j = q0 + tid; j < q1; j += SEL_THREADS) {
+                    const uint32_t key = keys[j];
+                    if ((key & mask) == prefix)
+                        atomicAdd(&h[(key >> shift) & dmask], 1);
+                }
+                for (int i = tid; i < NBINS; i += SEL_THREADS) hn[i] = 0;
+                SEL_TS(2 + 4 * pass);
                 __syncthreads();
-                find_digit(sm, sm.hist, nb, 0, k);
+                find_digit(sm, h, nb, 0, k);
             } else {
+                for (int i = tid; i < nb; i += SEL_THREADS) { sm.hist[i] = 0; sm.tot[i] = 0; }
+                __syncthreads();
+                for (int j = q0 + tid; j < q1; j += SEL_THREADS) {
+                    const uint32_t key = keys[j];
+                    if ((key & mask) == prefix)
+                        atomicAdd(&sm.hist[(key >> shift) & dmask], 1);
+                }
                 cluster.sync();             // all slices' histograms are complete
                 // reduce-scatter: CTA c sums bins [c*bs, (c+1)*bs) of every CTA
                 const int bs = nb / CL;
@@ -421,7 +438,6 @@ topb_kernel(const SelParams p) {
             prefix |= (uint32_t)sm.sh_i0 << shift;
             k = sm.sh_i1;
             mask |= dmask << shift;
-            __syncthreads();
             SEL_TS(5 + 4 * pass);
         }
         tau_key = prefix;
