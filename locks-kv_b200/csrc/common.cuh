@@ -140,7 +140,7 @@ __device__ __forceinline__ void mma_s8u8_k32(int (&d)[4], uint32_t a0,
                                              uint32_t a1, uint32_t a2,
                                              uint32_t a3, uint32_t b0,
                                              uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 "
         "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
@@ -151,7 +151,7 @@ __device__ __forceinline__ void mma_s8s8_k32(int (&d)[4], uint32_t a0,
                                              uint32_t a1, uint32_t a2,
                                              uint32_t a3, uint32_t b0,
                                              uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 "
         "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
@@ -162,7 +162,7 @@ __device__ __forceinline__ void mma_bf16_k16(float (&d)[4], uint32_t a0,
                                              uint32_t a1, uint32_t a2,
                                              uint32_t a3, uint32_t b0,
                                              uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
         "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -186,5 +186,34 @@ __device__ __forceinline__ float bf16_bits_to_f32(uint32_t b16) {
     return __uint_as_float(b16 << 16);
 }
 #endif  // __CUDACC__
+
+
+// ---- optional per-CTA wall-clock marks (debug builds only) -----------------------
+#ifdef LOCKS_TIMELINE
+#define TL_DECL(name) __device__ unsigned long long name[3][1024];
+#define TL_MARK(name, k)                                                        \
+    do {                                                                        \
+        if (threadIdx.x == 0) {                                                 \
+            const unsigned lin_ = blockIdx.x + gridDim.x * (blockIdx.y +        \
+                                  gridDim.y * blockIdx.z);                      \
+            if (lin_ < 1024) {                                                  \
+                unsigned long long t_;                                          \
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));          \
+                name[k][lin_] = t_;                                             \
+            }                                                                   \
+        }                                                                       \
+    } while (0)
+#define TL_GETTER(fn, name)                                                     \
+    extern "C" int fn(unsigned long long* out) {                                \
+        int e = (int)cudaMemcpyFromSymbol(out, name, sizeof(name));             \
+        static unsigned long long z_[3 * 1024];                                 \
+        cudaMemcpyToSymbol(name, z_, sizeof(name));                             \
+        return e;                                                               \
+    }
+#else
+#define TL_DECL(name)
+#define TL_MARK(name, k)
+#define TL_GETTER(fn, name)
+#endif
 
 }  // namespace locks

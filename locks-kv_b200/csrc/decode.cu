@@ -26,6 +26,19 @@ namespace cg = cooperative_groups;
 namespace locks {
 namespace {
 
+TL_DECL(g_dec_tl)
+#ifdef LOCKS_DEC_TIMING
+__device__ long long g_dec_ts[16];
+#define DEC_TS(i)                                                             \
+    do {                                                                      \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 &&          \
+            threadIdx.x == 0)                                                 \
+            g_dec_ts[i] = clock64();                                          \
+    } while (0)
+#else
+#define DEC_TS(i)
+#endif
+
 constexpr int DW = 8;                 // warps per CTA
 constexpr int DTHREADS = DW * 32;
 constexpr int DSTAGES = 2;
@@ -108,8 +121,12 @@ decode_kernel(const DecParams p) {
     const int gid = lane >> 2, tig = lane & 3;
     const int G = p.G;
     const int64_t row = (int64_t)r * p.n_kv + kh;
+    DEC_TS(0);
+    TL_MARK(g_dec_tl, 0);
     pdl_trigger();            // the next layer's scorer may start prefetching
     pdl_wait();               // page tables / counts come from the selector
+    DEC_TS(1);
+    TL_MARK(g_dec_tl, 1);
     const int seq_len = p.seq_lens[r];
 
     const int cnt = p.page_cnt ? p.page_cnt[row]
@@ -159,7 +176,9 @@ decode_kernel(const DecParams p) {
                    nv[it % DSTAGES]);
     };
     load_window(0);
+    DEC_TS(2);
     for (int it = 0; it < DSTAGES && it < n_mine; ++it) issue_it(it);
+    DEC_TS(3);
 
     // ---- Q fragments (A operand), rows gid and gid+8 -------------------------
     uint32_t qa[8][4];
@@ -287,7 +306,8 @@ decode_kernel(const DecParams p) {
         }
     }
 
-    // ---- combine the four warps ------------------------------------------------
+    DEC_TS(4);
+    // ---- combine the warps of the CTA --------------------------------------------
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
     if (G_HI) {
@@ -352,7 +372,9 @@ decode_kernel(const DecParams p) {
         if (d == 0) { sm.cta_m[g] = M; sm.cta_l[g] = Lsum; }
     }
     cg::cluster_group cluster = cg::this_cluster();
+    DEC_TS(5);
     cluster.sync();                               // every CTA's result is visible
+    DEC_TS(6);
     {
         const int CL = (int)gridDim.x;
         const int n_el = G * HD;
@@ -378,7 +400,10 @@ decode_kernel(const DecParams p) {
                 __float2bfloat16_rn(val);
         }
     }
+    DEC_TS(7);
     cluster.sync();                  // keep shared memory alive for remote readers
+    DEC_TS(8);
+    TL_MARK(g_dec_tl, 2);
 }
 
 struct MergeParams {
@@ -523,6 +548,13 @@ int check_kv(const char* who, const void* q, const void* k, const void* v,
 }  // namespace locks
 
 using namespace locks;
+
+TL_GETTER(locks_debug_dec_tl, locks::g_dec_tl)
+#ifdef LOCKS_DEC_TIMING
+extern "C" int locks_debug_dec_timing(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_dec_ts, sizeof(long long) * 16);
+}
+#endif
 
 extern "C" int locks_decode_split(
     const void* q, int64_t q_stride_req, const void* k_cache,

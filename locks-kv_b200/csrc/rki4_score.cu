@@ -73,7 +73,7 @@ __device__ __forceinline__ void mma_f16_k16(float (&d)[4], uint32_t a0,
                                             uint32_t a1, uint32_t a2,
                                             uint32_t a3, uint32_t b0,
                                             uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
         "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -129,6 +129,19 @@ __device__ __forceinline__ float quad_lse2(float t0, float t1, float t2,
     return mx + lg2_approx(sum);
 }
 
+TL_DECL(g_score_tl)
+#ifdef LOCKS_SCORE_TIMING
+__device__ long long g_score_ts[64];
+#define SC_TS(i)                                                              \
+    do {                                                                      \
+        if (blockIdx.x == 5 && blockIdx.y == 0 && blockIdx.z == 0 &&          \
+            threadIdx.x == 0 && (i) < 64)                                     \
+            g_score_ts[i] = clock64();                                        \
+    } while (0)
+#else
+#define SC_TS(i)
+#endif
+
 // GP = 4 : G <= 4, two pages per pass;  GP = 8 : G <= 8;  GP = 16 : G <= 16
 template <int GP>
 __global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM)
@@ -136,6 +149,8 @@ rki4_score_kernel(const ScoreParams p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     ScoreSmem& sm = *reinterpret_cast<ScoreSmem*>(smem_raw);
 
+    SC_TS(0);
+    TL_MARK(g_score_tl, 0);
     const int z = blockIdx.x, Z = gridDim.x;
     const int kh = blockIdx.y, r = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -184,10 +199,13 @@ rki4_score_kernel(const ScoreParams p) {
         return (lane < CHUNK && pg < pg1) ? bt[pg] : 0;
     };
     for (int k = 0; k < STAGES && k < nc; ++k) issue(k, bt_of(k));
+    SC_TS(1);
 
     // Everything above touches only per-step constants (block table, page
     // counts, summaries); q and the score buffers belong to the kernels before.
     pdl_wait();
+    SC_TS(2);
+    TL_MARK(g_score_tl, 1);
 
     // ---- per-head int8 round trip of q (overlaps the first copies) ----------
     for (int g = warp; g < G; g += NWARP) {
@@ -219,6 +237,7 @@ rki4_score_kernel(const ScoreParams p) {
         if (lane == 0) { sm.qs[g] = qs; sm.qsum[g] = sum; }
     }
     __syncthreads();
+    SC_TS(3);
 
     // ---- A fragments of q.  Row gid holds head gid % GP (the group is repeated
     // when it is shorter than 8 rows); rows 8..15 are used only for GP = 16. ----
@@ -262,7 +281,9 @@ rki4_score_kernel(const ScoreParams p) {
         const int n = min(CHUNK, pg1 - p0);
         // block-table entries of the chunk that will reuse this stage
         const int next_blk = (k + STAGES < nc) ? bt_of(k + STAGES) : 0;
+        SC_TS(4 + 2 * k);
         mbar_wait(&sm.full[warp][stage], (uint32_t)((k / STAGES) & 1), p.status);
+        SC_TS(5 + 2 * k);
         const uint8_t* crec = &sm.rec[warp][stage][0][0];
 
         // mu . q for the chunk's 8 pages: column (n) = page slot gid
@@ -283,7 +304,7 @@ rki4_score_kernel(const ScoreParams p) {
         if constexpr (GP == 4) {
             // ---- two pages per pass: rows 0-3 -> slot 2j, rows 4-7 -> 2j+1 ----
             const int sel = gid >> 2;
-#pragma unroll 2
+#pragma unroll 4
             for (int j = 0; j < CHUNK / 2; ++j) {
                 if (2 * j >= n) break;
                 const uint8_t* recA = crec + (2 * j) * REC_BYTES;
@@ -410,6 +431,8 @@ rki4_score_kernel(const ScoreParams p) {
         if (k + STAGES < nc) issue(k + STAGES, next_blk);
     }
 
+    SC_TS(30);
+    TL_MARK(g_score_tl, 2);
     pdl_trigger();
     if (p.hmax != nullptr && tig == 0) {
 #pragma unroll
@@ -424,6 +447,13 @@ rki4_score_kernel(const ScoreParams p) {
 
 }  // namespace
 }  // namespace locks
+
+TL_GETTER(locks_debug_score_tl, locks::g_score_tl)
+#ifdef LOCKS_SCORE_TIMING
+extern "C" int locks_debug_score_timing(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, locks::g_score_ts, sizeof(long long) * 64);
+}
+#endif
 
 extern "C" int locks_rki4_score_bt(
     const void* q, int64_t q_stride_req, const void* records_layer,

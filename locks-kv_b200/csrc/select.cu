@@ -69,6 +69,7 @@ struct SelParams {
     int owner_mode;     // keys of a whole row fit one CTA: helpers only combine
 };
 
+TL_DECL(g_sel_tl)
 #ifdef LOCKS_SEL_TIMING
 __device__ long long g_sel_ts[32];
 #define SEL_TS(i)                                                          \
@@ -235,6 +236,7 @@ topb_kernel(const SelParams p) {
     cg::cluster_group cluster = cg::this_cluster();
 
     SEL_TS(0);
+    TL_MARK(g_sel_tl, 0);
     pdl_trigger();               // the decode may be scheduled; it waits for us
     const int c_phys = blockIdx.x, CL_phys = gridDim.x;   // rank / size of cluster
     const int kh = blockIdx.y, r = blockIdx.z;
@@ -278,6 +280,8 @@ topb_kernel(const SelParams p) {
 
     for (int i = tid; i < NBINS; i += SEL_THREADS) sm.hist[i] = 0;   // pass-0 bins
     pdl_wait();                  // score_h / hmax / score come from the scorer
+    SEL_TS(22);
+    TL_MARK(g_sel_tl, 1);
 
     // ---------------- 1. GQA combine -> score[slice], keys[slice] --------------
     // remote shared memory may only be touched once every CTA of the cluster
@@ -523,11 +527,13 @@ topb_kernel(const SelParams p) {
     SEL_TS(18);
     if (CL > 1) cluster.sync();  // keep shared memory alive for remote readers
     SEL_TS(19);
+    TL_MARK(g_sel_tl, 2);
 }
 
 }  // namespace
 }  // namespace locks
 
+TL_GETTER(locks_debug_sel_tl, locks::g_sel_tl)
 #ifdef LOCKS_SEL_TIMING
 extern "C" int locks_debug_sel_timing(long long* out) {
     return (int)cudaMemcpyFromSymbol(out, locks::g_sel_ts, sizeof(long long) * 32);
