@@ -1,17 +1,21 @@
 // Sparse paged decode: split-K flash decode over the selected pages, the split
 // merge, the one-launch fused variant and the dense full-KV baseline.
 //
-// One kernel serves all three.  A CTA (4 warps) owns one (request, kv-head) and
+// One kernel serves all three.  A CTA (8 warps) owns one (request, kv-head) and
 // a contiguous run of page-table entries; its warps take entries round-robin
-// and each warp runs its own 2-stage shared-memory ring: 32 lanes issue 32 bulk
-// async copies (16 key rows + 16 value rows of 256 B, found through the page
-// table and the block table) that complete on the warp's mbarrier.  Rows past
-// seq_len are zero-filled instead of copied, so stale cache bytes cannot leak.
+// and each warp runs its own 2-stage shared-memory ring.  A page (16 key rows +
+// 16 value rows of 256 B, found through the page table and the block table) is
+// fetched with 16-byte cp.async copies, 16 per lane and one commit group per
+// page: a warp walks only a few pages, so what counts is how fast the first
+// copies are on their way, and 512 small bulk-copy requests per CTA queue up in
+// the copy engine far longer than the same bytes as coalesced LSU copies.
+// Rows past seq_len are zero-filled (source size 0), so stale cache bytes
+// cannot leak.
 //
 // Math per page, on warp-level tensor-core fragments whose 16 rows are the
 // query heads of the GQA group:  S = Q K^T (bf16, 16 m16n8k16 steps), online
 // softmax in fp32, O += P V with P split into two bf16 terms (32 steps), i.e.
-// P keeps 16 mantissa bits.  The four warps' (m, l, O) are combined through
+// P keeps 16 mantissa bits.  The warps' (m, l, O) are combined through
 // shared memory; the CTA then stores one split partial (split mode), or, in
 // fused mode, the CTAs of a thread-block cluster -- one cluster per (request,
 // kv-head), each CTA walking its share of the page list -- exchange their
@@ -55,11 +59,13 @@ static_assert(sizeof(WarpBuf) >= 16 * ACC_PITCH * 4, "combine buffer must fit");
 
 struct __align__(128) DecSmem {
     WarpBuf wb[DW];
-    uint64_t full[DW][DSTAGES];
     float cm[DW][16];
     float cl[DW][16];
-    float cta_m[16];               // CTA-level (m, l) for the cluster exchange
-    float cta_l[16];
+    // cluster exchange (fused mode): CTA c pushes its (m, l) to every CTA and
+    // the slice of its O that CTA d normalises into xacc[c] of CTA d
+    float xm[8][16];
+    float xl[8][16];
+    float xacc[16 * HD + 16];
 };
 
 struct DecParams {
@@ -83,6 +89,21 @@ struct DecParams {
     int* status;
 };
 
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src,
+                                           int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                 ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// One commit group per page: lane (h, c) = (lane >> 4, lane & 15) copies the
+// 16-byte chunk c of rows h, h + 2, ..., h + 14 of K and of V.
 __device__ __forceinline__ void issue_page(DecSmem& sm, const DecParams& p,
                                            int warp, int lane, int stage,
                                            int kh, int pt, int blk,
@@ -90,24 +111,22 @@ __device__ __forceinline__ void issue_page(DecSmem& sm, const DecParams& p,
     const int n_valid = (pt >= 0) ? min(max(seq_len - pt * PAGE_T, 0), PAGE_T) : 0;
     blk = max(blk, 0);
     n_valid_out = n_valid;
-    uint64_t* bar = &sm.full[warp][stage];
-    fence_proxy_async();
-    if (lane == 0) mbar_expect_tx(bar, (uint32_t)n_valid * 2u * (HD * 2));
-    __syncwarp();
-    const int t = lane & 15;
-    const bool is_v = lane >= 16;
-    uint8_t* dst = is_v ? &sm.wb[warp].v[stage][t][0] : &sm.wb[warp].k[stage][t][0];
-    if (t < n_valid) {
-        const __nv_bfloat16* base = is_v ? p.v_cache : p.k_cache;
-        const __nv_bfloat16* src = base + (int64_t)blk * p.stride_block +
-                                   (int64_t)t * p.stride_tok +
-                                   (int64_t)kh * p.stride_head;
-        bulk_g2s(dst, src, HD * 2, bar);
-    } else {
-        uint4* d4 = reinterpret_cast<uint4*>(dst);
+    const int c = lane & 15, h = lane >> 4;
+    const int64_t off = (int64_t)blk * p.stride_block + (int64_t)kh * p.stride_head +
+                        8 * c;
+    const __nv_bfloat16* ksrc = p.k_cache + off;
+    const __nv_bfloat16* vsrc = p.v_cache + off;
+    const uint32_t kdst = smem_u32(&sm.wb[warp].k[stage][0][16 * c]);
+    const uint32_t vdst = smem_u32(&sm.wb[warp].v[stage][0][16 * c]);
 #pragma unroll
-        for (int i = 0; i < (HD * 2) / 16; ++i) d4[i] = make_uint4(0, 0, 0, 0);
+    for (int i = 0; i < PAGE_T / 2; ++i) {
+        const int t = h + 2 * i;
+        const int nb = (t < n_valid) ? 16 : 0;        // 0: zero-fill, nothing read
+        const int64_t so = (int64_t)min(t, max(n_valid - 1, 0)) * p.stride_tok;
+        cp_async16(kdst + t * ROWB, ksrc + so, nb);
+        cp_async16(vdst + t * ROWB, vsrc + so, nb);
     }
+    cp_async_commit();
 }
 
 template <bool G_HI, bool CLUSTER>
@@ -124,47 +143,52 @@ decode_kernel(const DecParams p) {
     DEC_TS(0);
     TL_MARK(g_dec_tl, 0);
     pdl_trigger();            // the next layer's scorer may start prefetching
+    // remote shared memory may be written once every CTA of the cluster runs;
+    // this barrier costs nothing while the selector is still at work
+    if (CLUSTER) cg::this_cluster().sync();
+    const int seq_len = p.seq_lens[r];            // per-step constant
     pdl_wait();               // page tables / counts come from the selector
     DEC_TS(1);
     TL_MARK(g_dec_tl, 1);
-    const int seq_len = p.seq_lens[r];
 
-    const int cnt = p.page_cnt ? p.page_cnt[row]
-                               : (max(seq_len, 0) + PAGE_T - 1) / PAGE_T;
-    int j0, j1;
+    // Cluster mode deals the list out round-robin over all warps of the cluster
+    // (entry j -> CTA (j / DW) % CL, warp j % DW): which entries a warp reads
+    // does not depend on the page count, so the count, the first window of
+    // page-table entries and (one round trip later) their physical blocks are
+    // fetched together.  Split mode gives a CTA a contiguous run of entries.
+    int win_pt = -1, win_blk = 0;
+    const int stride = CLUSTER ? DW * (int)gridDim.x : DW;
     if (CLUSTER) {
-        // CTA `sp` of the cluster takes an even share of the list; an empty
-        // share still takes part in the cluster barriers below
-        const int per = (cnt + (int)gridDim.x - 1) / (int)gridDim.x;
-        j0 = min(sp * per, cnt);
-        j1 = min(j0 + per, cnt);
+        const int j = sp * DW + warp + lane * stride;
+        if (j < p.max_pages)
+            win_pt = p.page_table ? __ldcg(&p.page_table[row * p.max_pages + j]) : j;
+    }
+    const int cnt = p.page_cnt ? __ldcg(&p.page_cnt[row])
+                               : (max(seq_len, 0) + PAGE_T - 1) / PAGE_T;
+    if (CLUSTER)
+        win_blk = p.block_table[(int64_t)r * p.bt_stride + max(win_pt, 0)];
+    int first, jend;
+    if (CLUSTER) {
+        // an empty share still takes part in the cluster barrier below
+        first = sp * DW + warp;
+        jend = cnt;
     } else {
         const int pps = max((cnt + p.split - 1) / p.split, p.pps_min);
-        j0 = sp * pps;
+        const int j0 = sp * pps;
         if (j0 >= cnt) return;                    // inactive split: no store
-        j1 = min(j0 + pps, cnt);
+        first = j0 + warp;
+        jend = min(j0 + pps, cnt);
     }
-
-    if (tid == 0) {
-        for (int w = 0; w < DW; ++w)
-            for (int s = 0; s < DSTAGES; ++s) mbar_init(&sm.full[w][s], 1);
-        mbar_fence_init();
-    }
-    __syncthreads();
-
-    // pages of this warp: j0 + warp, j0 + warp + DW, ...
-    const int first = j0 + warp;
-    const int n_mine = (first < j1) ? (j1 - first + DW - 1) / DW : 0;
+    const int n_mine = (first < jend) ? (jend - first + stride - 1) / stride : 0;
     int nv[DSTAGES] = {0, 0};
     // Page-table entry and physical block of the warp's pages, 32 at a time
     // (lane i holds entry i of the window), so that the two dependent index
     // loads are paid once per window instead of once per page.
-    int win_pt = -1, win_blk = 0;
     auto load_window = [&](int it0) {
         const int it = it0 + lane;
         win_pt = -1; win_blk = 0;
         if (it < n_mine) {
-            const int j = first + it * DW;
+            const int j = first + it * stride;
             win_pt = p.page_table ? p.page_table[row * p.max_pages + j] : j;
             win_blk = p.block_table[(int64_t)r * p.bt_stride + max(win_pt, 0)];
         }
@@ -175,7 +199,7 @@ decode_kernel(const DecParams p) {
         issue_page(sm, p, warp, lane, it % DSTAGES, kh, pt, blk, seq_len,
                    nv[it % DSTAGES]);
     };
-    load_window(0);
+    if (!CLUSTER) load_window(0);
     DEC_TS(2);
     for (int it = 0; it < DSTAGES && it < n_mine; ++it) issue_it(it);
     DEC_TS(3);
@@ -206,8 +230,9 @@ decode_kernel(const DecParams p) {
 
     for (int it = 0; it < n_mine; ++it) {
         const int stage = it % DSTAGES;
-        mbar_wait(&sm.full[warp][stage], (uint32_t)((it / DSTAGES) & 1), p.status);
-        __syncwarp();
+        // groups complete in order; at most the next page's is younger
+        if (it + 1 < n_mine) cp_async_wait<1>(); else cp_async_wait<0>();
+        __syncwarp();                               // every lane's copies landed
         const int n_valid = nv[stage];
         if (n_valid > 0) {
             const uint32_t kbase = smem_u32(&sm.wb[warp].k[stage][0][0]);
@@ -323,8 +348,9 @@ decode_kernel(const DecParams p) {
     }
 #pragma unroll
     for (int nt = 0; nt < 16; ++nt) {
-        *reinterpret_cast<float2*>(&wacc[gid * ACC_PITCH + 8 * nt + 2 * tig]) =
-            make_float2(acc[nt][0], acc[nt][1]);
+        if (gid < G)
+            *reinterpret_cast<float2*>(&wacc[gid * ACC_PITCH + 8 * nt + 2 * tig]) =
+                make_float2(acc[nt][0], acc[nt][1]);
         if (G_HI)
             *reinterpret_cast<float2*>(
                 &wacc[(gid + 8) * ACC_PITCH + 8 * nt + 2 * tig]) =
@@ -353,9 +379,14 @@ decode_kernel(const DecParams p) {
         return;
     }
 
-    // ---- cluster mode: CTA result into wb[0]; element (g, d) is read from every
-    // warp's buffer and written back by the same thread ---------------------------
-    for (int e = tid; e < G * HD; e += DTHREADS) {
+    // ---- cluster mode: the CTA's (m, l, O) is pushed into the shared memory of
+    // the CTAs that normalise it (CTA d owns output elements [d*per_e, (d+1)*per_e));
+    // after one cluster barrier every CTA finishes its slice from local memory ----
+    cg::cluster_group cluster = cg::this_cluster();
+    const int CL = (int)gridDim.x;
+    const int n_el = G * HD;
+    const int per_e = (n_el + CL - 1) / CL;
+    for (int e = tid; e < n_el; e += DTHREADS) {
         const int g = e / HD, d = e % HD;
         float M = -INFINITY;
 #pragma unroll
@@ -368,40 +399,40 @@ decode_kernel(const DecParams p) {
             Lsum += wt * lw;
             o += wt * reinterpret_cast<const float*>(&sm.wb[w])[g * ACC_PITCH + d];
         }
-        reinterpret_cast<float*>(&sm.wb[0])[g * ACC_PITCH + d] = o;
-        if (d == 0) { sm.cta_m[g] = M; sm.cta_l[g] = Lsum; }
-    }
-    cg::cluster_group cluster = cg::this_cluster();
-    DEC_TS(5);
-    cluster.sync();                               // every CTA's result is visible
-    DEC_TS(6);
-    {
-        const int CL = (int)gridDim.x;
-        const int n_el = G * HD;
-        const int per_e = (n_el + CL - 1) / CL;   // output elements of this CTA
-        for (int e = sp * per_e + tid; e < min((sp + 1) * per_e, n_el);
-             e += DTHREADS) {
-            const int g = e / HD, dd = e % HD;
-            float M = -INFINITY;
-            for (int c = 0; c < CL; ++c)
-                M = fmaxf(M, *cluster.map_shared_rank(&sm.cta_m[g], c));
-            float Lsum = 0.f, o = 0.f;
-            for (int c = 0; c < CL; ++c) {
-                const float lw = *cluster.map_shared_rank(&sm.cta_l[g], c);
-                const float mw = *cluster.map_shared_rank(&sm.cta_m[g], c);
-                const float wt = (lw > 0.f) ? __expf(mw - M) : 0.f;
-                const float* racc = cluster.map_shared_rank(
-                    reinterpret_cast<const float*>(&sm.wb[0]), c);
-                Lsum += wt * lw;
-                o += wt * racc[g * ACC_PITCH + dd];
-            }
-            const float val = (Lsum > 0.f) ? o / Lsum : 0.f;
-            p.out[(int64_t)r * p.out_stride_req + (int64_t)(kh * G + g) * HD + dd] =
-                __float2bfloat16_rn(val);
+        const int dst = e / per_e;
+        cluster.map_shared_rank(sm.xacc, dst)[sp * per_e + (e - dst * per_e)] = o;
+        if (d < CL) {                      // lane d tells CTA d this head's (m, l)
+            cluster.map_shared_rank(&sm.xm[sp][g], d)[0] = M;
+            cluster.map_shared_rank(&sm.xl[sp][g], d)[0] = Lsum;
         }
     }
+    DEC_TS(5);
+    cluster.sync();                               // every CTA's pushes have landed
+    DEC_TS(6);
+    for (int e = sp * per_e + tid; e < min((sp + 1) * per_e, n_el); e += DTHREADS) {
+        const int g = e / HD, dd = e % HD;
+        float mw[8], lw[8];
+        float M = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            mw[c] = (c < CL) ? sm.xm[c][g] : -INFINITY;
+            lw[c] = (c < CL) ? sm.xl[c][g] : 0.f;
+            M = fmaxf(M, mw[c]);
+        }
+        float Lsum = 0.f, o = 0.f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            if (c < CL) {
+                const float wt = (lw[c] > 0.f) ? __expf(mw[c] - M) : 0.f;
+                Lsum += wt * lw[c];
+                o += wt * sm.xacc[c * per_e + (e - sp * per_e)];
+            }
+        }
+        const float val = (Lsum > 0.f) ? o / Lsum : 0.f;
+        p.out[(int64_t)r * p.out_stride_req + (int64_t)(kh * G + g) * HD + dd] =
+            __float2bfloat16_rn(val);
+    }
     DEC_TS(7);
-    cluster.sync();                  // keep shared memory alive for remote readers
     DEC_TS(8);
     TL_MARK(g_dec_tl, 2);
 }

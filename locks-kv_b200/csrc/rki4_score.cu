@@ -203,6 +203,9 @@ rki4_score_kernel(const ScoreParams p) {
 
     // Everything above touches only per-step constants (block table, page
     // counts, summaries); q and the score buffers belong to the kernels before.
+    // The selector may be scheduled as soon as CTAs of this grid retire: its
+    // prologue then overlaps the scorer's tail (it waits for the whole grid).
+    pdl_trigger();
     pdl_wait();
     SC_TS(2);
     TL_MARK(g_score_tl, 1);
@@ -433,7 +436,6 @@ rki4_score_kernel(const ScoreParams p) {
 
     SC_TS(30);
     TL_MARK(g_score_tl, 2);
-    pdl_trigger();
     if (p.hmax != nullptr && tig == 0) {
 #pragma unroll
         for (int h = 0; h < NR; ++h) {

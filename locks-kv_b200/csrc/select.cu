@@ -28,7 +28,11 @@ namespace cg = cooperative_groups;
 namespace locks {
 namespace {
 
-constexpr int SEL_THREADS = 1024;
+constexpr int SEL_THREADS = 1024;            // distributed (cluster) selection
+#ifndef LOCKS_SINGLE_THREADS
+#define LOCKS_SINGLE_THREADS 512
+#endif
+constexpr int SINGLE_THREADS = LOCKS_SINGLE_THREADS;   // single-CTA selection
 constexpr int SEL_WARPS = SEL_THREADS / 32;
 constexpr int MAX_G = 16;
 
@@ -67,6 +71,7 @@ struct SelParams {
     int32_t* page_cnt;
     int n_kv, G, max_pages, sink;
     int owner_mode;     // keys of a whole row fit one CTA: helpers only combine
+    int key_cap;        // key slots per CTA (the histogram copies follow them)
 };
 
 TL_DECL(g_sel_tl)
@@ -86,6 +91,11 @@ constexpr int RBITS0 = 11, RBITS1 = 11, RBITS2 = 10;
 constexpr int NBINS = 1 << RBITS0;                // 2048 (largest digit)
 constexpr int MAX_CL = 8;
 constexpr int KEYS_PER_CTA = 16384;               // shared-memory key capacity
+// single-CTA selection: the latency-bound radix / compaction steps run on a few
+// warps with many keys per thread (barriers and scans cost per warp, not per key)
+constexpr int AW = 8;                             // active warps
+constexpr int ATH = AW * 32;
+constexpr int HCOPIES = 4;                        // histogram copies, by lane & 3
 
 struct SelSmem {
     int hist[NBINS];               // this CTA's histogram of the current digit
@@ -100,7 +110,7 @@ struct SelSmem {
     int x_kept;                    // ... kept pages in my page slice
     uint32_t sh_prefix;
     int sh_k;
-    int sh_i0, sh_i1;
+    int sh_i0, sh_i1, sh_i2;
 };
 
 // inclusive scan of 32 per-warp totals by warp 0 (in place); returns nothing,
@@ -152,28 +162,107 @@ __device__ __forceinline__ void find_digit(SelSmem& sm, const int* h, int nb,
     __syncthreads();
 }
 
+__device__ __forceinline__ void bar_active() {
+    asm volatile("bar.sync 1, %0;" ::"n"(ATH) : "memory");
+}
+
+// slot of a histogram bin: HCOPIES counters per bin, one spare slot after every
+// 8 bins so that threads which each own 4 or 8 consecutive bins read them
+// without shared-memory bank conflicts
+__device__ __forceinline__ int hslot(int bin) { return bin + (bin >> 3); }
+constexpr int HSLOTS = NBINS + NBINS / 8;
+
+// find_digit run by the first AW warps (the others skip it) over a histogram
+// kept as HCOPIES interleaved copies; nb is 1024 or 2048.  Thread t owns the
+// nb / ATH bins just below nb - t * (nb / ATH) and clears them on the way, so
+// the buffer is zero again afterwards.  The caller's next CTA-wide barrier
+// publishes sm.sh_i0 = digit d, sm.sh_i1 = k - count(bins > d), sm.sh_i2 =
+// count(d).
+__device__ __forceinline__ void find_digit_active(SelSmem& sm, int* h4, int nb,
+                                                  int k) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int bpl = nb / ATH;                              // 8 or 4
+    const int hb = nb - 1 - (int)threadIdx.x * bpl;        // my highest bin
+    int c[8];
+    int mine = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        c[i] = 0;
+        if (i < bpl) {
+            int4* q = reinterpret_cast<int4*>(h4) + hslot(hb - i);
+            const int4 v = *q;
+            c[i] = v.x + v.y + v.z + v.w;
+            *q = make_int4(0, 0, 0, 0);
+        }
+        mine += c[i];
+    }
+    int inc = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) sm.wtot[warp] = inc;
+    bar_active();
+    const int wv = (lane < AW) ? sm.wtot[lane] : 0;
+    int winc = wv;
+#pragma unroll
+    for (int o = 1; o < AW; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, winc, o);
+        if (lane >= o) winc += t;
+    }
+    int above = __shfl_sync(0xffffffffu, winc - wv, warp) + inc - mine;
+    if (above < k && k <= above + mine) {
+        bool found = false;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (!found && i < bpl) {
+                if (k <= above + c[i]) {
+                    sm.sh_i0 = hb - i; sm.sh_i1 = k - above; sm.sh_i2 = c[i];
+                    found = true;
+                } else {
+                    above += c[i];
+                }
+            }
+        }
+    }
+}
+
 // nrm combine of the groups [g_beg, g_end) of one warp: score = sum_g
 // exp(S[g] - hm[g]).  GT = G rounded up to a power of two; rows beyond G are
 // read from row G-1 and masked, so the loads are unconditional and all loads
-// of a batch are in flight together.
-template <int GT>
+// of a batch (CB groups, chosen to cover the warp's share in one batch when it
+// can) are in flight together.  `sync_hm()` is called once by every thread,
+// after the first batch of loads has been issued and before hm_sh is read: the
+// barrier that publishes the per-head maxima overlaps the score loads.
+template <int GT, int CBW, class SyncFn, class KeyFn>
 __device__ __forceinline__ void combine_nrm_groups(
     const float* __restrict__ sh, float* __restrict__ score, uint32_t* keys,
     const float* hm_sh, int G, int MP, int s0, int n_loc, int n_comb,
-    int g_beg, int g_end, int lane) {
-    constexpr int CB = (32 / GT > 8) ? 8 : (GT >= 16 ? 1 : 32 / GT);   // <= 32 loads in flight
+    int g_beg, int g_end, int lane, SyncFn sync_hm, KeyFn fin_key) {
+    constexpr int CB = (CBW * GT > 32) ? (GT >= 32 ? 1 : 32 / GT) : CBW;   // <= 32 loads in flight
     float hm[GT];
-#pragma unroll
-    for (int g = 0; g < GT; ++g) hm[g] = hm_sh[min(g, G - 1)];
-    for (int gb = g_beg; gb < g_end; gb += CB) {
+    bool first = true;
+    int gb = g_beg;
+    do {
         float v[CB][GT];
 #pragma unroll
         for (int u = 0; u < CB; ++u) {
             const int j = (gb + u) * 32 + lane;
-            const int i = min(s0 + j, n_comb - 1);          // clamped: always valid
+            const int i = max(min(s0 + j, n_comb - 1), 0);  // clamped: always valid
 #pragma unroll
             for (int g = 0; g < GT; ++g)
                 v[u][g] = __ldcg(&sh[(int64_t)min(g, G - 1) * MP + i]);
+        }
+        if (first) {
+            SEL_TS(23);
+            sync_hm();
+            SEL_TS(24);
+#pragma unroll
+            for (int g = 0; g < GT; ++g) hm[g] = hm_sh[min(g, G - 1)];
+            first = false;
+            if (v[0][0] == 12345.f) hm[0] = 0.f;   // wait for the loads (timing only)
+            SEL_TS(25);
         }
 #pragma unroll
         for (int u = 0; u < CB; ++u) {
@@ -186,10 +275,11 @@ __device__ __forceinline__ void combine_nrm_groups(
                     acc += (g < G) ? e : 0.f;
                 }
                 if (i < n_comb) score[i] = acc; else acc = 0.f;
-                keys[j] = f2key(acc);
+                keys[j] = fin_key(f2key(acc), i);
             }
         }
-    }
+        gb += CB;
+    } while (gb < g_end);
 }
 
 // per-head maxima of the groups of one warp (clamped, unconditional loads)
@@ -220,6 +310,14 @@ __device__ __forceinline__ void sweep_max_groups(
     }
 }
 
+#define LOCKS_DISPATCH_CB(N, CALL)                 \
+    do {                                           \
+        if ((N) <= 1) { constexpr int CBW = 1; CALL; }       \
+        else if ((N) <= 2) { constexpr int CBW = 2; CALL; }  \
+        else if ((N) <= 4) { constexpr int CBW = 4; CALL; }  \
+        else { constexpr int CBW = 8; CALL; }                \
+    } while (0)
+
 #define LOCKS_DISPATCH_GT(G, CALL)                 \
     do {                                           \
         if ((G) <= 1) { constexpr int GT = 1; CALL; }        \
@@ -229,8 +327,12 @@ __device__ __forceinline__ void sweep_max_groups(
         else { constexpr int GT = 16; CALL; }                \
     } while (0)
 
-__global__ void __launch_bounds__(SEL_THREADS)
+// NT threads per CTA.  SINGLE: one CTA selects the whole row (owner mode or no
+// cluster); otherwise every CTA of the cluster selects its slice (NT = 1024).
+template <int NT, bool SINGLE>
+__global__ void __launch_bounds__(NT)
 topb_kernel(const SelParams p) {
+    constexpr int NW = NT / 32;
     __shared__ SelSmem sm;
     extern __shared__ __align__(16) uint32_t keys[];   // keys of my page slice
     cg::cluster_group cluster = cg::this_cluster();
@@ -260,13 +362,13 @@ topb_kernel(const SelParams p) {
     // CTA 0 through distributed shared memory; CTA 0 alone selects, the helpers
     // write the -1 padding that no selection can reach and leave.
     // Distributed mode (long contexts): every CTA keeps and selects its slice.
-    const bool owner = p.owner_mode && CL_phys > 1;
+    const bool owner = SINGLE && CL_phys > 1;
     // slice whose scores this CTA combines
     const int cper = (((span + CL_phys - 1) / CL_phys) + 31) & ~31;
     const int cs0 = min(c_phys * cper, span), cs1 = min(cs0 + cper, span);
     const int cn_loc = cs1 - cs0;
     const int cn_grp = (cn_loc + 31) >> 5;
-    const int cgpw = (cn_grp + SEL_WARPS - 1) / SEL_WARPS;
+    const int cgpw = (cn_grp + NW - 1) / NW;
     const int cg_beg = min(warp * cgpw, cn_grp), cg_end = min(cg_beg + cgpw, cn_grp);
     uint32_t* kdst = owner ? cluster.map_shared_rank(keys, 0) + cs0 : keys;
     // slice this CTA selects from
@@ -275,13 +377,33 @@ topb_kernel(const SelParams p) {
     const int n_loc = s1 - s0;
     // warp w owns groups [w*gpw, (w+1)*gpw) of 32 consecutive pages
     const int n_grp = (n_loc + 31) >> 5;
-    const int gpw = (n_grp + SEL_WARPS - 1) / SEL_WARPS;
+    const int gpw = (n_grp + NW - 1) / NW;
     const int g_beg = min(warp * gpw, n_grp), g_end = min(g_beg + gpw, n_grp);
 
-    for (int i = tid; i < NBINS; i += SEL_THREADS) sm.hist[i] = 0;   // pass-0 bins
+    constexpr bool single = SINGLE;                 // one CTA selects the row
+    int* h4 = reinterpret_cast<int*>(keys + p.key_cap);
+    if constexpr (single) {
+        if (c_phys == 0)
+            for (int i = tid; i < HSLOTS; i += NT)
+                reinterpret_cast<int4*>(h4)[i] = make_int4(0, 0, 0, 0);
+    } else {
+        for (int i = tid; i < NBINS; i += NT) sm.hist[i] = 0;
+    }
     pdl_wait();                  // score_h / hmax / score come from the scorer
     SEL_TS(22);
     TL_MARK(g_sel_tl, 1);
+
+    // Single-CTA selection folds the page classes into the keys: 0 = not a page
+    // of the row, 0xFFFFFFFF = always kept (sink / recent pages, short rows),
+    // anything between = a selectable page's score key.
+    auto fin_key = [&](uint32_t key, int i) -> uint32_t {
+        if (!single) return key;
+        if (i >= npg) return 0u;
+        if (keep_all || i < lo || i >= hi) return 0xFFFFFFFFu;
+        return min(max(key, 1u), 0xFFFFFFFEu);
+    };
+    if (single && c_phys == 0)       // key slots past the row read as "no page"
+        for (int i = span + tid; i < p.key_cap; i += NT) keys[i] = 0u;
 
     // ---------------- 1. GQA combine -> score[slice], keys[slice] --------------
     // remote shared memory may only be touched once every CTA of the cluster
@@ -289,18 +411,16 @@ topb_kernel(const SelParams p) {
     if (owner && !(p.combine == LOCKS_COMBINE_NRM && n_comb > 0)) cluster.sync();
     if (p.combine == LOCKS_COMBINE_NRM && n_comb > 0) {
         const float* sh = p.score_h + row * (int64_t)G * MP;
-        if (p.hmax != nullptr) {
+        const bool published = p.hmax != nullptr;
+        if (published) {
             if (tid < G) sm.hm_sh[tid] = key2f(p.hmax[row * G + tid]);
-            if (CL_phys > 1) cluster.sync();        // everyone has read the keys
-            else __syncthreads();
-            if (c_phys == 0 && tid < G) p.hmax[row * G + tid] = 0u;
         } else {
             LOCKS_DISPATCH_GT(G, (sweep_max_groups<GT>(
                 sh, sm.wmax[warp], G, MP, cs0, cn_loc, n_comb, cg_beg, cg_end, lane)));
             __syncthreads();
             if (tid < G) {
                 float m = -INFINITY;
-                for (int w = 0; w < SEL_WARPS; ++w) m = fmaxf(m, sm.wmax[w][tid]);
+                for (int w = 0; w < NW; ++w) m = fmaxf(m, sm.wmax[w][tid]);
                 sm.xmax[tid] = m;
             }
             if (CL_phys > 1) {
@@ -315,12 +435,19 @@ topb_kernel(const SelParams p) {
                 __syncthreads();
                 if (tid < G) sm.hm_sh[tid] = sm.xmax[tid];
             }
-            __syncthreads();
         }
         SEL_TS(20);
-        LOCKS_DISPATCH_GT(G, (combine_nrm_groups<GT>(
+        // the barrier below publishes hm_sh, tells every CTA of the cluster that
+        // all of them run (remote shared memory may be written) and, for the
+        // scorer's keys, that all of them have read hmax (CTA 0 re-arms it)
+        auto sync_hm = [&]() {
+            if (CL_phys > 1 && (published || owner)) cluster.sync();
+            else __syncthreads();
+            if (published && c_phys == 0 && tid < G) p.hmax[row * G + tid] = 0u;
+        };
+        LOCKS_DISPATCH_GT(G, LOCKS_DISPATCH_CB(cgpw, (combine_nrm_groups<GT, CBW>(
             sh, score, kdst, sm.hm_sh, G, MP, cs0, cn_loc, n_comb, cg_beg, cg_end,
-            lane)));
+            lane, sync_hm, fin_key))));
         SEL_TS(21);
     } else if (p.combine == LOCKS_COMBINE_MAX && n_comb > 0) {
         const float* sh = p.score_h + row * (int64_t)G * MP;
@@ -334,13 +461,13 @@ topb_kernel(const SelParams p) {
                         m = fmaxf(m, sh[(int64_t)g * MP + i]);
                     score[i] = m;
                 }
-                kdst[j] = f2key(m);
+                kdst[j] = fin_key(f2key(m), i);
             }
         }
     } else {
         for (int grp = cg_beg; grp < cg_end; ++grp) {
             const int j = grp * 32 + lane;
-            if (j < cn_loc) kdst[j] = f2key(score[cs0 + j]);
+            if (j < cn_loc) kdst[j] = fin_key(f2key(score[cs0 + j]), cs0 + j);
         }
     }
     if (owner) {
@@ -350,8 +477,8 @@ topb_kernel(const SelParams p) {
             const int cnt_max = keep_all ? npg
                                          : min(npg, (npg - L) + min(max(b, 0), L));
             int32_t* tabp = p.page_table + row * MP;
-            for (int i = cnt_max + (c_phys - 1) * SEL_THREADS + tid; i < MP;
-                 i += (CL_phys - 1) * SEL_THREADS)
+            for (int i = cnt_max + (c_phys - 1) * NT + tid; i < MP;
+                 i += (CL_phys - 1) * NT)
                 tabp[i] = -1;
             return;
         }
@@ -363,6 +490,150 @@ topb_kernel(const SelParams p) {
     // selectable part of the slice, in local indices
     const int q0 = max(s0, lo) - s0, q1 = min(s1, hi) - s0;
 
+    if constexpr (single) {
+        // ============ single-CTA selection (s0 = 0: local index = page) ==========
+        // The per-key loops run on all warps, 4 consecutive keys per lane; the
+        // digit search runs on the first AW warps only.
+        int32_t* tab = p.page_table + row * MP;
+        // ---- 2. threshold: keys > tau_key are kept, `quota` of the keys equal
+        // to it (in ascending page order) as well
+        uint32_t tau_key = 0u;   // below every page's key: every page is kept
+        int quota = 0;
+        if (!keep_all && b <= 0) {
+            tau_key = 0xFFFFFFFEu;   // only the always-kept pages lie above
+        } else if (!keep_all && b < L) {
+            uint32_t prefix = 0u, mask = 0u;
+            int k = b, shift = 32;
+            bool whole_bin = false;
+#pragma unroll 1
+            for (int pass = 0; pass < 3 && !whole_bin; ++pass) {
+                const int bits = (pass == 0) ? RBITS0 : (pass == 1) ? RBITS1 : RBITS2;
+                const int nb = 1 << bits;
+                shift -= bits;
+                const uint32_t dmask = (uint32_t)nb - 1u;
+                for (int base = 4 * tid; base < n_loc; base += 4 * NT) {
+                    const uint4 kv = *reinterpret_cast<const uint4*>(&keys[base]);
+                    const uint32_t kk[4] = {kv.x, kv.y, kv.z, kv.w};
+#pragma unroll
+                    for (int s = 0; s < 4; ++s) {
+                        const uint32_t key = kk[s];
+                        if (key - 1u < 0xFFFFFFFEu && (key & mask) == prefix)
+                            atomicAdd(&h4[(hslot((key >> shift) & dmask) << 2) |
+                                          (lane & 3)], 1);
+                    }
+                }
+                SEL_TS(2 + 4 * pass);
+                __syncthreads();
+                SEL_TS(3 + 4 * pass);
+                if (warp < AW) find_digit_active(sm, h4, nb, k);
+                SEL_TS(4 + 4 * pass);
+                __syncthreads();
+                prefix |= (uint32_t)sm.sh_i0 << shift;
+                k = sm.sh_i1;
+                mask |= dmask << shift;
+                // the bin is taken whole: no finer digit and no tie rule needed
+                whole_bin = (sm.sh_i2 == k);
+                SEL_TS(5 + 4 * pass);
+            }
+            if (whole_bin) { tau_key = prefix ? prefix - 1u : 0u; quota = 0; }
+            else { tau_key = prefix; quota = k; }
+        }
+        SEL_TS(13);
+
+        // ---- 3. keep flags + ascending compaction.  Warp w owns a contiguous
+        // run of keys and walks it 128 keys at a time.
+        const uint32_t lt_mask = (1u << lane) - 1u;
+        const int WS = (((n_loc + NW - 1) / NW) + 127) & ~127;
+        const int w0 = min(warp * WS, n_loc), w1 = min(w0 + WS, n_loc);
+        const bool ties = quota > 0;
+        int c_sure = 0, c_eq = 0;
+        for (int it = w0; it < w1; it += 128) {
+            const uint4 kv = *reinterpret_cast<const uint4*>(&keys[it + 4 * lane]);
+            c_sure += (kv.x > tau_key) + (kv.y > tau_key) + (kv.z > tau_key) +
+                      (kv.w > tau_key);
+            c_eq += (kv.x == tau_key) + (kv.y == tau_key) + (kv.z == tau_key) +
+                    (kv.w == tau_key);
+        }
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) {
+            c_eq += __shfl_xor_sync(0xffffffffu, c_eq, o);
+            c_sure += __shfl_xor_sync(0xffffffffu, c_sure, o);
+        }
+        if (lane == 0) { sm.wtot[warp] = c_eq; sm.wtot2[warp] = c_sure; }
+        SEL_TS(15);
+        __syncthreads();
+        // every warp derives all warps' tie ranks and output slots by itself
+        const int e_w = (lane < NW) ? sm.wtot[lane] : 0;
+        const int s_w = (lane < NW) ? sm.wtot2[lane] : 0;
+        int einc = e_w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, einc, o);
+            if (lane >= o) einc += t;
+        }
+        const int k_w = s_w + min(max(quota - (einc - e_w), 0), e_w);
+        int kinc = k_w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, kinc, o);
+            if (lane >= o) kinc += t;
+        }
+        int pos = __shfl_sync(0xffffffffu, kinc - k_w, warp);
+        int eqr = __shfl_sync(0xffffffffu, einc - e_w, warp);
+        const int cnt = __shfl_sync(0xffffffffu, kinc, 31);
+        SEL_TS(17);
+        for (int it = w0; it < w1; it += 128) {
+            const int base = it + 4 * lane;
+            const uint4 kv = *reinterpret_cast<const uint4*>(&keys[base]);
+            const uint32_t kk[4] = {kv.x, kv.y, kv.z, kv.w};
+            bool keep[4];
+#pragma unroll
+            for (int s = 0; s < 4; ++s) keep[s] = kk[s] > tau_key;
+            if (ties) {
+                uint32_t eb[4];
+                int lower = 0, total = 0;
+#pragma unroll
+                for (int s = 0; s < 4; ++s) {
+                    eb[s] = __ballot_sync(0xffffffffu, kk[s] == tau_key);
+                    lower += __popc(eb[s] & lt_mask);
+                    total += __popc(eb[s]);
+                }
+                int rank = eqr + lower;              // ties before (lane, s = 0)
+#pragma unroll
+                for (int s = 0; s < 4; ++s) {
+                    if (kk[s] == tau_key) { keep[s] = rank < quota; ++rank; }
+                }
+                eqr += total;
+            }
+            int slot = pos, total = 0;
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                const uint32_t kb = __ballot_sync(0xffffffffu, keep[s]);
+                slot += __popc(kb & lt_mask);
+                total += __popc(kb);
+            }
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                if (keep[s]) tab[slot++] = base + s;
+            }
+            pos += total;
+        }
+        // -1 padding: in owner mode the helper CTAs did the part no selection
+        // can reach
+        {
+            const int cnt_max = keep_all ? npg
+                                         : min(npg, (npg - L) + min(max(b, 0), L));
+            const int pad_end = owner ? cnt_max : MP;
+            for (int i = cnt + tid; i < pad_end; i += NT) tab[i] = -1;
+        }
+        if (tid == 0) p.page_cnt[row] = cnt;
+        SEL_TS(18);
+        SEL_TS(19);
+        TL_MARK(g_sel_tl, 2);
+        return;
+    }
+
+    if constexpr (!single) {
     // ---------------- 2. threshold key (b-th largest of [lo, hi)) -------------
     uint32_t tau_key = 0u;       // below every real key: everything is "> tau"
     int quota = 0;
@@ -378,24 +649,10 @@ topb_kernel(const SelParams p) {
             const int nb = 1 << bits;
             shift -= bits;
             const uint32_t dmask = (uint32_t)nb - 1u;
-            if (CL == 1) {
-                // two histogram buffers: this pass counts into one (zeroed
-                // before) while clearing the other for the next pass
-                int* h = (pass & 1) ? sm.tot : sm.hist;
-                int* hn = (pass & 1) ? sm.hist : sm.tot;
-                for (int j = q0 + tid; j < q1; j += SEL_THREADS) {
-                    const uint32_t key = keys[j];
-                    if ((key & mask) == prefix)
-                        atomicAdd(&h[(key >> shift) & dmask], 1);
-                }
-                for (int i = tid; i < NBINS; i += SEL_THREADS) hn[i] = 0;
-                SEL_TS(2 + 4 * pass);
+            {
+                for (int i = tid; i < nb; i += NT) { sm.hist[i] = 0; sm.tot[i] = 0; }
                 __syncthreads();
-                find_digit(sm, h, nb, 0, k);
-            } else {
-                for (int i = tid; i < nb; i += SEL_THREADS) { sm.hist[i] = 0; sm.tot[i] = 0; }
-                __syncthreads();
-                for (int j = q0 + tid; j < q1; j += SEL_THREADS) {
+                for (int j = q0 + tid; j < q1; j += NT) {
                     const uint32_t key = keys[j];
                     if ((key & mask) == prefix)
                         atomicAdd(&sm.hist[(key >> shift) & dmask], 1);
@@ -403,7 +660,7 @@ topb_kernel(const SelParams p) {
                 cluster.sync();             // all slices' histograms are complete
                 // reduce-scatter: CTA c sums bins [c*bs, (c+1)*bs) of every CTA
                 const int bs = nb / CL;
-                for (int e = tid; e < bs * CL; e += SEL_THREADS) {
+                for (int e = tid; e < bs * CL; e += NT) {
                     const int bin = c * bs + (e % bs), src = e / bs;
                     const int v = cluster.map_shared_rank(sm.hist, src)[bin];
                     if (v) atomicAdd(&sm.tot[bin], v);
@@ -411,7 +668,7 @@ topb_kernel(const SelParams p) {
                 __syncthreads();
                 // total of my bin slice
                 int part = 0;
-                for (int e = tid; e < bs; e += SEL_THREADS) part += sm.tot[c * bs + e];
+                for (int e = tid; e < bs; e += NT) part += sm.tot[c * bs + e];
 #pragma unroll
                 for (int o = 16; o >= 1; o >>= 1)
                     part += __shfl_xor_sync(0xffffffffu, part, o);
@@ -419,7 +676,7 @@ topb_kernel(const SelParams p) {
                 __syncthreads();
                 if (tid == 0) {
                     int t = 0;
-                    for (int w = 0; w < SEL_WARPS; ++w) t += sm.wtot2[w];
+                    for (int w = 0; w < NW; ++w) t += sm.wtot2[w];
                     sm.x_slice_tot = t;
                 }
                 cluster.sync();             // slice totals + summed slices ready
@@ -433,7 +690,7 @@ topb_kernel(const SelParams p) {
                 // copy that summed slice locally (into hist, now free) and search
                 const int* rt = cluster.map_shared_rank(sm.tot, sl);
                 __syncthreads();
-                for (int e = tid; e < nb; e += SEL_THREADS)
+                for (int e = tid; e < nb; e += NT)
                     sm.hist[e] = (e >= sl * bs && e < (sl + 1) * bs) ? rt[e] : 0;
                 __syncthreads();
                 find_digit(sm, sm.hist, (sl + 1) * bs, above, k);
@@ -469,7 +726,7 @@ topb_kernel(const SelParams p) {
     __syncthreads();
     int eq_base = warp ? sm.wtot[warp - 1] : 0;
     if (CL > 1) {
-        if (tid == 0) sm.x_eq = sm.wtot[SEL_WARPS - 1];
+        if (tid == 0) sm.x_eq = sm.wtot[NW - 1];
         SEL_TS(14);
         cluster.sync();
         for (int cc = 0; cc < c; ++cc)
@@ -483,7 +740,7 @@ topb_kernel(const SelParams p) {
     scan_warp_totals(sm.wtot2);
     __syncthreads();
     int pos = warp ? sm.wtot2[warp - 1] : 0;
-    int cnt = sm.wtot2[SEL_WARPS - 1];
+    int cnt = sm.wtot2[NW - 1];
     if (CL > 1) {
         if (tid == 0) sm.x_kept = cnt;
         SEL_TS(16);
@@ -520,7 +777,7 @@ topb_kernel(const SelParams p) {
         const int pad_end = owner
             ? (keep_all ? npg : min(npg, (npg - L) + min(max(b, 0), L)))
             : MP;
-        for (int i = cnt + c * SEL_THREADS + tid; i < pad_end; i += CL * SEL_THREADS)
+        for (int i = cnt + c * NT + tid; i < pad_end; i += CL * NT)
             tab[i] = -1;
     }
     if (c == 0 && tid == 0) p.page_cnt[row] = cnt;
@@ -528,6 +785,7 @@ topb_kernel(const SelParams p) {
     if (CL > 1) cluster.sync();  // keep shared memory alive for remote readers
     SEL_TS(19);
     TL_MARK(g_sel_tl, 2);
+    }  // distributed selection
 }
 
 }  // namespace
@@ -597,22 +855,29 @@ extern "C" int locks_topb_select(
                   "locks_topb_select: max_pages %d beyond the supported %d",
                   max_pages, MAX_CL * KEYS_PER_CTA);
     p.owner_mode = owner_mode ? 1 : 0;
-    const int per_cta = owner_mode
-        ? ((max_pages + 31) & ~31) + 32 * 4
+    // key slots per CTA (the compaction reads whole 128-key rows), followed in
+    // single-CTA selection by the interleaved histogram copies
+    const bool single_cta = owner_mode || cl == 1;
+    const int per_cta = single_cta
+        ? ((max_pages + 127) & ~127) + 128
         : ((((max_pages + cl - 1) / cl) + 31) & ~31) + 32;
-    const int dyn_smem = per_cta * 4;
+    p.key_cap = per_cta;
+    const int dyn_smem = (per_cta + (single_cta ? HSLOTS * HCOPIES : 0)) * 4;
     static bool attr_done[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        cudaFuncSetAttribute(topb_kernel,
+        cudaFuncSetAttribute(topb_kernel<SINGLE_THREADS, true>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (KEYS_PER_CTA + 256 + HSLOTS * HCOPIES) * 4);
+        cudaFuncSetAttribute(topb_kernel<SEL_THREADS, false>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (KEYS_PER_CTA + 64) * 4);
         attr_done[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(cl, n_kv, n_req);
-    cfg.blockDim = dim3(SEL_THREADS, 1, 1);
+    cfg.blockDim = dim3(single_cta ? SINGLE_THREADS : SEL_THREADS, 1, 1);
     cfg.dynamicSmemBytes = dyn_smem;
     cfg.stream = static_cast<cudaStream_t>(stream);
     cudaLaunchAttribute attr[2];
@@ -624,7 +889,9 @@ extern "C" int locks_topb_select(
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, topb_kernel, p);
+    cudaError_t e = single_cta
+        ? cudaLaunchKernelEx(&cfg, topb_kernel<SINGLE_THREADS, true>, p)
+        : cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, false>, p);
     if (e != cudaSuccess)
         return fail(LOCKS_ERR_LAUNCH, "locks_topb_select: %s",
                     cudaGetErrorString(e));
