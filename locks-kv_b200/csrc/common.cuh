@@ -135,17 +135,6 @@ __device__ __forceinline__ void bulk_g2s_hint(void* dst, const void* src,
 }
 
 // ---- warp-level tensor-core fragments (M = 16 rows: the GQA group) ---------
-// D(16x8,s32) += A(16x32,s8,row) * B(32x8,u8,col)
-__device__ __forceinline__ void mma_s8u8_k32(int (&d)[4], uint32_t a0,
-                                             uint32_t a1, uint32_t a2,
-                                             uint32_t a3, uint32_t b0,
-                                             uint32_t b1) {
-    asm(
-        "mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 "
-        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
 // D(16x8,s32) += A(16x32,s8,row) * B(32x8,s8,col)
 __device__ __forceinline__ void mma_s8s8_k32(int (&d)[4], uint32_t a0,
                                              uint32_t a1, uint32_t a2,
@@ -156,6 +145,17 @@ __device__ __forceinline__ void mma_s8s8_k32(int (&d)[4], uint32_t a0,
         "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// D(16x8,s32) = A(16x32,s8,row) * B(32x8,s8,col)   (zero accumulator)
+__device__ __forceinline__ void mma_s8s8_k32_z(int (&d)[4], uint32_t a0,
+                                               uint32_t a1, uint32_t a2,
+                                               uint32_t a3, uint32_t b0,
+                                               uint32_t b1) {
+    asm(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 // D(16x8,f32) += A(16x16,bf16,row) * B(16x8,bf16,col)
 __device__ __forceinline__ void mma_bf16_k16(float (&d)[4], uint32_t a0,

@@ -1,19 +1,21 @@
 // Page scorer: per-head page log-sum-exp from the packed rki4 summary records.
 //
-// Grid (zsplit, n_kv, n_req), 128 threads, 4 CTAs per SM.  A CTA owns one
-// (request, kv-head) and a contiguous, evenly sized range of logical pages; its
-// four warps split that range again and run INDEPENDENTLY: each warp walks its
-// pages in chunks of 8 through a private 2-stage shared-memory ring.  Eight
-// lanes turn block-table entries into record addresses and issue one 832-byte
-// bulk async copy each (a record is one contiguous burst); completion is
-// tracked by the warp's own mbarrier, so the main loop has no CTA-wide barrier.
+// Grid (zsplit, n_kv, n_req), 128 threads, 4 CTAs per SM.  The W = 4 * zsplit
+// warps of a (request, kv-head) run INDEPENDENTLY and share its pages in chunks
+// of 8, dealt round-robin (warp gw takes chunks gw, gw + W, ...: neighbouring
+// warps read neighbouring block-table entries).  Each warp owns a 2-stage shared-
+// memory ring: eight lanes turn block-table entries into record addresses and
+// issue one 832-byte bulk async copy each (a record is one contiguous burst);
+// completion is tracked by the warp's own mbarrier, so the main loop has no
+// CTA-wide barrier.
 //
 // A chunk is scored with warp-level tensor-core fragments whose rows are the
 // query heads of the GQA group:
 //
 //   mu.q     s8 x s8  m16n8k32, the 8 pages of the chunk as the 8 columns
-//   V^T q    s8 x u8  m16n8k32, 4 k-steps per page; the int4 codes are used
-//            biased by +8 (one XOR per 8 nibbles), 8*sum(q8) is subtracted after
+//   V^T q    s8 x s8  m16n8k32, 4 k-steps per page; an int4 code is used in
+//            the high half of a byte (code * 16, still a signed byte: one shift
+//            and two masks per 8 codes), the factor 16 goes into the scale
 //   C qt     f16      m16n8k16: qt = hi + lo in fp16 (22 significant bits);
 //            C (int8) is exact in fp16
 //   LSE      base-2, 4 tokens per lane, two shuffle steps for max and for sum
@@ -40,7 +42,6 @@ struct __align__(128) ScoreSmem {
     uint8_t rec[NWARP][STAGES][CHUNK][REC_BYTES];
     int8_t q8[16][128];
     float qs[16];
-    int qsum[16];
     uint64_t full[NWARP][STAGES];
 };
 
@@ -79,6 +80,17 @@ __device__ __forceinline__ void mma_f16_k16(float (&d)[4], uint32_t a0,
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// D = A * B   (zero accumulator)
+__device__ __forceinline__ void mma_f16_k16_z(float (&d)[4], uint32_t a0,
+                                              uint32_t a1, uint32_t a2,
+                                              uint32_t a3, uint32_t b0,
+                                              uint32_t b1) {
+    asm(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
 // f0, f1 -> packed fp16 (hi parts) and packed fp16 (residuals)
 __device__ __forceinline__ void split_f16x2(float f0, float f1, uint32_t& hi,
                                             uint32_t& lo) {
@@ -96,7 +108,7 @@ __device__ __forceinline__ uint32_t s8x2_to_f16x2(uint32_t cc) {
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-// c[row][r] = sum_d q8[row][d] * (code[d][r] + 8) for one page
+// c[row][r] = 16 * sum_d q8[row][d] * code[d][r] for one page
 template <bool HI>
 __device__ __forceinline__ void project_page(int (&c)[4], const uint8_t* rec,
                                              int gid, int tig,
@@ -107,12 +119,16 @@ __device__ __forceinline__ void project_page(int (&c)[4], const uint8_t* rec,
     const uint4 vw =
         *reinterpret_cast<const uint4*>(rec + RO_V4 + gid * 64 + tig * 16);
     const uint32_t vword[4] = {vw.x, vw.y, vw.z, vw.w};
-    c[0] = c[1] = c[2] = c[3] = 0;
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
-        const uint32_t u = vword[s] ^ 0x88888888u;
-        mma_s8u8_k32(c, qe[s], HI ? qe_hi[s] : 0u, qo[s], HI ? qo_hi[s] : 0u,
-                     u & 0x0F0F0F0Fu, (u >> 4) & 0x0F0F0F0Fu);
+        const uint32_t even = (vword[s] << 4) & 0xF0F0F0F0u;   // low nibbles * 16
+        const uint32_t odd = vword[s] & 0xF0F0F0F0u;           // high nibbles * 16
+        if (s == 0)
+            mma_s8s8_k32_z(c, qe[s], HI ? qe_hi[s] : 0u, qo[s], HI ? qo_hi[s] : 0u,
+                           even, odd);
+        else
+            mma_s8s8_k32(c, qe[s], HI ? qe_hi[s] : 0u, qo[s], HI ? qo_hi[s] : 0u,
+                         even, odd);
     }
 }
 
@@ -157,16 +173,24 @@ rki4_score_kernel(const ScoreParams p) {
     const int gid = lane >> 2, tig = lane & 3;
     const int G = p.G;
 
-    int n_hi = p.n_sel_hi[r];
-    n_hi = min(n_hi, min(p.max_pages, p.bt_width));
+    // Warp gw takes chunks gw, gw + W, gw + 2W, ...  The first two chunks' place
+    // does not depend on the page count, so their block-table entries are fetched
+    // together with it and the copies start one round trip earlier.
+    const int W = NWARP * Z;
+    const int gw = z * NWARP + warp;
+    const int cap = min(p.max_pages, p.bt_width);
+    const int32_t* bt = p.block_table + (int64_t)r * p.bt_stride;
+    auto bt_at = [&](int page0) -> int {
+        const int pg = page0 + lane;
+        return (lane < CHUNK && pg < cap) ? bt[pg] : 0;
+    };
+    const int blk0 = bt_at(gw * CHUNK), blk1 = bt_at((gw + W) * CHUNK);
+    const int n_hi = min(p.n_sel_hi[r], cap);
     if (n_hi <= 0) return;
-    // contiguous page range of this CTA, then of this warp
-    const int cg0 = (int)(((int64_t)n_hi * z) / Z);
-    const int cg1 = (int)(((int64_t)n_hi * (z + 1)) / Z);
-    if (cg1 <= cg0) return;
-    const int pg0 = cg0 + (int)(((int64_t)(cg1 - cg0) * warp) / NWARP);
-    const int pg1 = cg0 + (int)(((int64_t)(cg1 - cg0) * (warp + 1)) / NWARP);
-    const int nc = (pg1 - pg0 + CHUNK - 1) / CHUNK;        // chunks of this warp
+    const int NC = (n_hi + CHUNK - 1) / CHUNK;
+    const int n_items = (gw < NC) ? (NC - gw + W - 1) / W : 0;
+    auto item_page0 = [&](int k) -> int { return (gw + k * W) * CHUNK; };
+    auto item_len = [&](int k) -> int { return min(CHUNK, n_hi - item_page0(k)); };
 
     if (tid == 0) {
         for (int w = 0; w < NWARP; ++w)
@@ -175,15 +199,12 @@ rki4_score_kernel(const ScoreParams p) {
     }
     __syncthreads();
 
-    const int32_t* bt = p.block_table + (int64_t)r * p.bt_stride;
     const uint8_t* recs = p.records + (int64_t)kh * REC_BYTES;
     const int64_t blk_stride = (int64_t)p.n_kv * REC_BYTES;
     // summaries are streamed once per step: do not let them push the scores,
     // page tables and K/V pages of the following kernels out of L2
     const uint64_t stream_policy = l2_policy_evict_first();
-    auto issue = [&](int chunk, int blk) {
-        const int stage = chunk % STAGES;
-        const int n = min(CHUNK, pg1 - pg0 - chunk * CHUNK);
+    auto issue = [&](int stage, int n, int blk) {
         fence_proxy_async();
         if (lane == 0)
             mbar_expect_tx(&sm.full[warp][stage], (uint32_t)n * REC_BYTES);
@@ -194,11 +215,8 @@ rki4_score_kernel(const ScoreParams p) {
                           REC_BYTES, &sm.full[warp][stage], stream_policy);
         }
     };
-    auto bt_of = [&](int chunk) -> int {
-        const int pg = pg0 + chunk * CHUNK + lane;
-        return (lane < CHUNK && pg < pg1) ? bt[pg] : 0;
-    };
-    for (int k = 0; k < STAGES && k < nc; ++k) issue(k, bt_of(k));
+    if (n_items > 0) issue(0, item_len(0), blk0);
+    if (n_items > 1) issue(1, item_len(1), blk1);
     SC_TS(1);
 
     // Everything above touches only per-step constants (block table, page
@@ -225,31 +243,27 @@ rki4_score_kernel(const ScoreParams p) {
         for (int o = 16; o >= 1; o >>= 1)
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
         const float qs = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
-        int sum = 0;
         uint32_t packed = 0;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int c = __float2int_rn(__fdiv_rn(v[i], qs));
-            sum += c;
             packed |= (uint32_t)(c & 0xFF) << (8 * i);
         }
-#pragma unroll
-        for (int o = 16; o >= 1; o >>= 1)
-            sum += __shfl_xor_sync(0xffffffffu, sum, o);
         *reinterpret_cast<uint32_t*>(&sm.q8[g][4 * lane]) = packed;
-        if (lane == 0) { sm.qs[g] = qs; sm.qsum[g] = sum; }
+        if (lane == 0) sm.qs[g] = qs;
     }
     __syncthreads();
     SC_TS(3);
 
     // ---- A fragments of q.  Row gid holds head gid % GP (the group is repeated
     // when it is shorter than 8 rows); rows 8..15 are used only for GP = 16. ----
+    const float scale2 = p.scale * 1.4426950408889634f;     // base-2 logits
     constexpr int NR = (GP == 16) ? 2 : 1;
     constexpr bool HI = (GP == 16);
     constexpr int GROW = (GP < 8) ? GP : 8;
     uint32_t qn[NR][8], qe[NR][4], qo[NR][4];
-    float qsc[NR];
-    int qsm8[NR];
+    float qsc[NR];         // q scale * log2(e) * softmax scale (mu . q term)
+    float qsv[NR];         // the same / 16 (the V codes enter as code * 16)
 #pragma unroll
     for (int h = 0; h < NR; ++h) {
         const int g = (gid % GROW) + 8 * h;
@@ -266,31 +280,30 @@ rki4_score_kernel(const ScoreParams p) {
             qe[h][s] = __byte_perm(n0, n1, 0x6420);
             qo[h][s] = __byte_perm(n0, n1, 0x7531);
         }
-        qsc[h] = live ? sm.qs[g] : 0.f;
-        qsm8[h] = live ? 8 * sm.qsum[g] : 0;
+        qsc[h] = live ? sm.qs[g] * scale2 : 0.f;
+        qsv[h] = qsc[h] * 0.0625f;
     }
 
     float run_max[NR];
 #pragma unroll
     for (int h = 0; h < NR; ++h) run_max[h] = -INFINITY;
-    const float scale2 = p.scale * 1.4426950408889634f;     // base-2 logits
     constexpr float LN2 = 0.6931471805599453f;
     float* out_base =
         p.score_h + ((int64_t)r * p.n_kv + kh) * (int64_t)G * p.max_pages;
 
-    for (int k = 0; k < nc; ++k) {
-        const int stage = k % STAGES;
-        const int p0 = pg0 + k * CHUNK;
-        const int n = min(CHUNK, pg1 - p0);
-        // block-table entries of the chunk that will reuse this stage
-        const int next_blk = (k + STAGES < nc) ? bt_of(k + STAGES) : 0;
+    for (int k = 0; k < n_items; ++k) {
+        const int stage = k & 1;
+        const int p0 = item_page0(k);
+        const int n = item_len(k);
+        // block-table entries of the item that will reuse this stage
+        const int next_blk = (k + 2 < n_items) ? bt_at(item_page0(k + 2)) : 0;
         SC_TS(4 + 2 * k);
-        mbar_wait(&sm.full[warp][stage], (uint32_t)((k / STAGES) & 1), p.status);
+        mbar_wait(&sm.full[warp][stage], (uint32_t)((k >> 1) & 1), p.status);
         SC_TS(5 + 2 * k);
         const uint8_t* crec = &sm.rec[warp][stage][0][0];
 
         // mu . q for the chunk's 8 pages: column (n) = page slot gid
-        int muc[4] = {0, 0, 0, 0};
+        int muc[4];
         {
             const uint8_t* mrec = crec + gid * REC_BYTES + RO_MU8 + 32 * tig;
             const uint4 m0 = *reinterpret_cast<const uint4*>(mrec);
@@ -298,18 +311,24 @@ rki4_score_kernel(const ScoreParams p) {
             const uint32_t mw[8] = {m0.x, m0.y, m0.z, m0.w,
                                     m1.x, m1.y, m1.z, m1.w};
 #pragma unroll
-            for (int s = 0; s < 4; ++s)
-                mma_s8s8_k32(muc, qn[0][2 * s], HI ? qn[NR - 1][2 * s] : 0u,
-                             qn[0][2 * s + 1], HI ? qn[NR - 1][2 * s + 1] : 0u,
-                             mw[2 * s], mw[2 * s + 1]);
+            for (int s = 0; s < 4; ++s) {
+                if (s == 0)
+                    mma_s8s8_k32_z(muc, qn[0][0], HI ? qn[NR - 1][0] : 0u, qn[0][1],
+                                   HI ? qn[NR - 1][1] : 0u, mw[0], mw[1]);
+                else
+                    mma_s8s8_k32(muc, qn[0][2 * s], HI ? qn[NR - 1][2 * s] : 0u,
+                                 qn[0][2 * s + 1], HI ? qn[NR - 1][2 * s + 1] : 0u,
+                                 mw[2 * s], mw[2 * s + 1]);
+            }
         }
 
         if constexpr (GP == 4) {
             // ---- two pages per pass: rows 0-3 -> slot 2j, rows 4-7 -> 2j+1 ----
             const int sel = gid >> 2;
-#pragma unroll 4
-            for (int j = 0; j < CHUNK / 2; ++j) {
-                if (2 * j >= n) break;
+            // no per-pair exit test: slots past n hold stale bytes whose results
+            // are dropped, and without the branch the pairs' dependency chains
+            // interleave; a chunk of at most 4 pages runs the 2-pair variant
+            auto do_pair = [&](int j) {
                 const uint8_t* recA = crec + (2 * j) * REC_BYTES;
                 const uint8_t* recB = recA + REC_BYTES;
                 const uint8_t* own = sel ? recB : recA;
@@ -327,11 +346,10 @@ rki4_score_kernel(const ScoreParams p) {
                                            (lane & ~3) | j);
                 uint32_t a_hi, a_lo;
                 split_f16x2(
-                    (float)(c0 - qsm8[0]) *
-                        (qsc[0] * bf16_bits_to_f32(vs2 & 0xFFFFu)),
-                    (float)(c1 - qsm8[0]) * (qsc[0] * bf16_bits_to_f32(vs2 >> 16)),
+                    (float)c0 * (qsv[0] * bf16_bits_to_f32(vs2 & 0xFFFFu)),
+                    (float)c1 * (qsv[0] * bf16_bits_to_f32(vs2 >> 16)),
                     a_hi, a_lo);
-                const float mud = (float)mq * (qsc[0] * mus * scale2);
+                const float mud = (float)mq * (qsc[0] * mus);
                 // block-diagonal A: k 0-7 multiply page A's C, k 8-15 page B's
                 const uint32_t a0h = sel ? 0u : a_hi, a2h = sel ? a_hi : 0u;
                 const uint32_t a0l = sel ? 0u : a_lo, a2l = sel ? a_lo : 0u;
@@ -343,8 +361,7 @@ rki4_score_kernel(const ScoreParams p) {
                         *reinterpret_cast<const uint16_t*>(recA + off));
                     const uint32_t bB = s8x2_to_f16x2(
                         *reinterpret_cast<const uint16_t*>(recB + off));
-                    x[th][0] = x[th][1] = x[th][2] = x[th][3] = 0.f;
-                    mma_f16_k16(x[th], a0h, 0u, a2h, 0u, bA, bB);
+                    mma_f16_k16_z(x[th], a0h, 0u, a2h, 0u, bA, bB);
                     mma_f16_k16(x[th], a0l, 0u, a2l, 0u, bA, bB);
                 }
                 const uint32_t csa =
@@ -352,10 +369,10 @@ rki4_score_kernel(const ScoreParams p) {
                 const uint32_t csb =
                     *reinterpret_cast<const uint32_t*>(own + RO_CS + 16 + 4 * tig);
                 const float S = LN2 * quad_lse2(
-                    fmaf(bf16_bits_to_f32(csa & 0xFFFFu) * scale2, x[0][0], mud),
-                    fmaf(bf16_bits_to_f32(csa >> 16) * scale2, x[0][1], mud),
-                    fmaf(bf16_bits_to_f32(csb & 0xFFFFu) * scale2, x[1][0], mud),
-                    fmaf(bf16_bits_to_f32(csb >> 16) * scale2, x[1][1], mud));
+                    fmaf(bf16_bits_to_f32(csa & 0xFFFFu), x[0][0], mud),
+                    fmaf(bf16_bits_to_f32(csa >> 16), x[0][1], mud),
+                    fmaf(bf16_bits_to_f32(csb & 0xFFFFu), x[1][0], mud),
+                    fmaf(bf16_bits_to_f32(csb >> 16), x[1][1], mud));
                 const int slot = 2 * j + sel;
                 const int g = gid & 3;
                 if (slot < n && g < G) {
@@ -363,6 +380,13 @@ rki4_score_kernel(const ScoreParams p) {
                         out_base[(int64_t)g * p.max_pages + p0 + slot] = S;
                     run_max[0] = fmaxf(run_max[0], S);
                 }
+            };
+            if (n > CHUNK / 2) {
+#pragma unroll
+                for (int j = 0; j < CHUNK / 2; ++j) do_pair(j);
+            } else {
+#pragma unroll
+                for (int j = 0; j < CHUNK / 4; ++j) do_pair(j);
             }
         } else {
             // ---- one page per pass, rows = heads (8, or 16 with the hi rows) --
@@ -390,10 +414,10 @@ rki4_score_kernel(const ScoreParams p) {
                 float mud[NR];
 #pragma unroll
                 for (int h = 0; h < NR; ++h) {
-                    split_f16x2((float)(c1[2 * h] - qsm8[h]) * (qsc[h] * vs0),
-                                (float)(c1[2 * h + 1] - qsm8[h]) * (qsc[h] * vs1),
+                    split_f16x2((float)c1[2 * h] * (qsv[h] * vs0),
+                                (float)c1[2 * h + 1] * (qsv[h] * vs1),
                                 a_hi[h], a_lo[h]);
-                    mud[h] = (float)(h == 0 ? mlo : mhi) * (qsc[h] * mus * scale2);
+                    mud[h] = (float)(h == 0 ? mlo : mhi) * (qsc[h] * mus);
                 }
                 float x[2][4];
 #pragma unroll
@@ -401,18 +425,17 @@ rki4_score_kernel(const ScoreParams p) {
                     const uint32_t bC =
                         s8x2_to_f16x2(*reinterpret_cast<const uint16_t*>(
                             rec + RO_C8 + (8 * th + gid) * 8 + 2 * tig));
-                    x[th][0] = x[th][1] = x[th][2] = x[th][3] = 0.f;
-                    mma_f16_k16(x[th], a_hi[0], HI ? a_hi[NR - 1] : 0u, a_lo[0],
-                                HI ? a_lo[NR - 1] : 0u, bC, bC);
+                    mma_f16_k16_z(x[th], a_hi[0], HI ? a_hi[NR - 1] : 0u, a_lo[0],
+                                  HI ? a_lo[NR - 1] : 0u, bC, bC);
                 }
                 const uint32_t csa =
                     *reinterpret_cast<const uint32_t*>(rec + RO_CS + 4 * tig);
                 const uint32_t csb =
                     *reinterpret_cast<const uint32_t*>(rec + RO_CS + 16 + 4 * tig);
-                const float cs0 = bf16_bits_to_f32(csa & 0xFFFFu) * scale2;
-                const float cs1 = bf16_bits_to_f32(csa >> 16) * scale2;
-                const float cs2 = bf16_bits_to_f32(csb & 0xFFFFu) * scale2;
-                const float cs3 = bf16_bits_to_f32(csb >> 16) * scale2;
+                const float cs0 = bf16_bits_to_f32(csa & 0xFFFFu);
+                const float cs1 = bf16_bits_to_f32(csa >> 16);
+                const float cs2 = bf16_bits_to_f32(csb & 0xFFFFu);
+                const float cs3 = bf16_bits_to_f32(csb >> 16);
 #pragma unroll
                 for (int h = 0; h < NR; ++h) {
                     const float S = LN2 * quad_lse2(
@@ -431,7 +454,7 @@ rki4_score_kernel(const ScoreParams p) {
         }
 
         __syncwarp();                         // the warp is done with `stage`
-        if (k + STAGES < nc) issue(k + STAGES, next_blk);
+        if (k + 2 < n_items) issue(stage, item_len(k + 2), next_blk);
     }
 
     SC_TS(30);
