@@ -187,6 +187,20 @@ int locks_decode_fused(const void* q, int64_t q_stride_req, const void* k_cache,
                        int head_dim, int page, int max_pages, float scale,
                        int* status, locks_stream_t stream);
 
+/* Merge of split partials gathered from several ranks (context parallel: every
+ * rank decodes the selected pages it holds, the partial sets are all-gathered,
+ * every rank merges them).  No counterpart in the reference, which is single
+ * GPU; the merge formula is attention/merge.py:105-152.
+ * packs: n_groups sets, pack_stride floats apart (a multiple of 4); one set is
+ * m (n_req, n_kv, split, G) | l (same) | acc (n_req, n_kv, split, G, head_dim),
+ * contiguous, i.e. what locks_decode_split wrote through three pointers into
+ * one buffer.  EVERY split of every set is read; a split that attended nothing
+ * must carry l = 0 (clear l before the decode).  packs 16-byte aligned,
+ * n_req*n_kv*split*G even. */
+int locks_merge_gathered(const float* packs, int64_t pack_stride, int n_groups,
+                         void* out, int64_t out_stride_req, int n_req, int n_kv,
+                         int G, int head_dim, int split, locks_stream_t stream);
+
 /* Split decode + merge WITHOUT caller-provided partial buffers.  No counterpart
  * in the reference (its kernels always take caller-allocated partials).
  * For callers that cannot allocate device memory -- e.g. a host-language

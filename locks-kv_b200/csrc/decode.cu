@@ -446,6 +446,9 @@ struct MergeParams {
     __nv_bfloat16* out;
     int64_t out_stride_req;
     int n_kv, G, split, pps_min;
+    int n_groups;                  // partial sets (one per rank when gathered)
+    int64_t group_stride;          // floats between two sets (m, l and acc alike)
+    int all_splits;                // read every split (empty ones carry l = 0)
 };
 
 // grid (n_kv*G, n_req), 128 threads.  Warp w merges splits w, w+4, ... online
@@ -458,19 +461,26 @@ __global__ void __launch_bounds__(HD) merge_kernel(const MergeParams p) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int kh = h / p.G, g = h % p.G;
     const int64_t row = (int64_t)r * p.n_kv + kh;
-    const int cnt = p.page_cnt ? p.page_cnt[row]
-                               : (max(p.seq_lens[r], 0) + PAGE_T - 1) / PAGE_T;
-    const int pps = max((cnt + p.split - 1) / p.split, p.pps_min);
-    const int n_act = (cnt + pps - 1) / pps;
+    int n_act = p.split;
+    if (!p.all_splits) {
+        const int cnt = p.page_cnt ? p.page_cnt[row]
+                                   : (max(p.seq_lens[r], 0) + PAGE_T - 1) / PAGE_T;
+        const int pps = max((cnt + p.split - 1) / p.split, p.pps_min);
+        n_act = (cnt + pps - 1) / pps;
+    }
+    const int n_tot = n_act * p.n_groups;
     const int64_t base = row * p.split * p.G + g;
     float M = -INFINITY, Ls = 0.f;
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 4
-    for (int s = warp; s < n_act; s += 4) {
+    for (int e = warp; e < n_tot; e += 4) {
+        const int grp = e / n_act, s = e - grp * n_act;
         const int64_t i = base + (int64_t)s * p.G;
-        const float m = p.m_part[i], l = p.l_part[i];
-        const float4 a =
-            *reinterpret_cast<const float4*>(&p.acc_part[i * HD + 4 * lane]);
+        const float* mp = p.m_part + grp * p.group_stride;
+        const float* lp = p.l_part + grp * p.group_stride;
+        const float* ap = p.acc_part + grp * p.group_stride;
+        const float m = mp[i], l = lp[i];
+        const float4 a = *reinterpret_cast<const float4*>(&ap[i * HD + 4 * lane]);
         if (l > 0.f) {
             const float Mn = fmaxf(M, m);
             const float ao = __expf(M - Mn), w = __expf(m - Mn);
@@ -640,9 +650,38 @@ extern "C" int locks_merge_splits(
     p.page_cnt = page_cnt; p.seq_lens = nullptr;
     p.out = static_cast<__nv_bfloat16*>(out); p.out_stride_req = out_stride_req;
     p.n_kv = n_kv; p.G = G; p.split = split; p.pps_min = pps_min;
+    p.n_groups = 1; p.group_stride = 0; p.all_splits = 0;
     merge_kernel<<<dim3(n_kv * G, n_req), HD, 0,
                    static_cast<cudaStream_t>(stream)>>>(p);
     return check_launch("locks_merge_splits");
+}
+
+extern "C" int locks_merge_gathered(
+    const float* packs, int64_t pack_stride, int n_groups, void* out,
+    int64_t out_stride_req, int n_req, int n_kv, int G, int head_dim, int split,
+    locks_stream_t stream) {
+    LOCKS_REQUIRE(packs && out, LOCKS_ERR_ARG,
+                  "locks_merge_gathered: null pointer argument");
+    LOCKS_REQUIRE(head_dim == HD, LOCKS_ERR_GEOMETRY,
+                  "locks_merge_gathered: supports head_dim 128, got %d", head_dim);
+    const int64_t n_ml = (int64_t)n_req * n_kv * split * G;
+    LOCKS_REQUIRE(n_req >= 0 && n_req <= 65535 && n_kv >= 1 && G >= 1 &&
+                      split >= 1 && n_groups >= 1 &&
+                      pack_stride >= n_ml * (2 + HD) && (pack_stride % 4) == 0 &&
+                      (n_ml % 2) == 0 &&
+                      (reinterpret_cast<uintptr_t>(packs) & 15) == 0,
+                  LOCKS_ERR_ARG,
+                  "locks_merge_gathered: bad size, stride or alignment");
+    if (n_req == 0) return LOCKS_OK;
+    MergeParams p{};
+    p.m_part = packs; p.l_part = packs + n_ml; p.acc_part = packs + 2 * n_ml;
+    p.page_cnt = nullptr; p.seq_lens = nullptr;
+    p.out = static_cast<__nv_bfloat16*>(out); p.out_stride_req = out_stride_req;
+    p.n_kv = n_kv; p.G = G; p.split = split; p.pps_min = 1;
+    p.n_groups = n_groups; p.group_stride = pack_stride; p.all_splits = 1;
+    merge_kernel<<<dim3(n_kv * G, n_req), HD, 0,
+                   static_cast<cudaStream_t>(stream)>>>(p);
+    return check_launch("locks_merge_gathered");
 }
 
 extern "C" int locks_decode_fused(

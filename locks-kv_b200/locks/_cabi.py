@@ -37,6 +37,7 @@ _SIGNATURES = {
                             _P], 1),
     "locks_merge_splits": ([_P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I,
                             _P], 1),
+    "locks_merge_gathered": ([_P, _L, _I, _P, _L, _I, _I, _I, _I, _I, _P], 1),
     "locks_decode_fused": ([_P, _L, _P, _P, _L, _L, _L, _P, _L, _P, _P, _P, _P,
                             _L, _I, _I, _I, _I, _I, _I, _F, _P, _P], 1),
     "locks_dense_decode": ([_P, _L, _P, _P, _L, _L, _L, _P, _L, _P, _P, _P, _P,

@@ -1,0 +1,227 @@
+"""Context-parallel driver of the decode hot path: ONE long sequence whose pages
+are spread over the ranks of a process group (one process per GPU).
+
+Rank k holds the contiguous page range ``[p0, p1)`` -- its K/V pages and their
+summaries -- and runs the same kernels as the single-GPU path on that slice.
+Per layer three small exchanges make the result equal to the single-GPU one:
+
+  1. all-reduce(max) of the per-head score maxima the scorer published (the
+     default GQA combine normalises by the maximum over ALL pages);
+  2. all-gather of every rank's best ``b`` (score, page) candidates -- the local
+     selector run with the global budget -- after which every rank applies the
+     same exact-b rule (score descending, page ascending) to the union and keeps
+     its own members plus its sink / recent-window pages;
+  3. all-gather of the split-K partials (m, l, acc) of the pages each rank
+     attended, merged by ``locks_merge_gathered``.
+
+The reference has no distributed code; the page rules are the reference's
+(``selection/select.py:28-58``, ``:183-222``), applied to global page numbers.
+The collectives go through ``torch.distributed`` (NCCL); remote data lands in
+local memory before a kernel of this library reads it.  The whole step has
+fixed shapes and no host synchronisation, so it can be captured in a CUDA graph.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _cabi
+from .attention import ResidentVSource
+from .attention.decode import _kv_args
+from .config import LocksConfig
+from .parallel import global_select
+from .selection import Rki4State, rki4_build_bulk, rki4_score_only
+from .selection.select import nrmtopb_select
+
+_SIGN = -(1 << 31)          # int32 view of 0x80000000
+_BIG_PAGE = (1 << 31) - 1
+
+
+def global_page_params(seq_len: int, page: int, cfg: LocksConfig):
+    """(n_pages, n_sel_hi, b) of the whole sequence, as ``derive_page_params``
+    computes them for a request (reference ``selection/select.py:28-58``)."""
+    npg = -(-int(seq_len) // page)
+    nsh = npg - cfg.window_pages
+    s = nsh - cfg.sink_pages
+    if cfg.budget_pages:
+        b = max(min(int(cfg.budget_pages), max(s, 1)), 1)
+    else:
+        frac = cfg.budget if cfg.budget is not None else 0.1
+        b = min(max(int(math.ceil(s * frac)), 1), max(s, 1))
+    return npg, nsh, b
+
+
+class ContextParallelHotPath:
+    """Decode steps of one sequence over the ranks of ``group``.
+
+    kv_caches: per layer, this rank's paged cache ``(NB, 2, page, n_kv, d)``;
+    block_table: ``(1, p1 - p0)`` int32, local page j -> local block.
+    """
+
+    def __init__(self, kv_caches: List[torch.Tensor], block_table: torch.Tensor,
+                 *, seq_len: int, p0: int, p1: int, n_kv: int, G: int,
+                 scale: float, cfg: LocksConfig, group=None, split: int = 4):
+        dev = kv_caches[0].device
+        self.device, self.cfg, self.group = dev, cfg, group
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.kv_caches, self.block_table = kv_caches, block_table
+        NB, _, page, _, d = kv_caches[0].shape
+        self.page, self.d, self.n_kv, self.G = int(page), int(d), n_kv, G
+        self.scale = float(scale)
+        self.p0, self.p1 = int(p0), int(p1)
+        n_loc = self.p1 - self.p0
+        assert n_loc >= 1 and block_table.shape == (1, n_loc)
+        npg, nsh, b = global_page_params(seq_len, self.page, cfg)
+        assert self.p1 <= npg
+        self.npg, self.nsh, self.b = npg, nsh, b
+        # the slice seen as a sequence of its own: local page j = global p0 + j
+        self.sink_loc = min(max(cfg.sink_pages - self.p0, 0), n_loc)
+        self.nsh_loc = min(max(nsh - self.p0, 0), n_loc)
+        tok_loc = min(int(seq_len) - self.p0 * self.page, n_loc * self.page)
+        self.seq_lens = torch.tensor([tok_loc], dtype=torch.int32, device=dev)
+        L = len(kv_caches)
+        st = Rki4State(dev, num_layers=L, num_blocks=int(NB), n_kv=n_kv, G=G,
+                       head_dim=int(d), page=int(page), max_reqs=1,
+                       max_pages=n_loc, budget_pages=b,
+                       sink_pages=self.sink_loc,
+                       window_pages=max(cfg.window_pages, 1),
+                       combine=cfg.quad_combine, zsplit=cfg.rki4_zsplit)
+        assert st.combine == "nrm", "context parallel implements the nrm combine"
+        st.scale = self.scale
+        st.n_pages.fill_(n_loc)
+        st.n_sel_hi.fill_(self.nsh_loc)
+        st.b_fix.fill_(b)
+        self.st = st
+        self.K_layers = [c[:, 0] for c in kv_caches]
+        self.vsources = [ResidentVSource(c) for c in kv_caches]
+        H = n_kv * G
+        self.q = torch.zeros(L, 1, H, d, device=dev, dtype=torch.bfloat16)
+        self.out = torch.zeros(L, 1, H, d, device=dev, dtype=torch.bfloat16)
+        # most pages a rank can end up attending: b selected + sink + window
+        self.cap = min(n_loc, b + cfg.sink_pages + cfg.window_pages + 1)
+        # split-K partials of all ranks: [world][m | l | acc], this rank writes
+        # (and all-gathers in place) its own set
+        self.split = int(split)
+        n_ml = n_kv * self.split * G
+        self.n_ml = n_ml
+        self.pack_len = (n_ml * (2 + d) + 3) // 4 * 4
+        self.packs = torch.zeros(self.world, self.pack_len, device=dev,
+                                 dtype=torch.float32)
+        mine = self.packs[self.rank]
+        self.m_part = mine[:n_ml]
+        self.l_part = mine[n_ml:2 * n_ml]
+        self.acc_part = mine[2 * n_ml:2 * n_ml + n_ml * d]
+        self.cand = torch.zeros(self.world, 2, n_kv, self.cap, device=dev,
+                                dtype=torch.float32)
+        self._col = torch.arange(self.cap, device=dev)[None, :]
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+
+    # ---- summaries ---------------------------------------------------------
+    def build_all(self) -> int:
+        settled = self.seq_lens - 1 if self.p1 == self.npg else self.seq_lens
+        max_fin = int(settled.max().item()) // self.page
+        return rki4_build_bulk(self.st, self.K_layers, self.block_table, settled,
+                               1, max_fin)
+
+    # ---- the three exchanges -------------------------------------------------
+    def _exchange_hmax(self) -> None:
+        """Keys are order-preserving as UNSIGNED ints; flipping the top bit
+        makes the int32 maximum agree.  0 ("no page scored here") loses."""
+        if self.world == 1:
+            return
+        hm = self.st.hmax
+        hm.bitwise_xor_(_SIGN)
+        dist.all_reduce(hm, op=dist.ReduceOp.MAX, group=self.group)
+        hm.bitwise_xor_(_SIGN)
+
+    def _exchange_candidates(self) -> None:
+        """Local top-b list -> global exact-b cut -> this rank's final list."""
+        st, cap = self.st, self.cap
+        tab = st.page_table[0, :, :cap]                       # (n_kv, cap) local ids
+        live = tab >= 0
+        selectable = live & (tab >= self.sink_loc) & (tab < self.nsh_loc)
+        sc = torch.gather(st.score[0], 1, tab.clamp(min=0).long())
+        neg = torch.full_like(sc, float("-inf"))
+        mine = self.cand[self.rank]
+        mine[0] = torch.where(selectable, sc, neg)
+        # page ids travel as exact small floats (< 2^24 pages)
+        mine[1] = torch.where(selectable, (tab + self.p0).float(),
+                              torch.full_like(sc, float(1 << 24)))
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.cand.view(-1), mine.reshape(-1),
+                                        group=self.group)
+        all_s = self.cand[:, 0].permute(1, 0, 2).reshape(self.n_kv, -1)
+        all_p = self.cand[:, 1].permute(1, 0, 2).reshape(self.n_kv, -1)
+        keep = global_select(all_s, all_p, self.b)
+        keep_mine = keep.view(self.n_kv, self.world, cap)[:, self.rank]
+        final = live & (~selectable | keep_mine)
+        # stable compaction of the kept entries (ascending page order is kept)
+        pos = torch.cumsum(final, dim=1) - 1
+        dst = torch.where(final, pos, torch.full_like(pos, cap))
+        buf = torch.full((self.n_kv, cap + 1), -1, dtype=tab.dtype,
+                         device=tab.device)
+        buf.scatter_(1, dst, tab)
+        tab.copy_(buf[:, :cap])
+        st.page_cnt[0] = final.sum(dim=1).to(st.page_cnt.dtype)
+
+    def _decode_and_merge(self, l: int) -> None:
+        st = self.st
+        q = self.q[l]
+        k, v = _kv_args(self.kv_caches[l], self.vsources[l])
+        self.l_part.zero_()                  # splits without pages must read l = 0
+        _cabi.call("locks_decode_split", _cabi.ptr(q), q.stride(0), _cabi.ptr(k),
+                   _cabi.ptr(v), k.stride(0), k.stride(1), k.stride(2),
+                   _cabi.ptr(self.block_table), self.block_table.stride(0),
+                   _cabi.ptr(st.page_table), _cabi.ptr(st.page_cnt),
+                   _cabi.ptr(self.seq_lens), _cabi.ptr(self.m_part),
+                   _cabi.ptr(self.l_part), _cabi.ptr(self.acc_part), 1,
+                   int(self.n_kv), int(self.G), int(self.d), int(self.page),
+                   int(st.max_pages), int(self.split), 1, float(self.scale),
+                   _cabi.ptr(st.status), _cabi.stream())
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.packs.view(-1), self.packs[self.rank],
+                                        group=self.group)
+        out = self.out[l]
+        _cabi.call("locks_merge_gathered", _cabi.ptr(self.packs),
+                   int(self.pack_len), int(self.world), _cabi.ptr(out),
+                   out.stride(0), 1, int(self.n_kv), int(self.G), int(self.d),
+                   int(self.split), _cabi.stream())
+
+    # ---- one decode step ---------------------------------------------------
+    def _layers(self) -> None:
+        st = self.st
+        for l in range(len(self.kv_caches)):
+            rki4_score_only(st, l, self.q[l], self.block_table, self.seq_lens, 1,
+                            self.scale)
+            self._exchange_hmax()
+            nrmtopb_select(st, 1, has_hmax=True)
+            if self.nsh_loc == 0:
+                st.hmax.zero_()      # nothing scored here: the selector did not re-arm it
+            self._exchange_candidates()
+            self._decode_and_merge(l)
+
+    def step_eager(self) -> torch.Tensor:
+        self._layers()
+        return self.out
+
+    def capture(self) -> None:
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self._layers()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._layers()
+        self.graph = g
+
+    def step(self) -> torch.Tensor:
+        if self.graph is None:
+            self.capture()
+        self.graph.replay()
+        return self.out

@@ -202,6 +202,41 @@ def make_gqa_case(seed: int, shape: GqaShape, seq_lens, *, device="cpu",
                    needles=needles, scale=1.0 / math.sqrt(d))
 
 
+def make_gqa_shard(seed: int, shape: GqaShape, seq_len: int, p0: int, p1: int,
+                   *, device, n_layers: Optional[int] = None,
+                   spare_blocks: int = 3):
+    """Pages ``[p0, p1)`` of the ONE sequence ``make_gqa_case(seed, shape,
+    [seq_len])`` describes, as a paged cache of their own (context-parallel
+    shard).  Returns ``(kv_caches, q (L, 1, H, d), block_table (1, p1-p0))``;
+    local page j is global page p0 + j, blocks are a seeded permutation."""
+    L = shape.n_layers if n_layers is None else n_layers
+    page, n_kv, d = shape.page, shape.n_kv, shape.d
+    npg = (int(seq_len) + page - 1) // page
+    assert 0 <= p0 < p1 <= npg
+    n_loc = p1 - p0
+    NB = n_loc + spare_blocks
+    g = _gen("cpu", seed * 7 + 3 + 1009 * p0)
+    bt = torch.randperm(NB, generator=g)[:n_loc].to(torch.int32)[None]
+    blocks = bt[0].to(device=device, dtype=torch.int64)
+    caches, qs = [], []
+    for l in range(L):
+        K, V, q, _ = gqa_tokens(seed, l, 0, int(seq_len), shape, device)
+        t0, t1 = p0 * page, min(p1 * page, int(seq_len))
+        K, V = K[t0:t1], V[t0:t1]
+        pad = n_loc * page - (t1 - t0)
+        if pad:
+            z = torch.zeros(pad, n_kv, d, device=device, dtype=torch.bfloat16)
+            K, V = torch.cat([K, z]), torch.cat([V, z])
+        kvc = torch.zeros(NB, 2, page, n_kv, d, device=device,
+                          dtype=torch.bfloat16)
+        kvc[blocks, 0] = K.reshape(n_loc, page, n_kv, d)
+        kvc[blocks, 1] = V.reshape(n_loc, page, n_kv, d)
+        del K, V
+        caches.append(kvc)
+        qs.append(q[None])
+    return caches, torch.stack(qs), bt.to(device).contiguous()
+
+
 # --------------------------------------------------------------------------- #
 # MLA (latent KV) workloads                                                    #
 # --------------------------------------------------------------------------- #
