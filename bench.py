@@ -48,7 +48,7 @@ def workload(name: str, ctx: int | None):
         sh, c = synth.CONFIG0, 4096
     elif name == "c1":
         sh, c = synth.CONFIG1, 131072
-    elif name == "c4":
+    elif name in ("c4", "c4cp"):
         sh, c = synth.CONFIG4, 1048576
     else:
         raise SystemExit(f"unknown workload {name}")
@@ -455,6 +455,123 @@ def run_gpu(args, sh, seq_len):
     return line
 
 
+def run_gpu_cp(args, sh, seq_len):
+    """Workload c4cp: ONE sequence (config 4: 1M tokens) whose pages are split
+    over the ranks -- context parallel, three small exchanges per layer.  Strong
+    scaling: the job is the same at every N."""
+    import torch.distributed as dist
+    from locks import LocksConfig, synth
+    from locks.cp_hotpath import ContextParallelHotPath
+    from locks.parallel import partition_pages
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    npg = -(-seq_len // sh.page)
+    p0, p1 = partition_pages(npg, world)[rank]
+    caches, q, bt = synth.make_gqa_shard(1234, sh, seq_len, p0, p1, device=dev)
+    cfg = LocksConfig(budget_pages=sh.budget_pages, sink_pages=sh.sink_pages,
+                      window_pages=sh.window_pages)
+    cp = ContextParallelHotPath(caches, bt, seq_len=seq_len, p0=p0, p1=p1,
+                                n_kv=sh.n_kv, G=sh.G,
+                                scale=1.0 / math.sqrt(sh.d), cfg=cfg,
+                                transport=os.environ.get("LOCKS_CP_TRANSPORT",
+                                                         "peer"))
+    t_build = timed(lambda: cp.build_all(), 1)
+    cp.q.copy_(q)
+    cp.capture()
+    for _ in range(max(args.warmup, 3)):
+        cp.step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        cp.step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms_step = e0.elapsed_time(e1) / args.steps
+    q_host = q.cpu().pin_memory()
+    out_host = torch.empty(cp.out.shape, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        cp.q.copy_(q_host, non_blocking=True)
+        cp.step()
+        out_host.copy_(cp.out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms_e2e = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms_step, ms_e2e], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step, ms_e2e = float(t[0].item()), float(t[1].item())
+        dist.barrier()
+    status = int(cp.st.status.item())
+    clocks = sampler.stop() if rank == 0 else None
+    line = None
+    if rank == 0:
+        b_score, b_dec, b_dense, nsh, A = algo_bytes(sh, seq_len)
+        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        peak = (float(json.load(open(peaks_path))["hbm_gbs"])
+                if os.path.exists(peaks_path) else 6650.0)
+        L = sh.n_layers
+        line = {
+            "metric": "sparse_decode_tokens_per_s", "value": 1.0 / (ms_step * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+            "tpot_ms": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"c4cp: {L} layers, {sh.n_kv * sh.G}q/"
+                                   f"{sh.n_kv}kv, d{sh.d}, page {sh.page}, ONE "
+                                   f"sequence of ctx {seq_len - 1} split over "
+                                   f"{world} GPU(s), budget {sh.budget_pages}+"
+                                   f"{sh.sink_pages} sink+{sh.window_pages} "
+                                   f"recent = {A} pages attended",
+                       "l2_policy": "inputs larger than L2 "
+                                    f"({(b_score + b_dec) / 1e9:.2f} GB per step)",
+                       "sharding": "contiguous page ranges; per layer: all-reduce"
+                                   "(max) of head maxima, all-gather of <= b "
+                                   "candidates, all-gather of split-K partials; "
+                                   f"transport {cp.transport}"},
+            "clocks": clocks,
+            "e2e": {"value": 1.0 / (ms_e2e * 1e-3), "unit": "tokens/s",
+                    "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": q_host.numel() * 2,
+                    "d2h_bytes_per_step": out_host.numel() * 2},
+            "gpu_launches": 6 * L * args.steps,
+            "step_roofline": {
+                "algorithmic_bytes": b_score + b_dec,
+                "achieved_gbs": (b_score + b_dec) / (ms_step * 1e-3) / 1e9,
+                "frac_of_measured_peak_x_gpus":
+                    (b_score + b_dec) / (ms_step * 1e-3) / 1e9 / (peak * world)},
+            "us_per_layer": ms_step * 1e3 / L,
+            "build": {"bulk_ms": t_build},
+            "status_word": status,
+        }
+        print(json.dumps(line), flush=True)
+    sys.stdout.flush()
+    # leave without tearing NCCL down (graphs that captured collectives are alive)
+    os._exit(0)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -477,6 +594,9 @@ def main():
         if rank != 0:
             return
         print(json.dumps(run_reference(args, sh, seq_len)), flush=True)
+        return
+    if args.workload_name == "c4cp":
+        run_gpu_cp(args, sh, seq_len)
         return
     line = run_gpu(args, sh, seq_len)
     if line is not None:

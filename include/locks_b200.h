@@ -201,6 +201,50 @@ int locks_merge_gathered(const float* packs, int64_t pack_stride, int n_groups,
                          void* out, int64_t out_stride_req, int n_req, int n_kv,
                          int G, int head_dim, int split, locks_stream_t stream);
 
+/* ---- Context parallel (one sequence over several GPUs) -------------------------
+ * No counterpart in the reference (single GPU).  Every rank scores and selects
+ * on its own page range with the GLOBAL budget b (locks_rki4_score_bt after an
+ * all-reduce(max) of hmax, locks_topb_select); the two calls below sit on either
+ * side of the all-gather of the candidates.  Local page j is global page p0 + j;
+ * sink_loc / nsh_loc are the sequence's sink count and n_sel_hi in local page
+ * numbers, clamped to the range.
+ * locks_cp_pack: cand_rows = this rank's (2, n_kv, cap) floats: the combined
+ *   score and the global page of the first cap page-table entries that are
+ *   selectable pages; forced pages and empty slots travel as -inf.
+ * locks_cp_select: cand = the gathered rows, cand_stride floats apart.  Keeps, in
+ *   this rank's page table, its forced pages and those of its candidates that are
+ *   among the b best of ALL candidates by (score descending, page ascending) --
+ *   the exact-b tie rule of selection/select.py:183-222 -- in ascending page
+ *   order, -1 padded up to cap; page_cnt = entries kept. */
+int locks_cp_pack(const int32_t* page_table, const float* score, float* cand_rows,
+                  int n_kv, int max_pages, int cap, int sink_loc, int nsh_loc,
+                  int p0, locks_stream_t stream);
+int locks_cp_select(const float* cand, int64_t cand_stride, int32_t* page_table,
+                    int32_t* page_cnt, int world, int rank, int n_kv, int cap,
+                    int max_pages, int b, int sink_loc, int nsh_loc,
+                    locks_stream_t stream);
+
+/* Peer exchange for the context-parallel path: all-gather (mode 0) or
+ * element-wise unsigned max of uint32 words (mode 1) of a small payload, one
+ * kernel per rank over NVLink peer memory.  Every rank allocates one region
+ * (locks_cp_region_bytes gives the size; locks_cp_alloc: cudaMalloc, zeroed),
+ * exports it (locks_cp_ipc_export: 64-byte CUDA IPC handle) and opens the
+ * peers' regions (locks_cp_ipc_open); peers[r] is rank r's region as seen from
+ * this process (peers[rank] = the local pointer).  All ranks must issue the same
+ * sequence of exchanges on a region, at most 8 ranks.  nbytes, slot_bytes:
+ * multiples of 16, nbytes <= slot_bytes.  mode 0: out = (world, nbytes);
+ * mode 1: out = nbytes.  A rank that does not see all peers within about two
+ * seconds sets *status to LOCKS_ST_WAIT_TIMEOUT and returns (out undefined). */
+int locks_cp_region_bytes(int slot_bytes, int64_t* out);
+int locks_cp_alloc(int64_t bytes, void** out);
+int locks_cp_free(void* region);
+int locks_cp_ipc_export(void* region, unsigned char* handle64);
+int locks_cp_ipc_open(const unsigned char* handle64, void** out);
+int locks_cp_ipc_close(void* peer_region);
+int locks_cp_exchange(void* const* peers, int world, int rank, const void* payload,
+                      int nbytes, int slot_bytes, void* out, int mode, int* status,
+                      locks_stream_t stream);
+
 /* Split decode + merge WITHOUT caller-provided partial buffers.  No counterpart
  * in the reference (its kernels always take caller-allocated partials).
  * For callers that cannot allocate device memory -- e.g. a host-language

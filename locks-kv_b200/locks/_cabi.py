@@ -37,6 +37,15 @@ _SIGNATURES = {
                             _P], 1),
     "locks_merge_splits": ([_P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I,
                             _P], 1),
+    "locks_cp_pack": ([_P, _P, _P, _I, _I, _I, _I, _I, _I, _P], 1),
+    "locks_cp_select": ([_P, _L, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P], 1),
+    "locks_cp_region_bytes": ([_I, _P], 0),
+    "locks_cp_alloc": ([_L, _P], 0),
+    "locks_cp_free": ([_P], 0),
+    "locks_cp_ipc_export": ([_P, _P], 0),
+    "locks_cp_ipc_open": ([_P, _P], 0),
+    "locks_cp_ipc_close": ([_P], 0),
+    "locks_cp_exchange": ([_P, _I, _I, _P, _I, _I, _P, _I, _P, _P], 1),
     "locks_merge_gathered": ([_P, _L, _I, _P, _L, _I, _I, _I, _I, _I, _P], 1),
     "locks_decode_fused": ([_P, _L, _P, _P, _L, _L, _L, _P, _L, _P, _P, _P, _P,
                             _L, _I, _I, _I, _I, _I, _I, _F, _P, _P], 1),

@@ -32,7 +32,6 @@ from . import _cabi
 from .attention import ResidentVSource
 from .attention.decode import _kv_args
 from .config import LocksConfig
-from .parallel import global_select
 from .selection import Rki4State, rki4_build_bulk, rki4_score_only
 from .selection.select import nrmtopb_select
 
@@ -63,7 +62,8 @@ class ContextParallelHotPath:
 
     def __init__(self, kv_caches: List[torch.Tensor], block_table: torch.Tensor,
                  *, seq_len: int, p0: int, p1: int, n_kv: int, G: int,
-                 scale: float, cfg: LocksConfig, group=None, split: int = 4):
+                 scale: float, cfg: LocksConfig, group=None, split: int = 2,
+                 transport: str = "peer"):
         dev = kv_caches[0].device
         self.device, self.cfg, self.group = dev, cfg, group
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -111,14 +111,33 @@ class ContextParallelHotPath:
         self.pack_len = (n_ml * (2 + d) + 3) // 4 * 4
         self.packs = torch.zeros(self.world, self.pack_len, device=dev,
                                  dtype=torch.float32)
-        mine = self.packs[self.rank]
+        # (the peer transport gathers from a buffer of its own into `packs`)
+        self.pack_mine = torch.zeros(self.pack_len, device=dev, dtype=torch.float32)
+        mine = self.pack_mine if (transport == "peer" and self.world > 1) \
+            else self.packs[self.rank]
         self.m_part = mine[:n_ml]
         self.l_part = mine[n_ml:2 * n_ml]
         self.acc_part = mine[2 * n_ml:2 * n_ml + n_ml * d]
-        self.cand = torch.zeros(self.world, 2, n_kv, self.cap, device=dev,
-                                dtype=torch.float32)
-        self._col = torch.arange(self.cap, device=dev)[None, :]
+        cand_len = (2 * n_kv * self.cap + 3) // 4 * 4     # 16-byte multiple
+        self.cand_flat = torch.zeros(self.world, cand_len, device=dev,
+                                     dtype=torch.float32)
+        self.cand = self.cand_flat
+        self.cand_mine = torch.zeros(cand_len, device=dev, dtype=torch.float32)
+        self.cand_stride = cand_len
         self.graph: Optional[torch.cuda.CUDAGraph] = None
+        # transport of the three exchanges: "peer" = one fused kernel per rank
+        # over NVLink peer memory (locks_cp_exchange), "nccl" = library
+        # collectives (kept as the baseline the fused kernel is measured against)
+        assert transport in ("peer", "nccl")
+        self.transport = transport if self.world > 1 else "none"
+        self.hm_pad = None
+        if self.transport == "peer":
+            from .peer import PeerExchange
+            slot = max(self.pack_len * 4, self.cand[0].numel() * 4, 64 * 4)
+            self.px = PeerExchange(slot, group)
+            # the keys padded to a multiple of 16 bytes
+            n_hm = (st.hmax.numel() + 3) // 4 * 4
+            self.hm_pad = torch.zeros(n_hm, device=dev, dtype=torch.int32)
 
     # ---- summaries ---------------------------------------------------------
     def build_all(self) -> int:
@@ -134,6 +153,15 @@ class ContextParallelHotPath:
         if self.world == 1:
             return
         hm = self.st.hmax
+        if self.transport == "peer":
+            n = hm.numel()
+            if self.hm_pad.numel() == n:
+                self.px.all_max_u32(hm.view(-1), self.st.status)
+            else:
+                self.hm_pad[:n].copy_(hm.view(-1))
+                self.px.all_max_u32(self.hm_pad, self.st.status)
+                hm.view(-1).copy_(self.hm_pad[:n])
+            return
         hm.bitwise_xor_(_SIGN)
         dist.all_reduce(hm, op=dist.ReduceOp.MAX, group=self.group)
         hm.bitwise_xor_(_SIGN)
@@ -141,32 +169,21 @@ class ContextParallelHotPath:
     def _exchange_candidates(self) -> None:
         """Local top-b list -> global exact-b cut -> this rank's final list."""
         st, cap = self.st, self.cap
-        tab = st.page_table[0, :, :cap]                       # (n_kv, cap) local ids
-        live = tab >= 0
-        selectable = live & (tab >= self.sink_loc) & (tab < self.nsh_loc)
-        sc = torch.gather(st.score[0], 1, tab.clamp(min=0).long())
-        neg = torch.full_like(sc, float("-inf"))
-        mine = self.cand[self.rank]
-        mine[0] = torch.where(selectable, sc, neg)
-        # page ids travel as exact small floats (< 2^24 pages)
-        mine[1] = torch.where(selectable, (tab + self.p0).float(),
-                              torch.full_like(sc, float(1 << 24)))
-        if self.world > 1:
+        mine = self.cand_mine if self.transport == "peer" else self.cand[self.rank]
+        _cabi.call("locks_cp_pack", _cabi.ptr(st.page_table), _cabi.ptr(st.score),
+                   _cabi.ptr(mine), int(self.n_kv), int(st.max_pages), int(cap),
+                   int(self.sink_loc), int(self.nsh_loc), int(self.p0),
+                   _cabi.stream())
+        if self.transport == "peer":
+            self.px.all_gather(self.cand_mine, self.cand, self.st.status)
+        elif self.world > 1:
             dist.all_gather_into_tensor(self.cand.view(-1), mine.reshape(-1),
                                         group=self.group)
-        all_s = self.cand[:, 0].permute(1, 0, 2).reshape(self.n_kv, -1)
-        all_p = self.cand[:, 1].permute(1, 0, 2).reshape(self.n_kv, -1)
-        keep = global_select(all_s, all_p, self.b)
-        keep_mine = keep.view(self.n_kv, self.world, cap)[:, self.rank]
-        final = live & (~selectable | keep_mine)
-        # stable compaction of the kept entries (ascending page order is kept)
-        pos = torch.cumsum(final, dim=1) - 1
-        dst = torch.where(final, pos, torch.full_like(pos, cap))
-        buf = torch.full((self.n_kv, cap + 1), -1, dtype=tab.dtype,
-                         device=tab.device)
-        buf.scatter_(1, dst, tab)
-        tab.copy_(buf[:, :cap])
-        st.page_cnt[0] = final.sum(dim=1).to(st.page_cnt.dtype)
+        _cabi.call("locks_cp_select", _cabi.ptr(self.cand),
+                   int(self.cand_stride), _cabi.ptr(st.page_table), _cabi.ptr(st.page_cnt),
+                   int(self.world), int(self.rank), int(self.n_kv), int(cap),
+                   int(st.max_pages), int(self.b), int(self.sink_loc),
+                   int(self.nsh_loc), _cabi.stream())
 
     def _decode_and_merge(self, l: int) -> None:
         st = self.st
@@ -182,7 +199,9 @@ class ContextParallelHotPath:
                    int(self.n_kv), int(self.G), int(self.d), int(self.page),
                    int(st.max_pages), int(self.split), 1, float(self.scale),
                    _cabi.ptr(st.status), _cabi.stream())
-        if self.world > 1:
+        if self.transport == "peer":
+            self.px.all_gather(self.pack_mine, self.packs, self.st.status)
+        elif self.world > 1:
             dist.all_gather_into_tensor(self.packs.view(-1), self.packs[self.rank],
                                         group=self.group)
         out = self.out[l]

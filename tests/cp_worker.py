@@ -39,7 +39,8 @@ def main() -> int:
     p0, p1 = partition_pages(npg, world)[rank]
     caches, q, bt = synth.make_gqa_shard(11, shape, seq_len, p0, p1, device=dev)
     cp = ContextParallelHotPath(caches, bt, seq_len=seq_len, p0=p0, p1=p1,
-                                n_kv=shape.n_kv, G=shape.G, scale=scale, cfg=cfg)
+                                n_kv=shape.n_kv, G=shape.G, scale=scale, cfg=cfg,
+                                transport=os.environ.get("CP_TRANSPORT", "peer"))
     cp.build_all()
     cp.q.copy_(q)
     out_eager = cp.step_eager().clone()
@@ -79,7 +80,7 @@ def main() -> int:
                       f" extra {extra}, missing {miss})")
                 ok = False
         err = (out_eager.float() - ref.float()).abs().max().item()
-        print(f"context parallel x{world}: seq {seq_len}, {npg} pages, "
+        print(f"context parallel x{world} ({cp.transport}): seq {seq_len}, {npg} pages, "
               f"max |out - single GPU| = {err:.3e}")
         if not err <= 2e-2:              # bf16 outputs, different merge order
             ok = False
