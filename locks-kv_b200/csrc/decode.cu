@@ -468,7 +468,7 @@ __global__ void __launch_bounds__(HD) merge_kernel(const MergeParams p) {
         const int pps = max((cnt + p.split - 1) / p.split, p.pps_min);
         n_act = (cnt + pps - 1) / pps;
     }
-    const int n_tot = n_act * p.n_groups;
+    const int n_tot = n_act * max(p.n_groups, 1);
     const int64_t base = row * p.split * p.G + g;
     float M = -INFINITY, Ls = 0.f;
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);

@@ -1,24 +1,28 @@
 // Per-step page parameters, GQA score combine and exact top-b page selection.
 //
-// topb kernel: one thread-block CLUSTER (1, 2, 4 or 8 CTAs of 1024 threads) per
-// (request, kv-head); CTA c owns a contiguous slice of the pages and keeps the
-// slice's 32-bit order-preserving score keys in shared memory, so every pass
-// after the first runs out of shared memory.  A single CTA is used whenever the
-// keys of one (request, kv-head) fit (<= 16384 pages); longer contexts spread
-// over a cluster and meet through distributed shared memory.
-//   1. combine the per-head scores of the slice into one score per page (nrm
-//      or max); the per-head maxima come from the scorer's published keys or
-//      from a (cluster-wide) sweep,
-//   2. b-th largest score of the selectable range by a 3-pass MSD radix select
-//      (11/11/10 bits): shared-memory histogram per CTA; in a cluster, CTA c
-//      sums bin slice c of all CTAs (reduce-scatter through DSMEM), the slice
-//      totals locate the slice that holds the digit and that slice alone is
-//      read back,
-//   3. keep flags with the exact-b tie rule; each warp owns consecutive groups
-//      of 32 pages, so ballots give the in-group ranks, and warp / CTA totals
-//      give the tie ranks and the output slots; ascending compaction, -1
-//      padding.
-// No global scratch and a single launch for any page count.
+// topb kernel, one launch for any page count, no global scratch.  Scores become
+// 32-bit order-preserving keys that live in shared memory from the combine on.
+//
+// Rows of up to 16 384 pages -- SINGLE-CTA selection (512 threads).  Up to four
+// CTAs of a thread-block cluster share the GQA combine (nrm or max; the per-head
+// maxima come from the keys the scorer published, or from a sweep) and push
+// their keys into CTA 0 through distributed shared memory; CTA 0 selects alone:
+//   * the page classes are folded into the keys (0 = not a page of the row,
+//     0xFFFFFFFF = sink / recent page, always kept), so the later passes test
+//     nothing but the key;
+//   * b-th largest key by an MSD radix select (11/11/10 bits) over four
+//     interleaved histogram copies (fewer same-address atomics); the digit
+//     search runs on 8 warps, each thread owning 8 consecutive bins; a pass whose
+//     digit bin is taken whole ends the search (the usual case after 22 bits);
+//   * keep flags and ascending compaction in one count loop, ONE barrier and one
+//     write loop: every warp derives all warps' tie ranks and output slots from
+//     the per-warp totals by itself; four consecutive keys per lane.
+//
+// Longer rows -- DISTRIBUTED selection: a cluster of 2, 4 or 8 CTAs of 1024
+// threads, CTA c keeps and selects the keys of its page slice; per radix pass
+// CTA c sums bin slice c of all CTAs (reduce-scatter through DSMEM), the slice
+// totals locate the slice that holds the digit and that slice alone is read
+// back; tie ranks and output slots are exchanged the same way.
 #include <cooperative_groups.h>
 
 #include "common.cuh"
