@@ -3,10 +3,15 @@
 // topb kernel, one launch for any page count, no global scratch.  Scores become
 // 32-bit order-preserving keys that live in shared memory from the combine on.
 //
-// Rows of up to 16 384 pages -- SINGLE-CTA selection (512 threads).  Up to four
+// Rows of up to 16 384 pages -- OWNER mode (512 threads per CTA).  Up to four
 // CTAs of a thread-block cluster share the GQA combine (nrm or max; the per-head
 // maxima come from the keys the scorer published, or from a sweep) and push
-// their keys into CTA 0 through distributed shared memory; CTA 0 selects alone:
+// their keys into CTA 0 through distributed shared memory; CTA 0 selects alone.
+// Longer rows -- SLICED mode: a cluster of 2, 4 or 8 CTAs, CTA c keeps and
+// selects the keys of its page slice with the same code; per radix pass every CTA
+// adds its non-empty bins to totals kept by CTA 0 (DSMEM atomics), CTA 0 finds
+// the digit and stores it into every CTA; the per-CTA tie and kept totals are
+// exchanged once more for the tie ranks and output slots.  Either way:
 //   * the page classes are folded into the keys (0 = not a page of the row,
 //     0xFFFFFFFF = sink / recent page, always kept), so the later passes test
 //     nothing but the key;
@@ -17,12 +22,6 @@
 //   * keep flags and ascending compaction in one count loop, ONE barrier and one
 //     write loop: every warp derives all warps' tie ranks and output slots from
 //     the per-warp totals by itself; four consecutive keys per lane.
-//
-// Longer rows -- DISTRIBUTED selection: a cluster of 2, 4 or 8 CTAs of 1024
-// threads, CTA c keeps and selects the keys of its page slice; per radix pass
-// CTA c sums bin slice c of all CTAs (reduce-scatter through DSMEM), the slice
-// totals locate the slice that holds the digit and that slice alone is read
-// back; tie ranks and output slots are exchanged the same way.
 #include <cooperative_groups.h>
 
 #include "common.cuh"
@@ -32,12 +31,8 @@ namespace cg = cooperative_groups;
 namespace locks {
 namespace {
 
-constexpr int SEL_THREADS = 1024;            // distributed (cluster) selection
-#ifndef LOCKS_SINGLE_THREADS
-#define LOCKS_SINGLE_THREADS 512
-#endif
-constexpr int SINGLE_THREADS = LOCKS_SINGLE_THREADS;   // single-CTA selection
-constexpr int SEL_WARPS = SEL_THREADS / 32;
+constexpr int SEL_THREADS = 512;
+constexpr int SEL_WARPS = 32;                // capacity of the per-warp arrays
 constexpr int MAX_G = 16;
 
 __global__ void derive_kernel(const int32_t* __restrict__ seq_lens, int n_req,
@@ -91,15 +86,16 @@ __device__ long long g_sel_ts[32];
 #define SEL_TS(i)
 #endif
 
-constexpr int RBITS0 = 11, RBITS1 = 11, RBITS2 = 10;
-constexpr int NBINS = 1 << RBITS0;                // 2048 (largest digit)
-constexpr int MAX_CL = 8;
 constexpr int KEYS_PER_CTA = 16384;               // shared-memory key capacity
 // single-CTA selection: the latency-bound radix / compaction steps run on a few
 // warps with many keys per thread (barriers and scans cost per warp, not per key)
 constexpr int AW = 8;                             // active warps
 constexpr int ATH = AW * 32;
 constexpr int HCOPIES = 4;                        // histogram copies, by lane & 3
+
+constexpr int RBITS0 = 11, RBITS1 = 11, RBITS2 = 10;
+constexpr int NBINS = 1 << RBITS0;                // 2048 (largest digit)
+constexpr int MAX_CL = 8;
 
 struct SelSmem {
     int hist[NBINS];               // this CTA's histogram of the current digit
@@ -115,56 +111,9 @@ struct SelSmem {
     uint32_t sh_prefix;
     int sh_k;
     int sh_i0, sh_i1, sh_i2;
+    int x_eq_all[MAX_CL];          // sliced mode: per-CTA tie / sure-kept totals
+    int x_sure_all[MAX_CL];
 };
-
-// inclusive scan of 32 per-warp totals by warp 0 (in place); returns nothing,
-// callers read exclusive bases as (w ? a[w-1] : 0) and the total as a[31]
-__device__ __forceinline__ void scan_warp_totals(int* a) {
-    if (threadIdx.x < 32) {
-        int v = a[threadIdx.x];
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int t = __shfl_up_sync(0xffffffffu, v, o);
-            if ((int)threadIdx.x >= o) v += t;
-        }
-        a[threadIdx.x] = v;
-    }
-}
-
-// Among bins [0, nb) of `h` (nb a multiple of 64, <= 2048) find the largest
-// bin d with  count(bins > d) < k <= count(bins >= d);  `above0` pages already
-// lie above bin nb-1.  Warp w owns the 64 bins just below nb-64w.  On return
-// (after the trailing __syncthreads) sm.sh_i0 = d, sm.sh_i1 = k - count above d.
-__device__ __forceinline__ void find_digit(SelSmem& sm, const int* h, int nb,
-                                           int above0, int k) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int hi_bin = nb - 1 - 64 * warp - 2 * lane;      // and hi_bin - 1
-    int ca = 0, cb = 0;
-    if (hi_bin >= 1) { ca = h[hi_bin]; cb = h[hi_bin - 1]; }
-    int inc = ca + cb;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int t = __shfl_up_sync(0xffffffffu, inc, o);
-        if (lane >= o) inc += t;
-    }
-    if (lane == 31) sm.wtot[warp] = inc;
-    __syncthreads();
-    // every warp scans the 32 warp totals itself (no second barrier)
-    const int wv = sm.wtot[lane];
-    int winc = wv;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int t = __shfl_up_sync(0xffffffffu, winc, o);
-        if (lane >= o) winc += t;
-    }
-    const int base = above0 + __shfl_sync(0xffffffffu, winc - wv, warp);
-    const int above = base + inc - (ca + cb);
-    if (above < k && k <= above + ca + cb) {
-        if (k <= above + ca) { sm.sh_i0 = hi_bin; sm.sh_i1 = k - above; }
-        else { sm.sh_i0 = hi_bin - 1; sm.sh_i1 = k - above - ca; }
-    }
-    __syncthreads();
-}
 
 __device__ __forceinline__ void bar_active() {
     asm volatile("bar.sync 1, %0;" ::"n"(ATH) : "memory");
@@ -182,6 +131,7 @@ constexpr int HSLOTS = NBINS + NBINS / 8;
 // the buffer is zero again afterwards.  The caller's next CTA-wide barrier
 // publishes sm.sh_i0 = digit d, sm.sh_i1 = k - count(bins > d), sm.sh_i2 =
 // count(d).
+template <bool COPIES>
 __device__ __forceinline__ void find_digit_active(SelSmem& sm, int* h4, int nb,
                                                   int k) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -193,10 +143,15 @@ __device__ __forceinline__ void find_digit_active(SelSmem& sm, int* h4, int nb,
     for (int i = 0; i < 8; ++i) {
         c[i] = 0;
         if (i < bpl) {
-            int4* q = reinterpret_cast<int4*>(h4) + hslot(hb - i);
-            const int4 v = *q;
-            c[i] = v.x + v.y + v.z + v.w;
-            *q = make_int4(0, 0, 0, 0);
+            if (COPIES) {
+                int4* q = reinterpret_cast<int4*>(h4) + hslot(hb - i);
+                const int4 v = *q;
+                c[i] = v.x + v.y + v.z + v.w;
+                *q = make_int4(0, 0, 0, 0);
+            } else {                  // one plain counter per bin (cluster totals)
+                c[i] = h4[hb - i];
+                h4[hb - i] = 0;
+            }
         }
         mine += c[i];
     }
@@ -227,6 +182,25 @@ __device__ __forceinline__ void find_digit_active(SelSmem& sm, int* h4, int nb,
                 } else {
                     above += c[i];
                 }
+            }
+        }
+    }
+}
+
+// Sliced selection: the first AW warps add this CTA's bin counts (the copies
+// summed) to the cluster totals kept by CTA 0 and clear the bins on the way.
+__device__ __forceinline__ void push_bins(int* h4, int nb, int* tot0) {
+    const int bpl = nb / ATH;
+    const int hb = nb - 1 - (int)threadIdx.x * bpl;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        if (i < bpl) {
+            int4* q = reinterpret_cast<int4*>(h4) + hslot(hb - i);
+            const int4 v = *q;
+            const int c = v.x + v.y + v.z + v.w;
+            if (c) {
+                *q = make_int4(0, 0, 0, 0);
+                atomicAdd(&tot0[hb - i], c);
             }
         }
     }
@@ -333,9 +307,10 @@ __device__ __forceinline__ void sweep_max_groups(
         else { constexpr int GT = 16; CALL; }                \
     } while (0)
 
-// NT threads per CTA.  SINGLE: one CTA selects the whole row (owner mode or no
-// cluster); otherwise every CTA of the cluster selects its slice (NT = 1024).
-template <int NT, bool SINGLE>
+// NT threads per CTA.  OWNER: CTA 0 selects the whole row, the other CTAs of the
+// cluster only combine (or there is no cluster); otherwise every CTA of the
+// cluster keeps and selects the keys of its page slice.
+template <int NT, bool OWNER>
 __global__ void __launch_bounds__(NT)
 topb_kernel(const SelParams p) {
     constexpr int NW = NT / 32;
@@ -367,8 +342,9 @@ topb_kernel(const SelParams p) {
     // CTA of the cluster combines a slice of the scores and pushes the keys into
     // CTA 0 through distributed shared memory; CTA 0 alone selects, the helpers
     // write the -1 padding that no selection can reach and leave.
-    // Distributed mode (long contexts): every CTA keeps and selects its slice.
-    const bool owner = SINGLE && CL_phys > 1;
+    // Sliced mode (long contexts): every CTA keeps and selects its slice; the
+    // histograms meet in CTA 0, which finds each digit and tells the others.
+    const bool owner = OWNER && CL_phys > 1;
     // slice whose scores this CTA combines
     const int cper = (((span + CL_phys - 1) / CL_phys) + 31) & ~31;
     const int cs0 = min(c_phys * cper, span), cs1 = min(cs0 + cper, span);
@@ -386,35 +362,32 @@ topb_kernel(const SelParams p) {
     const int gpw = (n_grp + NW - 1) / NW;
     const int g_beg = min(warp * gpw, n_grp), g_end = min(g_beg + gpw, n_grp);
 
-    constexpr bool single = SINGLE;                 // one CTA selects the row
+    const bool selects = !owner || c_phys == 0;     // this CTA runs a selection
     int* h4 = reinterpret_cast<int*>(keys + p.key_cap);
-    if constexpr (single) {
-        if (c_phys == 0)
-            for (int i = tid; i < HSLOTS; i += NT)
-                reinterpret_cast<int4*>(h4)[i] = make_int4(0, 0, 0, 0);
-    } else {
-        for (int i = tid; i < NBINS; i += NT) sm.hist[i] = 0;
+    if (selects) {
+        for (int i = tid; i < HSLOTS; i += NT)
+            reinterpret_cast<int4*>(h4)[i] = make_int4(0, 0, 0, 0);
+        for (int i = tid; i < NBINS; i += NT) sm.tot[i] = 0;
     }
     pdl_wait();                  // score_h / hmax / score come from the scorer
     SEL_TS(22);
     TL_MARK(g_sel_tl, 1);
 
-    // Single-CTA selection folds the page classes into the keys: 0 = not a page
-    // of the row, 0xFFFFFFFF = always kept (sink / recent pages, short rows),
-    // anything between = a selectable page's score key.
+    // The page classes are folded into the keys: 0 = not a page of the row,
+    // 0xFFFFFFFF = always kept (sink / recent pages, short rows), anything
+    // between = a selectable page's score key.
     auto fin_key = [&](uint32_t key, int i) -> uint32_t {
-        if (!single) return key;
         if (i >= npg) return 0u;
         if (keep_all || i < lo || i >= hi) return 0xFFFFFFFFu;
         return min(max(key, 1u), 0xFFFFFFFEu);
     };
-    if (single && c_phys == 0)       // key slots past the row read as "no page"
-        for (int i = span + tid; i < p.key_cap; i += NT) keys[i] = 0u;
+    if (selects)                     // key slots past the slice read as "no page"
+        for (int i = n_loc + tid; i < p.key_cap; i += NT) keys[i] = 0u;
 
     // ---------------- 1. GQA combine -> score[slice], keys[slice] --------------
     // remote shared memory may only be touched once every CTA of the cluster
     // runs: the nrm branch has a cluster barrier of its own, the others get one
-    if (owner && !(p.combine == LOCKS_COMBINE_NRM && n_comb > 0)) cluster.sync();
+    if (CL_phys > 1 && !(p.combine == LOCKS_COMBINE_NRM && n_comb > 0)) cluster.sync();
     if (p.combine == LOCKS_COMBINE_NRM && n_comb > 0) {
         const float* sh = p.score_h + row * (int64_t)G * MP;
         const bool published = p.hmax != nullptr;
@@ -447,7 +420,7 @@ topb_kernel(const SelParams p) {
         // all of them run (remote shared memory may be written) and, for the
         // scorer's keys, that all of them have read hmax (CTA 0 re-arms it)
         auto sync_hm = [&]() {
-            if (CL_phys > 1 && (published || owner)) cluster.sync();
+            if (CL_phys > 1) cluster.sync();
             else __syncthreads();
             if (published && c_phys == 0 && tid < G) p.hmax[row * G + tid] = 0u;
         };
@@ -493,305 +466,183 @@ topb_kernel(const SelParams p) {
     }
     SEL_TS(1);
 
-    // selectable part of the slice, in local indices
-    const int q0 = max(s0, lo) - s0, q1 = min(s1, hi) - s0;
-
-    if constexpr (single) {
-        // ============ single-CTA selection (s0 = 0: local index = page) ==========
-        // The per-key loops run on all warps, 4 consecutive keys per lane; the
-        // digit search runs on the first AW warps only.
-        int32_t* tab = p.page_table + row * MP;
-        // ---- 2. threshold: keys > tau_key are kept, `quota` of the keys equal
-        // to it (in ascending page order) as well
-        uint32_t tau_key = 0u;   // below every page's key: every page is kept
-        int quota = 0;
-        if (!keep_all && b <= 0) {
-            tau_key = 0xFFFFFFFEu;   // only the always-kept pages lie above
-        } else if (!keep_all && b < L) {
-            uint32_t prefix = 0u, mask = 0u;
-            int k = b, shift = 32;
-            bool whole_bin = false;
-#pragma unroll 1
-            for (int pass = 0; pass < 3 && !whole_bin; ++pass) {
-                const int bits = (pass == 0) ? RBITS0 : (pass == 1) ? RBITS1 : RBITS2;
-                const int nb = 1 << bits;
-                shift -= bits;
-                const uint32_t dmask = (uint32_t)nb - 1u;
-                for (int base = 4 * tid; base < n_loc; base += 4 * NT) {
-                    const uint4 kv = *reinterpret_cast<const uint4*>(&keys[base]);
-                    const uint32_t kk[4] = {kv.x, kv.y, kv.z, kv.w};
-#pragma unroll
-                    for (int s = 0; s < 4; ++s) {
-                        const uint32_t key = kk[s];
-                        if (key - 1u < 0xFFFFFFFEu && (key & mask) == prefix)
-                            atomicAdd(&h4[(hslot((key >> shift) & dmask) << 2) |
-                                          (lane & 3)], 1);
-                    }
-                }
-                SEL_TS(2 + 4 * pass);
-                __syncthreads();
-                SEL_TS(3 + 4 * pass);
-                if (warp < AW) find_digit_active(sm, h4, nb, k);
-                SEL_TS(4 + 4 * pass);
-                __syncthreads();
-                prefix |= (uint32_t)sm.sh_i0 << shift;
-                k = sm.sh_i1;
-                mask |= dmask << shift;
-                // the bin is taken whole: no finer digit and no tie rule needed
-                whole_bin = (sm.sh_i2 == k);
-                SEL_TS(5 + 4 * pass);
-            }
-            if (whole_bin) { tau_key = prefix ? prefix - 1u : 0u; quota = 0; }
-            else { tau_key = prefix; quota = k; }
-        }
-        SEL_TS(13);
-
-        // ---- 3. keep flags + ascending compaction.  Warp w owns a contiguous
-        // run of keys and walks it 128 keys at a time.
-        const uint32_t lt_mask = (1u << lane) - 1u;
-        const int WS = (((n_loc + NW - 1) / NW) + 127) & ~127;
-        const int w0 = min(warp * WS, n_loc), w1 = min(w0 + WS, n_loc);
-        const bool ties = quota > 0;
-        int c_sure = 0, c_eq = 0;
-        for (int it = w0; it < w1; it += 128) {
-            const uint4 kv = *reinterpret_cast<const uint4*>(&keys[it + 4 * lane]);
-            c_sure += (kv.x > tau_key) + (kv.y > tau_key) + (kv.z > tau_key) +
-                      (kv.w > tau_key);
-            c_eq += (kv.x == tau_key) + (kv.y == tau_key) + (kv.z == tau_key) +
-                    (kv.w == tau_key);
-        }
-#pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) {
-            c_eq += __shfl_xor_sync(0xffffffffu, c_eq, o);
-            c_sure += __shfl_xor_sync(0xffffffffu, c_sure, o);
-        }
-        if (lane == 0) { sm.wtot[warp] = c_eq; sm.wtot2[warp] = c_sure; }
-        SEL_TS(15);
-        __syncthreads();
-        // every warp derives all warps' tie ranks and output slots by itself
-        const int e_w = (lane < NW) ? sm.wtot[lane] : 0;
-        const int s_w = (lane < NW) ? sm.wtot2[lane] : 0;
-        int einc = e_w;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int t = __shfl_up_sync(0xffffffffu, einc, o);
-            if (lane >= o) einc += t;
-        }
-        const int k_w = s_w + min(max(quota - (einc - e_w), 0), e_w);
-        int kinc = k_w;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int t = __shfl_up_sync(0xffffffffu, kinc, o);
-            if (lane >= o) kinc += t;
-        }
-        int pos = __shfl_sync(0xffffffffu, kinc - k_w, warp);
-        int eqr = __shfl_sync(0xffffffffu, einc - e_w, warp);
-        const int cnt = __shfl_sync(0xffffffffu, kinc, 31);
-        SEL_TS(17);
-        for (int it = w0; it < w1; it += 128) {
-            const int base = it + 4 * lane;
-            const uint4 kv = *reinterpret_cast<const uint4*>(&keys[base]);
-            const uint32_t kk[4] = {kv.x, kv.y, kv.z, kv.w};
-            bool keep[4];
-#pragma unroll
-            for (int s = 0; s < 4; ++s) keep[s] = kk[s] > tau_key;
-            if (ties) {
-                uint32_t eb[4];
-                int lower = 0, total = 0;
-#pragma unroll
-                for (int s = 0; s < 4; ++s) {
-                    eb[s] = __ballot_sync(0xffffffffu, kk[s] == tau_key);
-                    lower += __popc(eb[s] & lt_mask);
-                    total += __popc(eb[s]);
-                }
-                int rank = eqr + lower;              // ties before (lane, s = 0)
-#pragma unroll
-                for (int s = 0; s < 4; ++s) {
-                    if (kk[s] == tau_key) { keep[s] = rank < quota; ++rank; }
-                }
-                eqr += total;
-            }
-            int slot = pos, total = 0;
-#pragma unroll
-            for (int s = 0; s < 4; ++s) {
-                const uint32_t kb = __ballot_sync(0xffffffffu, keep[s]);
-                slot += __popc(kb & lt_mask);
-                total += __popc(kb);
-            }
-#pragma unroll
-            for (int s = 0; s < 4; ++s) {
-                if (keep[s]) tab[slot++] = base + s;
-            }
-            pos += total;
-        }
-        // -1 padding: in owner mode the helper CTAs did the part no selection
-        // can reach
-        {
-            const int cnt_max = keep_all ? npg
-                                         : min(npg, (npg - L) + min(max(b, 0), L));
-            const int pad_end = owner ? cnt_max : MP;
-            for (int i = cnt + tid; i < pad_end; i += NT) tab[i] = -1;
-        }
-        if (tid == 0) p.page_cnt[row] = cnt;
-        SEL_TS(18);
-        SEL_TS(19);
-        TL_MARK(g_sel_tl, 2);
-        return;
-    }
-
-    if constexpr (!single) {
-    // ---------------- 2. threshold key (b-th largest of [lo, hi)) -------------
-    uint32_t tau_key = 0u;       // below every real key: everything is "> tau"
+    // ============ selection over keys[0, n_loc) (local index j = page - s0) ======
+    // The per-key loops run on all warps, 4 consecutive keys per lane; the digit
+    // search runs on the first AW warps (of CTA 0 in sliced mode).
+    int32_t* tab = p.page_table + row * MP;
+    // ---- 2. threshold: keys > tau_key are kept, `quota` of the keys equal to it
+    // (in ascending page order) as well
+    uint32_t tau_key = 0u;       // below every page's key: every page is kept
     int quota = 0;
     if (!keep_all && b <= 0) {
-        tau_key = 0xFFFFFFFFu;   // above every real key: no selectable page kept
+        tau_key = 0xFFFFFFFEu;   // only the always-kept pages lie above
     } else if (!keep_all && b < L) {
         uint32_t prefix = 0u, mask = 0u;
-        int k = b;
-        int shift = 32;
+        int k = b, shift = 32;
+        bool whole_bin = false;
+        int* tot0 = (CL > 1) ? cluster.map_shared_rank(sm.tot, 0) : sm.tot;
 #pragma unroll 1
-        for (int pass = 0; pass < 3; ++pass) {
+        for (int pass = 0; pass < 3 && !whole_bin; ++pass) {
             const int bits = (pass == 0) ? RBITS0 : (pass == 1) ? RBITS1 : RBITS2;
             const int nb = 1 << bits;
             shift -= bits;
             const uint32_t dmask = (uint32_t)nb - 1u;
-            {
-                for (int i = tid; i < nb; i += NT) { sm.hist[i] = 0; sm.tot[i] = 0; }
-                __syncthreads();
-                for (int j = q0 + tid; j < q1; j += NT) {
-                    const uint32_t key = keys[j];
-                    if ((key & mask) == prefix)
-                        atomicAdd(&sm.hist[(key >> shift) & dmask], 1);
-                }
-                cluster.sync();             // all slices' histograms are complete
-                // reduce-scatter: CTA c sums bins [c*bs, (c+1)*bs) of every CTA
-                const int bs = nb / CL;
-                for (int e = tid; e < bs * CL; e += NT) {
-                    const int bin = c * bs + (e % bs), src = e / bs;
-                    const int v = cluster.map_shared_rank(sm.hist, src)[bin];
-                    if (v) atomicAdd(&sm.tot[bin], v);
-                }
-                __syncthreads();
-                // total of my bin slice
-                int part = 0;
-                for (int e = tid; e < bs; e += NT) part += sm.tot[c * bs + e];
+            for (int base = 4 * tid; base < n_loc; base += 4 * NT) {
+                const uint4 kv = *reinterpret_cast<const uint4*>(&keys[base]);
+                const uint32_t kk[4] = {kv.x, kv.y, kv.z, kv.w};
 #pragma unroll
-                for (int o = 16; o >= 1; o >>= 1)
-                    part += __shfl_xor_sync(0xffffffffu, part, o);
-                if (lane == 0) sm.wtot2[warp] = part;
-                __syncthreads();
-                if (tid == 0) {
-                    int t = 0;
-                    for (int w = 0; w < NW; ++w) t += sm.wtot2[w];
-                    sm.x_slice_tot = t;
+                for (int s = 0; s < 4; ++s) {
+                    const uint32_t key = kk[s];
+                    if (key - 1u < 0xFFFFFFFEu && (key & mask) == prefix)
+                        atomicAdd(&h4[(hslot((key >> shift) & dmask) << 2) |
+                                      (lane & 3)], 1);
                 }
-                cluster.sync();             // slice totals + summed slices ready
-                // locate the slice (from the top) that holds the k-th key
-                int above = 0, sl = CL - 1;
-                for (int cc = CL - 1; cc >= 0; --cc) {
-                    const int t = *cluster.map_shared_rank(&sm.x_slice_tot, cc);
-                    if (k <= above + t) { sl = cc; break; }
-                    above += t;
+            }
+            SEL_TS(2 + 4 * pass);
+            __syncthreads();
+            SEL_TS(3 + 4 * pass);
+            if (CL == 1) {
+                if (warp < AW) find_digit_active<true>(sm, h4, nb, k);
+                SEL_TS(4 + 4 * pass);
+                __syncthreads();
+            } else {
+                if (warp < AW) push_bins(h4, nb, tot0);
+                cluster.sync();                       // the totals are complete
+                if (c == 0) {
+                    if (warp < AW) find_digit_active<false>(sm, sm.tot, nb, k);
+                    __syncthreads();
+                    if (tid > 0 && tid < CL) {        // tell the other CTAs
+                        *cluster.map_shared_rank(&sm.sh_i0, tid) = sm.sh_i0;
+                        *cluster.map_shared_rank(&sm.sh_i1, tid) = sm.sh_i1;
+                        *cluster.map_shared_rank(&sm.sh_i2, tid) = sm.sh_i2;
+                    }
                 }
-                // copy that summed slice locally (into hist, now free) and search
-                const int* rt = cluster.map_shared_rank(sm.tot, sl);
-                __syncthreads();
-                for (int e = tid; e < nb; e += NT)
-                    sm.hist[e] = (e >= sl * bs && e < (sl + 1) * bs) ? rt[e] : 0;
-                __syncthreads();
-                find_digit(sm, sm.hist, (sl + 1) * bs, above, k);
-                cluster.sync();             // remote reads of tot are finished
+                cluster.sync();                       // the digit has arrived
             }
             prefix |= (uint32_t)sm.sh_i0 << shift;
             k = sm.sh_i1;
             mask |= dmask << shift;
+            // the bin is taken whole: no finer digit and no tie rule needed
+            whole_bin = (sm.sh_i2 == k);
             SEL_TS(5 + 4 * pass);
         }
-        tau_key = prefix;
-        quota = k;
+        if (whole_bin) { tau_key = prefix ? prefix - 1u : 0u; quota = 0; }
+        else { tau_key = prefix; quota = k; }
     }
+    SEL_TS(13);
 
-    // ---------------- 3. keep flags + ascending compaction --------------------
-    // one pass over my groups: pages kept outright (outside the selectable
-    // range, or above the threshold) and pages tied with the threshold
+    // ---- 3. keep flags + ascending compaction.  Warp w owns a contiguous run of
+    // keys and walks it 128 keys at a time.
     const uint32_t lt_mask = (1u << lane) - 1u;
-    int w_eq = 0, w_sure = 0;
-    for (int grp = g_beg; grp < g_end; ++grp) {
-        const int j = grp * 32 + lane, i = s0 + j;
-        const bool in = j < n_loc && i < npg;
-        const bool selr = !keep_all && j >= q0 && j < q1;
-        const uint32_t key = (j < n_loc) ? keys[j] : 0u;
-        const bool eq = selr && key == tau_key;
-        const bool sure = in && (!selr || key > tau_key);
-        w_eq += __popc(__ballot_sync(0xffffffffu, eq));
-        w_sure += __popc(__ballot_sync(0xffffffffu, sure));
+    const int WS = (((n_loc + NW - 1) / NW) + 127) & ~127;
+    const int w0 = min(warp * WS, n_loc), w1 = min(w0 + WS, n_loc);
+    const bool ties = quota > 0;
+    int c_sure = 0, c_eq = 0;
+    for (int it = w0; it < w1; it += 128) {
+        const uint4 kv = *reinterpret_cast<const uint4*>(&keys[it + 4 * lane]);
+        c_sure += (kv.x > tau_key) + (kv.y > tau_key) + (kv.z > tau_key) +
+                  (kv.w > tau_key);
+        c_eq += (kv.x == tau_key) + (kv.y == tau_key) + (kv.z == tau_key) +
+                (kv.w == tau_key);
     }
-    if (lane == 0) sm.wtot[warp] = w_eq;
-    __syncthreads();
-    scan_warp_totals(sm.wtot);
-    __syncthreads();
-    int eq_base = warp ? sm.wtot[warp - 1] : 0;
-    if (CL > 1) {
-        if (tid == 0) sm.x_eq = sm.wtot[NW - 1];
-        SEL_TS(14);
-        cluster.sync();
-        for (int cc = 0; cc < c; ++cc)
-            eq_base += *cluster.map_shared_rank(&sm.x_eq, cc);
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) {
+        c_eq += __shfl_xor_sync(0xffffffffu, c_eq, o);
+        c_sure += __shfl_xor_sync(0xffffffffu, c_sure, o);
     }
+    if (lane == 0) { sm.wtot[warp] = c_eq; sm.wtot2[warp] = c_sure; }
     SEL_TS(15);
-    // ties are kept in ascending page order until `quota` of them are taken
-    const int w_kept = w_sure + min(max(quota - eq_base, 0), w_eq);
-    if (lane == 0) sm.wtot2[warp] = w_kept;
     __syncthreads();
-    scan_warp_totals(sm.wtot2);
-    __syncthreads();
-    int pos = warp ? sm.wtot2[warp - 1] : 0;
-    int cnt = sm.wtot2[NW - 1];
+    // every warp derives all warps' tie ranks and output slots by itself
+    const int e_w = (lane < NW) ? sm.wtot[lane] : 0;
+    const int s_w = (lane < NW) ? sm.wtot2[lane] : 0;
+    int einc = e_w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, einc, o);
+        if (lane >= o) einc += t;
+    }
+    // sliced mode: ties and kept pages of the slices before mine
+    int eq_before = 0, pos_before = 0, cnt_all = 0;
     if (CL > 1) {
-        if (tid == 0) sm.x_kept = cnt;
-        SEL_TS(16);
+        const int eq_mine = __shfl_sync(0xffffffffu, einc, 31);
+        int sinc = s_w;
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1)
+            sinc += __shfl_xor_sync(0xffffffffu, sinc, o);
+        if (tid < CL) {
+            *cluster.map_shared_rank(&sm.x_eq_all[c], tid) = eq_mine;
+            *cluster.map_shared_rank(&sm.x_sure_all[c], tid) = sinc;
+        }
         cluster.sync();
-        cnt = 0;
+        int eb = 0;
         for (int cc = 0; cc < CL; ++cc) {
-            const int v = *cluster.map_shared_rank(&sm.x_kept, cc);
-            if (cc < c) pos += v;
-            cnt += v;
+            const int e = sm.x_eq_all[cc];
+            const int kept = sm.x_sure_all[cc] + min(max(quota - eb, 0), e);
+            if (cc < c) { eq_before += e; pos_before += kept; }
+            cnt_all += kept;
+            eb += e;
         }
     }
+    const int k_w = s_w + min(max(quota - eq_before - (einc - e_w), 0), e_w);
+    int kinc = k_w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, kinc, o);
+        if (lane >= o) kinc += t;
+    }
+    int pos = pos_before + __shfl_sync(0xffffffffu, kinc - k_w, warp);
+    int eqr = eq_before + __shfl_sync(0xffffffffu, einc - e_w, warp);
+    const int cnt = (CL > 1) ? cnt_all : __shfl_sync(0xffffffffu, kinc, 31);
     SEL_TS(17);
-    int32_t* tab = p.page_table + row * MP;
-    {
-        int eqr = eq_base;
-        for (int grp = g_beg; grp < g_end; ++grp) {
-            const int j = grp * 32 + lane, i = s0 + j;
-            const bool in = j < n_loc && i < npg;
-            const bool selr = !keep_all && j >= q0 && j < q1;
-            const uint32_t key = (j < n_loc) ? keys[j] : 0u;
-            const bool eq = selr && key == tau_key;
-            const uint32_t eqb = __ballot_sync(0xffffffffu, eq);
-            bool keep = in;
-            if (selr) keep = eq ? (eqr + __popc(eqb & lt_mask) + 1 <= quota)
-                                : (key > tau_key);
-            eqr += __popc(eqb);
-            const uint32_t kb = __ballot_sync(0xffffffffu, keep);
-            if (keep) tab[pos + __popc(kb & lt_mask)] = i;
-            pos += __popc(kb);
+    for (int it = w0; it < w1; it += 128) {
+        const int base = it + 4 * lane;
+        const uint4 kv = *reinterpret_cast<const uint4*>(&keys[base]);
+        const uint32_t kk[4] = {kv.x, kv.y, kv.z, kv.w};
+        bool keep[4];
+#pragma unroll
+        for (int s = 0; s < 4; ++s) keep[s] = kk[s] > tau_key;
+        if (ties) {
+            uint32_t eb[4];
+            int lower = 0, total = 0;
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                eb[s] = __ballot_sync(0xffffffffu, kk[s] == tau_key);
+                lower += __popc(eb[s] & lt_mask);
+                total += __popc(eb[s]);
+            }
+            int rank = eqr + lower;                  // ties before (lane, s = 0)
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                if (kk[s] == tau_key) { keep[s] = rank < quota; ++rank; }
+            }
+            eqr += total;
         }
+        int slot = pos, total = 0;
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+            const uint32_t kb = __ballot_sync(0xffffffffu, keep[s]);
+            slot += __popc(kb & lt_mask);
+            total += __popc(kb);
+        }
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+            if (keep[s]) tab[slot++] = s0 + base + s;
+        }
+        pos += total;
     }
-    // -1 padding of [cnt, MP), shared by the cluster
+    // -1 padding of [cnt, MP): in owner mode the helper CTAs did the part no
+    // selection can reach, in sliced mode the CTAs share it
     {
-        const int pad_end = owner
-            ? (keep_all ? npg : min(npg, (npg - L) + min(max(b, 0), L)))
-            : MP;
-        for (int i = cnt + c * NT + tid; i < pad_end; i += CL * NT)
-            tab[i] = -1;
+        const int cnt_max = keep_all ? npg
+                                     : min(npg, (npg - L) + min(max(b, 0), L));
+        const int pad_end = owner ? cnt_max : MP;
+        for (int i = cnt + c * NT + tid; i < pad_end; i += CL * NT) tab[i] = -1;
     }
     if (c == 0 && tid == 0) p.page_cnt[row] = cnt;
     SEL_TS(18);
-    if (CL > 1) cluster.sync();  // keep shared memory alive for remote readers
     SEL_TS(19);
     TL_MARK(g_sel_tl, 2);
-    }  // distributed selection
 }
 
 }  // namespace
@@ -855,35 +706,38 @@ extern "C" int locks_topb_select(
         while (cl * 2 <= want && cl * 2 <= useful && cl < 4) cl *= 2;
     } else {
         while (cl < MAX_CL && (max_pages + cl - 1) / cl > KEYS_PER_CTA) cl *= 2;
+        // more CTAs share the combine when SMs are free
+        const int want = sm_count() / max(1, n_kv * n_req);
+        while (cl * 2 <= MAX_CL && cl * 2 <= want && max_pages / (cl * 2) >= 4096)
+            cl *= 2;
     }
     LOCKS_REQUIRE(owner_mode || (max_pages + cl - 1) / cl <= KEYS_PER_CTA,
                   LOCKS_ERR_SIZE,
                   "locks_topb_select: max_pages %d beyond the supported %d",
                   max_pages, MAX_CL * KEYS_PER_CTA);
     p.owner_mode = owner_mode ? 1 : 0;
-    // key slots per CTA (the compaction reads whole 128-key rows), followed in
-    // single-CTA selection by the interleaved histogram copies
-    const bool single_cta = owner_mode || cl == 1;
-    const int per_cta = single_cta
-        ? ((max_pages + 127) & ~127) + 128
-        : ((((max_pages + cl - 1) / cl) + 31) & ~31) + 32;
+    // key slots per CTA (the compaction reads whole 128-key rows), followed by
+    // the interleaved histogram copies
+    const int slice = owner_mode ? max_pages
+                                 : ((((max_pages + cl - 1) / cl) + 31) & ~31);
+    const int per_cta = ((slice + 127) & ~127) + 128;
     p.key_cap = per_cta;
-    const int dyn_smem = (per_cta + (single_cta ? HSLOTS * HCOPIES : 0)) * 4;
+    const int dyn_smem = (per_cta + HSLOTS * HCOPIES) * 4;
     static bool attr_done[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        cudaFuncSetAttribute(topb_kernel<SINGLE_THREADS, true>,
+        cudaFuncSetAttribute(topb_kernel<SEL_THREADS, true>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (KEYS_PER_CTA + 256 + HSLOTS * HCOPIES) * 4);
+                             (KEYS_PER_CTA + 512 + HSLOTS * HCOPIES) * 4);
         cudaFuncSetAttribute(topb_kernel<SEL_THREADS, false>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (KEYS_PER_CTA + 64) * 4);
+                             (KEYS_PER_CTA + 512 + HSLOTS * HCOPIES) * 4);
         attr_done[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(cl, n_kv, n_req);
-    cfg.blockDim = dim3(single_cta ? SINGLE_THREADS : SEL_THREADS, 1, 1);
+    cfg.blockDim = dim3(SEL_THREADS, 1, 1);
     cfg.dynamicSmemBytes = dyn_smem;
     cfg.stream = static_cast<cudaStream_t>(stream);
     cudaLaunchAttribute attr[2];
@@ -895,8 +749,8 @@ extern "C" int locks_topb_select(
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
-    cudaError_t e = single_cta
-        ? cudaLaunchKernelEx(&cfg, topb_kernel<SINGLE_THREADS, true>, p)
+    cudaError_t e = owner_mode
+        ? cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, true>, p)
         : cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, false>, p);
     if (e != cudaSuccess)
         return fail(LOCKS_ERR_LAUNCH, "locks_topb_select: %s",
