@@ -201,6 +201,30 @@ int locks_merge_gathered(const float* packs, int64_t pack_stride, int n_groups,
                          void* out, int64_t out_stride_req, int n_req, int n_kv,
                          int G, int head_dim, int split, locks_stream_t stream);
 
+/* ---- KV-write neighbour: rotate K, store K/V into the paged cache, build the
+ * summary of a page the token completes ------------------------------------------
+ * key, val: bf16 (n_tok, n_kv, head_dim), row / head strides in elements.  Row r
+ * goes to slot = slot_mapping[r] (block slot / page, token slot % page); slot < 0
+ * skips the row.  cos_sin: optional bf16 (P, rot_dim) table, cos half then sin
+ * half per position; K channels below rot_dim are rotated at positions[r] in
+ * half-split (neox != 0) or interleaved pairing with separately rounded fp32
+ * products (no fused multiply-add), the rest of K and all of V are copied.
+ * Replaces tier/k5_cuda.py:55-77, 660-687 (rope_and_cache_fixc_kernel).
+ * records_layer / tags_layer: optional, this layer's (NB, n_kv, 832) summary
+ * records and (NB, n_kv, 8) tags; when the row lands on token page-1 of its block
+ * the block's summaries are rebuilt from the cache in the same launch -- the
+ * arithmetic of locks_rki4_build (selection/rki4_build.py:45-225), which replaces
+ * the separate tail refresh of selection/rki4_tailgraph.py. */
+int locks_kv_write(const void* key, int64_t k_row_stride, int64_t k_head_stride,
+                   const void* val, int64_t v_row_stride, int64_t v_head_stride,
+                   void* k_cache, void* v_cache, int64_t kv_stride_block,
+                   int64_t kv_stride_tok, int64_t kv_stride_head,
+                   const int64_t* slot_mapping, const int64_t* positions,
+                   const void* cos_sin, int64_t cos_sin_row_stride, int rot_dim,
+                   int neox, void* records_layer, void* tags_layer, int n_tok,
+                   int n_kv, int head_dim, int page, int num_blocks,
+                   locks_stream_t stream);
+
 /* ---- Context parallel (one sequence over several GPUs) -------------------------
  * No counterpart in the reference (single GPU).  Every rank scores and selects
  * on its own page range with the GLOBAL budget b (locks_rki4_score_bt after an

@@ -390,9 +390,9 @@ rki4_score_kernel(const ScoreParams p) {
             }
         } else {
             // ---- one page per pass, rows = heads (8, or 16 with the hi rows) --
-#pragma unroll 2
+            // as above: no exit test inside the unrolled group of pages
+#pragma unroll 4
             for (int i = 0; i < CHUNK; ++i) {
-                if (i >= n) break;
                 const uint8_t* rec = crec + i * REC_BYTES;
                 int c1[4];
                 project_page<HI>(c1, rec, gid, tig, qe[0], qo[0], qe[NR - 1],
@@ -444,7 +444,7 @@ rki4_score_kernel(const ScoreParams p) {
                         fmaf(cs2, x[1][2 * h], mud[h]),
                         fmaf(cs3, x[1][2 * h + 1], mud[h]));
                     const int g = gid + 8 * h;
-                    if (g < G) {
+                    if (g < G && i < n) {
                         if (tig == (i & 3))
                             out_base[(int64_t)g * p.max_pages + p0 + i] = S;
                         run_max[h] = fmaxf(run_max[h], S);

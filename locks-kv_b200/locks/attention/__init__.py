@@ -4,8 +4,9 @@ from __future__ import annotations
 from .decode import (DenseDecodeBuffers, ResidentVSource, VSource,  # noqa: F401
                      dense_paged_decode, ensure_stage_b_buffers,
                      sparse_paged_decode_batched, sparse_paged_decode_fused)
+from .kv_write import rope_and_cache  # noqa: F401
 from .merge import merge_splits  # noqa: F401
 
 __all__ = ["sparse_paged_decode_batched", "sparse_paged_decode_fused",
            "dense_paged_decode", "DenseDecodeBuffers", "ResidentVSource",
-           "VSource", "ensure_stage_b_buffers", "merge_splits"]
+           "VSource", "ensure_stage_b_buffers", "merge_splits", "rope_and_cache"]

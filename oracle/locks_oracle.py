@@ -14,6 +14,9 @@ piece is the symmetric eigensolver: the reference calls ``torch.linalg.eigh``
 ``numpy.linalg.eigh`` (also ``ssyevd``).  Eigenvectors carry a free sign, so
 summary codes are compared after per-column sign alignment
 (:func:`align_signs`); everything downstream of the codes is sign-invariant.
+One function is NOT pinned: :func:`rope_and_cache` restates a CUDA-only kernel
+of the reference (no CPU twin exists to generate vectors from); its arithmetic
+is a handful of fp32 products and sums read directly off the source.
 
 All "bf16" arrays are float32 arrays holding bf16-representable values.
 """
@@ -475,6 +478,49 @@ def gqa_decode_step(slabs, q, Kc, Vc, block_table, seq_lens, scale, *, n_kv, G,
     return {"n_pages": npg, "n_sel_hi": nsh, "b": b, "score_h": score_h,
             "score": score, "page_table": table, "page_cnt": cnt,
             "m_part": m, "l_part": l, "acc_part": acc, "out": out}
+
+
+# --------------------------------------------------------------------------- #
+# KV-write neighbour (parity unpinned: the reference kernel is CUDA-only)       #
+# --------------------------------------------------------------------------- #
+def rope_and_cache(key, val, k_cache, v_cache, slot_mapping, positions, cos_sin,
+                   rot_dim, neox, page=16):
+    """Rotate the new tokens' K and scatter K, V into the paged cache, in place.
+
+    tier/k5_cuda.py:55-77 (``locks_rope_elem``) and :660-687
+    (``rope_and_cache_fixc_kernel``).  key, val: (n_tok, n_kv, d) bf16-valued
+    float32; caches (NB, page, n_kv, d); cos_sin (P, rot_dim) = cos half | sin
+    half, bf16-valued.  Channels below rot_dim: fp32 products rounded
+    separately, then one rounded sum / difference, then bf16; half-split
+    pairing (lo, lo + rot/2) when ``neox`` else interleaved (dd, dd ^ 1).
+    slot < 0 skips the row."""
+    key = np.asarray(key, np.float32)
+    val = np.asarray(val, np.float32)
+    half = rot_dim // 2
+    for r in range(key.shape[0]):
+        s = int(slot_mapping[r])
+        if s < 0:
+            continue
+        blk, t = s // page, s % page
+        v_cache[blk, t] = val[r]
+        out = key[r].copy()
+        if cos_sin is not None:
+            c = np.asarray(cos_sin[int(positions[r]), :half], np.float32)
+            sn = np.asarray(cos_sin[int(positions[r]), half:rot_dim], np.float32)
+            x = key[r]
+            if neox:
+                e, o = x[:, :half], x[:, half:rot_dim]
+                lo = (e * c).astype(np.float32) - (o * sn).astype(np.float32)
+                hi = (o * c).astype(np.float32) + (e * sn).astype(np.float32)
+                out[:, :half], out[:, half:rot_dim] = lo, hi
+            else:
+                ev, od = x[:, 0:rot_dim:2], x[:, 1:rot_dim:2]
+                out[:, 0:rot_dim:2] = (ev * c).astype(np.float32) - \
+                    (od * sn).astype(np.float32)
+                out[:, 1:rot_dim:2] = (od * c).astype(np.float32) + \
+                    (ev * sn).astype(np.float32)
+            out[:, :rot_dim] = bf16_round(out[:, :rot_dim])
+        k_cache[blk, t] = out
 
 
 # --------------------------------------------------------------------------- #

@@ -1,0 +1,99 @@
+"""GPU parity of the KV-write neighbour: rotated K and V land in the paged cache
+bit-exactly as the oracle's restatement of the reference kernel says, and the
+summary of a page completed by the write equals the stand-alone builder's."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+import locks_oracle as orc
+from conftest import t2n
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _table(P, rot, seed):
+    g = torch.Generator().manual_seed(seed)
+    ang = torch.rand(P, rot // 2, generator=g) * 6.28
+    return torch.cat([ang.cos(), ang.sin()], 1).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("neox", [True, False])
+@pytest.mark.parametrize("rot", [128, 64])
+def test_rope_and_cache_bit_exact(neox, rot):
+    from locks.attention import rope_and_cache
+    n_tok, n_kv, d, page, NB, P = 7, 8, 128, 16, 12, 4096
+    g = torch.Generator().manual_seed(5 + rot + int(neox))
+    key = torch.randn(n_tok, n_kv, d, generator=g).to(torch.bfloat16)
+    val = torch.randn(n_tok, n_kv, d, generator=g).to(torch.bfloat16)
+    cache = torch.randn(NB, 2, page, n_kv, d, generator=g).to(torch.bfloat16)
+    cs = _table(P, rot, 9)
+    slots = torch.tensor([3 * page + 5, 0, -1, 11 * page + 15, 7 * page + 1,
+                          2 * page + 9, 5 * page + 4], dtype=torch.int64)
+    pos = torch.tensor([100, 0, 7, 4095, 17, 2049, 333], dtype=torch.int64)
+    kc = cache[:, 0].float().numpy().copy()
+    vc = cache[:, 1].float().numpy().copy()
+    orc.rope_and_cache(key.float().numpy(), val.float().numpy(), kc, vc,
+                       slots.numpy(), pos.numpy(), cs.float().numpy(), rot, neox,
+                       page)
+    dev_cache = cache.to(DEV)
+    rope_and_cache(key.to(DEV), val.to(DEV), dev_cache, slots.to(DEV),
+                   pos.to(DEV), cs.to(DEV), neox=neox)
+    torch.cuda.synchronize()
+    got_k, got_v = t2n(dev_cache[:, 0].float()), t2n(dev_cache[:, 1].float())
+    assert np.array_equal(got_k, kc)
+    assert np.array_equal(got_v, vc)
+
+
+def test_plain_copy_without_table_and_strided_rows():
+    from locks.attention import rope_and_cache
+    n_tok, n_kv, d, page, NB = 3, 2, 128, 16, 4
+    g = torch.Generator().manual_seed(3)
+    qkv = torch.randn(n_tok, 3 * n_kv, d, generator=g).to(torch.bfloat16).to(DEV)
+    key, val = qkv[:, n_kv:2 * n_kv], qkv[:, 2 * n_kv:]       # strided views
+    cache = torch.zeros(2, NB, page, n_kv, d, dtype=torch.bfloat16, device=DEV)
+    slots = torch.tensor([17, 2, 63], dtype=torch.int64, device=DEV)
+    rope_and_cache(key, val, cache, slots, None, None)
+    torch.cuda.synchronize()
+    for r, s in enumerate([17, 2, 63]):
+        assert torch.equal(cache[0, s // page, s % page], key[r])
+        assert torch.equal(cache[1, s // page, s % page], val[r])
+    assert int((cache != 0).any(-1).any(-1).sum()) == 2 * n_tok
+
+
+def test_page_completion_builds_the_summary():
+    """The write that lands on token 15 of a block leaves the block's records
+    and tags exactly as a stand-alone build of that block does."""
+    from locks.attention import rope_and_cache
+    from locks.selection import Rki4State, rki4_build_bulk
+    n_kv, G, d, page, NB = 8, 4, 128, 16, 6
+    g = torch.Generator().manual_seed(21)
+    cache = torch.randn(NB, 2, page, n_kv, d, generator=g).to(torch.bfloat16).to(DEV)
+
+    def state():
+        return Rki4State(DEV, num_layers=1, num_blocks=NB, n_kv=n_kv, G=G,
+                         head_dim=d, page=page, max_reqs=2, max_pages=NB)
+    st = state()
+    key = torch.randn(2, n_kv, d, generator=g).to(torch.bfloat16).to(DEV)
+    val = torch.randn(2, n_kv, d, generator=g).to(torch.bfloat16).to(DEV)
+    cs = _table(64, d, 4).to(DEV)
+    # row 0 completes block 4, row 1 lands mid-page in block 2
+    slots = torch.tensor([4 * page + 15, 2 * page + 3], dtype=torch.int64, device=DEV)
+    pos = torch.tensor([31, 9], dtype=torch.int64, device=DEV)
+    rope_and_cache(key, val, cache, slots, pos, cs, neox=True, st=st, lidx=0)
+    torch.cuda.synchronize()
+    # stand-alone build of block 4 from the cache as it is now
+    ref = state()
+    bt = torch.tensor([[4, 2]], dtype=torch.int32, device=DEV)
+    settled = torch.tensor([2 * page], dtype=torch.int32, device=DEV)
+    rki4_build_bulk(ref, [cache[:, 0]], bt, settled, 1, 1)      # page 0 -> block 4
+    torch.cuda.synchronize()
+    assert torch.equal(st.pp_rec[0, 4], ref.pp_rec[0, 4])
+    assert torch.equal(st.pp_tag[0, 4].view(torch.int16),
+                       ref.pp_tag[0, 4].view(torch.int16))
+    # nothing else was built: block 2 still carries the never-built NaN tag
+    assert bool(torch.isnan(st.pp_tag[0, 2].float()).all())
+    assert int(st.pp_rec[0, 2].abs().sum()) == 0
