@@ -331,6 +331,31 @@ def run_gpu(args, sh, seq_len):
     st.hmax.zero_() if st.hmax is not None else None
     hp.step()                       # leave a consistent selection behind
 
+    # ---- KV-write neighbour: rotate + store one new token per layer; in the
+    # second graph the token completes a page, so the page's summaries are built
+    # in the same launch (a spare block of the pool takes the writes) ------------
+    from locks.attention import rope_and_cache
+    NBc = int(caches[0].shape[0])
+    used = torch.zeros(NBc, dtype=torch.bool)
+    used[bt.cpu().long().flatten()] = True
+    spare = int((~used).nonzero()[0])
+    kw_key = torch.randn(R, sh.n_kv, sh.d, device=dev).to(torch.bfloat16)
+    kw_val = torch.randn(R, sh.n_kv, sh.d, device=dev).to(torch.bfloat16)
+    ang = torch.rand(64, sh.d // 2, device=dev) * 6.28
+    kw_cs = torch.cat([ang.cos(), ang.sin()], 1).to(torch.bfloat16)
+    kw_pos = torch.full((R,), 17, dtype=torch.int64, device=dev)
+    slot_mid = torch.full((R,), spare * sh.page + 3, dtype=torch.int64, device=dev)
+    slot_end = torch.full((R,), spare * sh.page + sh.page - 1, dtype=torch.int64,
+                          device=dev)
+    g_kw = stage_graph(lambda l: rope_and_cache(kw_key, kw_val, caches[l], slot_mid,
+                                                kw_pos, kw_cs, st=st, lidx=l))
+    g_kwb = stage_graph(lambda l: rope_and_cache(kw_key, kw_val, caches[l], slot_end,
+                                                 kw_pos, kw_cs, st=st, lidx=l))
+    ms_kw = timed(g_kw.replay, it) / L
+    ms_kwb = timed(g_kwb.replay, it) / L
+    from locks.selection import rki4_build_slots
+    ms_slots = timed(lambda: rki4_build_slots(st, hp.K_layers, slot_end), 10)
+
     # ---- dense full-KV baseline on the same caches ----------------------------
     dsplit = max(1, min(512, (4 * 148) // (sh.n_kv * R)))
     dbuf = DenseDecodeBuffers(dev, R, sh.n_kv, sh.G, sh.d, dsplit)
@@ -448,6 +473,12 @@ def run_gpu(args, sh, seq_len):
                   "speedup_sparse_over_dense": ms_dense / ms_step},
         "build": {"bulk_ms": t_build, "tail_ms_per_finalize": t_tail,
                   "tail_ms_amortised_per_step": t_tail / sh.page},
+        "kv_write": {"us_per_layer": ms_kw * 1e3,
+                     "us_per_layer_completing_a_page": ms_kwb * 1e3,
+                     "slot_driven_build_all_layers_us": ms_slots * 1e3,
+                     "note": "rotate K + store K,V (+ summary build of the "
+                             "completed page in the same launch); or one "
+                             "slot-driven build launch per step for all layers"},
         "cpu_baseline": cpu,
     }
     if world > 1:

@@ -201,6 +201,21 @@ int locks_merge_gathered(const float* packs, int64_t pack_stride, int n_groups,
                          void* out, int64_t out_stride_req, int n_req, int n_kv,
                          int G, int head_dim, int split, locks_stream_t stream);
 
+/* Summary build driven by the step's cache slots: job (layer, token, kv head)
+ * builds block slot / page when slot_mapping[token] is the LAST token of its
+ * block (the write completed the page) and does nothing otherwise.  Which blocks
+ * to refresh is thus decided on the device from the same slot_mapping the KV
+ * write used: the launch has a fixed shape and can sit in a CUDA graph (on a
+ * forked branch: the page is not scored before it leaves the recent window).
+ * Replaces the host-driven tail refresh of selection/rki4_build.py:318-364
+ * (rki4_build_tail) / selection/rki4_tailgraph.py. */
+int locks_rki4_build_slots(const void* const* k_layers, int64_t k_stride_block,
+                           int64_t k_stride_tok, int64_t k_stride_head,
+                           void* records, void* tags, const int64_t* slot_mapping,
+                           int n_tok, int layer0, int n_layers,
+                           int num_blocks_state, int num_blocks_cache, int n_kv,
+                           int head_dim, int page, locks_stream_t stream);
+
 /* ---- KV-write neighbour: rotate K, store K/V into the paged cache, build the
  * summary of a page the token completes ------------------------------------------
  * key, val: bf16 (n_tok, n_kv, head_dim), row / head strides in elements.  Row r

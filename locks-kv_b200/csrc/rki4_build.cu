@@ -14,7 +14,8 @@ struct BuildParams {
     uint8_t* records;
     __nv_bfloat16* tags;
     const int32_t* blocks;
-    int n_blocks, layer0, n_layers, nb_state, nb_cache, n_kv;
+    const int64_t* slots;              // slot mode: job i looks at slots[i]
+    int n_blocks, layer0, n_layers, nb_state, nb_cache, n_kv, page;
 };
 
 
@@ -27,7 +28,16 @@ __global__ void __launch_bounds__(BW * 32) rki4_build_kernel(const BuildParams p
     const int kh = (int)(job % p.n_kv);
     const int bi = (int)((job / p.n_kv) % p.n_blocks);
     const int layer = p.layer0 + (int)(job / ((int64_t)p.n_kv * p.n_blocks));
-    const int blk = p.blocks[bi];
+    int blk;
+    if (p.slots) {
+        // a cache slot that is the LAST token of its block names a page that
+        // has just been completed; every other slot is nobody's job
+        const int64_t s = p.slots[bi];
+        if (s < 0 || (s % p.page) != p.page - 1) return;
+        blk = (int)(s / p.page);
+    } else {
+        blk = p.blocks[bi];
+    }
     if (blk < 0 || blk >= p.nb_state || blk >= p.nb_cache) return;
     const __nv_bfloat16* K =
         static_cast<const __nv_bfloat16*>(p.k_layers[layer]) +
@@ -105,13 +115,47 @@ extern "C" int locks_rki4_build(
     p.sh = k_stride_head;
     p.records = static_cast<uint8_t*>(records);
     p.tags = static_cast<__nv_bfloat16*>(tags);
-    p.blocks = blocks; p.n_blocks = n_blocks; p.layer0 = layer0;
+    p.blocks = blocks; p.slots = nullptr; p.n_blocks = n_blocks; p.layer0 = layer0;
     p.n_layers = n_layers; p.nb_state = num_blocks_state;
-    p.nb_cache = num_blocks_cache; p.n_kv = n_kv;
+    p.nb_cache = num_blocks_cache; p.n_kv = n_kv; p.page = page;
     rki4_build_kernel<<<(unsigned)((n_jobs + BW - 1) / BW), BW * 32, 0,
                         static_cast<cudaStream_t>(stream)>>>(p);
     pdl_break();
     return check_launch("locks_rki4_build");
+}
+
+extern "C" int locks_rki4_build_slots(
+    const void* const* k_layers, int64_t k_stride_block, int64_t k_stride_tok,
+    int64_t k_stride_head, void* records, void* tags, const int64_t* slot_mapping,
+    int n_tok, int layer0, int n_layers, int num_blocks_state,
+    int num_blocks_cache, int n_kv, int head_dim, int page,
+    locks_stream_t stream) {
+    LOCKS_REQUIRE(k_layers && records && tags && (slot_mapping || n_tok == 0),
+                  LOCKS_ERR_ARG, "locks_rki4_build_slots: null pointer argument");
+    LOCKS_REQUIRE(head_dim == BUILD_HD && page == BUILD_PAGE_T, LOCKS_ERR_GEOMETRY,
+                  "locks_rki4_build_slots: supports head_dim 128 / page 16, got "
+                  "%d / %d", head_dim, page);
+    LOCKS_REQUIRE(n_tok >= 0 && layer0 >= 0 && n_layers >= 0 &&
+                      num_blocks_state >= 1 && num_blocks_cache >= 1 && n_kv >= 1 &&
+                      k_stride_block % 4 == 0 && k_stride_tok % 4 == 0 &&
+                      k_stride_head % 4 == 0,
+                  LOCKS_ERR_ARG, "locks_rki4_build_slots: bad size or stride");
+    const int64_t n_jobs = (int64_t)n_layers * n_tok * n_kv;
+    if (n_jobs == 0) return LOCKS_OK;
+    LOCKS_REQUIRE((n_jobs + BW - 1) / BW <= 2147483647LL, LOCKS_ERR_SIZE,
+                  "locks_rki4_build_slots: too many (layer, token, head) jobs");
+    BuildParams p;
+    p.k_layers = k_layers; p.sb = k_stride_block; p.st = k_stride_tok;
+    p.sh = k_stride_head;
+    p.records = static_cast<uint8_t*>(records);
+    p.tags = static_cast<__nv_bfloat16*>(tags);
+    p.blocks = nullptr; p.slots = slot_mapping; p.n_blocks = n_tok;
+    p.layer0 = layer0; p.n_layers = n_layers; p.nb_state = num_blocks_state;
+    p.nb_cache = num_blocks_cache; p.n_kv = n_kv; p.page = page;
+    rki4_build_kernel<<<(unsigned)((n_jobs + BW - 1) / BW), BW * 32, 0,
+                        static_cast<cudaStream_t>(stream)>>>(p);
+    pdl_break();
+    return check_launch("locks_rki4_build_slots");
 }
 
 extern "C" int locks_rki4_tag_scan(

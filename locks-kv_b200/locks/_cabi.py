@@ -37,6 +37,8 @@ _SIGNATURES = {
                             _P], 1),
     "locks_merge_splits": ([_P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I,
                             _P], 1),
+    "locks_rki4_build_slots": ([_P, _L, _L, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I,
+                                _I, _I, _P], 1),
     "locks_kv_write": ([_P, _L, _L, _P, _L, _L, _P, _P, _L, _L, _L, _P, _P, _P,
                         _L, _I, _I, _P, _P, _I, _I, _I, _I, _I, _P], 1),
     "locks_cp_pack": ([_P, _P, _P, _I, _I, _I, _I, _I, _I, _P], 1),

@@ -11,7 +11,8 @@ reference's ``selection/__init__.py``.
 from __future__ import annotations
 
 from .rki4_build import (rki4_build_bulk, rki4_build_delta,
-                         rki4_build_refresh, rki4_build_tail)
+                         rki4_build_refresh, rki4_build_slots,
+                         rki4_build_tail)
 from .rki4_score import rki4_score_only, rki4_score_state, rki4_select_only
 from .rki4_state import TAGW, Rki4State
 from .select import derive_page_params, nrmtopb_select, topb_select
@@ -20,7 +21,8 @@ from .mla_select import (MlaState, build_page_factors, build_prompt_factors,
                          mla_select_pages)
 
 __all__ = [
-    "Rki4State", "TAGW", "rki4_build_refresh", "rki4_build_tail",
+    "Rki4State", "TAGW", "rki4_build_refresh", "rki4_build_slots",
+    "rki4_build_tail",
     "rki4_build_bulk", "rki4_build_delta", "derive_page_params", "topb_select",
     "nrmtopb_select", "rki4_score_only", "rki4_select_only", "rki4_score_state",
     "MlaState", "build_page_factors", "build_prompt_factors", "mla_derive",

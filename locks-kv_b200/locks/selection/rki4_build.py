@@ -93,6 +93,29 @@ def rki4_build_tail(st: Rki4State, K_layers, block_table, seq_lens, n_req: int,
     return len(K_layers) * int(blocks.shape[0])
 
 
+def rki4_build_slots(st: Rki4State, K_layers, slot_mapping: torch.Tensor) -> None:
+    """Rebuild, in all layers, the pages that this step's cache writes completed:
+    a token whose ``slot_mapping`` entry is the last slot of its block names the
+    block; the decision is taken on the device, so the launch has a fixed shape,
+    needs no host-side refresh gate and can be captured in the decode graph
+    (the device-side form of the tail refresh, reference
+    ``selection/rki4_tailgraph.py`` / ``selection/rki4_build.py:318-364``)."""
+    assert slot_mapping.dtype == torch.int64 and slot_mapping.is_contiguous()
+    n_tok = int(slot_mapping.numel())
+    if n_tok == 0 or len(K_layers) == 0:
+        return
+    K0 = K_layers[0]
+    for K in K_layers:
+        _check_k(st, K)
+        assert K.stride() == K0.stride() and K.shape == K0.shape
+    ptrs = _k_ptr_array(st, K_layers)
+    _cabi.call("locks_rki4_build_slots", _cabi.ptr(ptrs), K0.stride(0),
+               K0.stride(1), K0.stride(2), _cabi.ptr(st.pp_rec),
+               _cabi.ptr(st.pp_tag), _cabi.ptr(slot_mapping), n_tok, 0,
+               len(K_layers), int(st.NB), int(K0.shape[0]), int(st.n_kv),
+               int(st.d), int(st.page), _cabi.stream())
+
+
 def rki4_build_bulk(st: Rki4State, K_layers, block_table, seq_lens, n_req: int,
                     max_fin: int, chunk_pairs: int = 8192) -> int:
     """Rebuild ALL finalized pages of ALL layers, no device sync.

@@ -97,3 +97,35 @@ def test_page_completion_builds_the_summary():
     # nothing else was built: block 2 still carries the never-built NaN tag
     assert bool(torch.isnan(st.pp_tag[0, 2].float()).all())
     assert int(st.pp_rec[0, 2].abs().sum()) == 0
+
+
+def test_slot_driven_build_matches_block_list_build():
+    """locks_rki4_build_slots builds exactly the blocks whose last slot was
+    written this step, in every layer, and leaves the others alone."""
+    from locks.selection import Rki4State, rki4_build_bulk, rki4_build_slots
+    n_kv, G, d, page, NB, L = 2, 16, 128, 16, 8, 3
+    g = torch.Generator().manual_seed(77)
+    caches = [torch.randn(NB, 2, page, n_kv, d, generator=g).to(torch.bfloat16).to(DEV)
+              for _ in range(L)]
+    K_layers = [c[:, 0] for c in caches]
+
+    def state():
+        return Rki4State(DEV, num_layers=L, num_blocks=NB, n_kv=n_kv, G=G,
+                         head_dim=d, page=page, max_reqs=4, max_pages=NB)
+    st = state()
+    # tokens: completes block 5, mid-page in block 1, skipped row, completes block 2
+    slots = torch.tensor([5 * page + 15, 1 * page + 7, -1, 2 * page + 15],
+                         dtype=torch.int64, device=DEV)
+    rki4_build_slots(st, K_layers, slots)
+    ref = state()
+    bt = torch.tensor([[5], [2]], dtype=torch.int32, device=DEV)
+    settled = torch.tensor([page, page], dtype=torch.int32, device=DEV)
+    rki4_build_bulk(ref, K_layers, bt, settled, 2, 1)
+    torch.cuda.synchronize()
+    for blk in (5, 2):
+        assert torch.equal(st.pp_rec[:, blk], ref.pp_rec[:, blk])
+        assert torch.equal(st.pp_tag[:, blk].view(torch.int16),
+                           ref.pp_tag[:, blk].view(torch.int16))
+    for blk in (0, 1, 3, 4, 6, 7):
+        assert bool(torch.isnan(st.pp_tag[:, blk].float()).all())
+        assert int(st.pp_rec[:, blk].abs().sum()) == 0
