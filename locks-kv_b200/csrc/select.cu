@@ -369,6 +369,9 @@ topb_kernel(const SelParams p) {
             reinterpret_cast<int4*>(h4)[i] = make_int4(0, 0, 0, 0);
         for (int i = tid; i < NBINS; i += NT) sm.tot[i] = 0;
     }
+    // remote shared memory may be touched once every CTA of the cluster runs;
+    // this barrier costs nothing while the scorer is still at work
+    if (CL_phys > 1) cluster.sync();
     pdl_wait();                  // score_h / hmax / score come from the scorer
     SEL_TS(22);
     TL_MARK(g_sel_tl, 1);
@@ -385,9 +388,6 @@ topb_kernel(const SelParams p) {
         for (int i = n_loc + tid; i < p.key_cap; i += NT) keys[i] = 0u;
 
     // ---------------- 1. GQA combine -> score[slice], keys[slice] --------------
-    // remote shared memory may only be touched once every CTA of the cluster
-    // runs: the nrm branch has a cluster barrier of its own, the others get one
-    if (CL_phys > 1 && !(p.combine == LOCKS_COMBINE_NRM && n_comb > 0)) cluster.sync();
     if (p.combine == LOCKS_COMBINE_NRM && n_comb > 0) {
         const float* sh = p.score_h + row * (int64_t)G * MP;
         const bool published = p.hmax != nullptr;
@@ -416,14 +416,9 @@ topb_kernel(const SelParams p) {
             }
         }
         SEL_TS(20);
-        // the barrier below publishes hm_sh, tells every CTA of the cluster that
-        // all of them run (remote shared memory may be written) and, for the
-        // scorer's keys, that all of them have read hmax (CTA 0 re-arms it)
-        auto sync_hm = [&]() {
-            if (CL_phys > 1) cluster.sync();
-            else __syncthreads();
-            if (published && c_phys == 0 && tid < G) p.hmax[row * G + tid] = 0u;
-        };
+        // the barrier below publishes hm_sh; the scorer's keys are re-armed
+        // further down, behind a cluster barrier every CTA passes after this read
+        auto sync_hm = [&]() { __syncthreads(); };
         LOCKS_DISPATCH_GT(G, LOCKS_DISPATCH_CB(cgpw, (combine_nrm_groups<GT, CBW>(
             sh, score, kdst, sm.hm_sh, G, MP, cs0, cn_loc, n_comb, cg_beg, cg_end,
             lane, sync_hm, fin_key))));
@@ -449,8 +444,11 @@ topb_kernel(const SelParams p) {
             if (j < cn_loc) kdst[j] = fin_key(f2key(score[cs0 + j]), cs0 + j);
         }
     }
+    const bool rearm = p.combine == LOCKS_COMBINE_NRM && n_comb > 0 &&
+                       p.hmax != nullptr;
     if (owner) {
         cluster.sync();                  // all keys have landed in CTA 0
+        if (rearm && c_phys == 0 && tid < G) p.hmax[row * G + tid] = 0u;
         if (c_phys != 0) {
             // entries no selection can reach: beyond the forced pages + budget
             const int cnt_max = keep_all ? npg
@@ -463,6 +461,9 @@ topb_kernel(const SelParams p) {
         }
     } else {
         __syncthreads();
+        // single CTA: every thread has read the keys; a cluster of slices re-arms
+        // behind the exchange of the compaction totals below
+        if (rearm && CL_phys == 1 && tid < G) p.hmax[row * G + tid] = 0u;
     }
     SEL_TS(1);
 
@@ -575,6 +576,7 @@ topb_kernel(const SelParams p) {
             *cluster.map_shared_rank(&sm.x_sure_all[c], tid) = sinc;
         }
         cluster.sync();
+        if (rearm && c == 0 && tid < G) p.hmax[row * G + tid] = 0u;
         int eb = 0;
         for (int cc = 0; cc < CL; ++cc) {
             const int e = sm.x_eq_all[cc];
