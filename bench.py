@@ -39,7 +39,7 @@ import torch  # noqa: E402
 
 REC_ALGO_BYTES = 818           # summary bytes per (page, kv-head) the scorer needs
 PAGE_KV_BYTES = 16 * 128 * 2 * 2   # K + V bytes of one attended (page, kv-head)
-SCORE_TRAFFIC_PER_UNIT = (54556416 + 57344) / 65480.0   # measured DRAM bytes per unit
+SCORE_TRAFFIC_PER_UNIT = (54559232 + 71936) / 65480.0   # measured DRAM bytes per unit
 
 
 def workload(name: str, ctx: int | None):

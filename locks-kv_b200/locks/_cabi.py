@@ -113,12 +113,14 @@ def call(name: str, *args) -> None:
 
 
 def ptr(t) -> c_void_p:
-    """Device pointer of a CUDA tensor (None -> NULL)."""
+    """Device pointer of a CUDA tensor, or of a pinned host tensor (unified
+    addressing: the GPU reads it over the host link); None -> NULL."""
     if t is None:
         return c_void_p(0)
-    if not t.is_cuda:
-        raise RuntimeError("LOCKS B200 kernels need CUDA tensors, got "
-                           f"{t.device} (there is no CPU path)")
+    if not t.is_cuda and not t.is_pinned():
+        raise RuntimeError("LOCKS B200 kernels need CUDA tensors (or pinned host "
+                           f"memory the GPU reads in place), got {t.device}: "
+                           "there is no CPU path")
     return c_void_p(t.data_ptr())
 
 

@@ -53,6 +53,37 @@ class ResidentVSource:
         return v, v.stride(0), v.stride(1), v.stride(2)
 
 
+class PinnedHostVSource:
+    """V lives in pinned host memory and is read IN PLACE by the decode kernel
+    over the host link (the memory-saving variant: the GPU keeps K and the
+    summaries, which selection needs for every page, while V -- needed only for
+    the ~b selected pages of a step -- stays in DRAM).  The plane has the K
+    plane's strides, so the kernels address both alike; the KV-write kernel can
+    store new V rows through the same pointer.  This is the seam of the
+    reference's V tier (``attention/decode.py:52-100``, ``tier/pool.py:104-184``)
+    without its staging pool: no copy engine, no residency map."""
+    SRC_ID = 1
+
+    def __init__(self, kv_cache: torch.Tensor):
+        k, v = _split_kv(kv_cache)
+        if v is None:
+            raise ValueError("PinnedHostVSource copies the V half of a cache "
+                             "that has one")
+        # smallest buffer that holds a plane with K's strides
+        span = 1 + sum((n - 1) * st for n, st in zip(k.shape, k.stride()))
+        self._buf = torch.empty(span, dtype=v.dtype, pin_memory=True)
+        self._v = torch.as_strided(self._buf, tuple(k.shape), tuple(k.stride()))
+        self._v.copy_(v)
+
+    @property
+    def plane(self) -> torch.Tensor:
+        return self._v
+
+    def args(self):
+        v = self._v
+        return v, v.stride(0), v.stride(1), v.stride(2)
+
+
 def _next_pow2(x: int) -> int:
     return 1 << max(0, int(x) - 1).bit_length()
 

@@ -165,3 +165,35 @@ def test_full_size_properties(cfgname):
         # on this data the planted pages carry almost all of the softmax mass,
         # so sparse and dense attention agree
         assert (out - dense[0].float()).abs().max().item() <= 5e-2
+
+
+def test_decode_reads_v_from_pinned_host_memory():
+    """V kept in pinned host memory (read in place over the host link) gives the
+    same output as V resident next to K, for the fused and the split decode."""
+    import math
+    from locks import LocksConfig, synth
+    from locks.attention import (PinnedHostVSource, sparse_paged_decode_batched,
+                                 sparse_paged_decode_fused)
+    from locks.hotpath import HotPath
+    sh = synth.GqaShape(n_layers=1, n_kv=8, G=4, d=128, page=16, budget_pages=32,
+                        sink_pages=1, window_pages=4, n_needles=4, n_outlier=4)
+    case = synth.make_gqa_case(5, sh, [3000, 517], device="cuda")
+    cfg = LocksConfig(budget_pages=32, sink_pages=1, window_pages=4)
+    hp = HotPath(case.kv_caches, case.block_table, case.seq_lens, n_kv=8, G=4,
+                 scale=1 / math.sqrt(128), cfg=cfg)
+    hp.build_all(); hp.derive(); hp.q.copy_(case.q)
+    ref = hp.step_eager()[0].clone()                 # resident V, fused decode
+    host_v = PinnedHostVSource(case.kv_caches[0])
+    assert not host_v.plane.is_cuda and host_v.plane.is_pinned()
+    # wipe the resident V half: the kernels must not be reading it
+    case.kv_caches[0][:, 1].zero_()
+    out = torch.zeros_like(ref)
+    sparse_paged_decode_fused(hp.q[0, :2], case.kv_caches[0], case.block_table,
+                              case.seq_lens, hp.st, out, host_v, scale=hp.scale)
+    torch.cuda.synchronize()
+    assert torch.equal(out[:2], ref[:2])
+    out2 = torch.zeros_like(ref)
+    sparse_paged_decode_batched(hp.q[0, :2], case.kv_caches[0], case.block_table,
+                                case.seq_lens, hp.st, out2, host_v, scale=hp.scale)
+    torch.cuda.synchronize()
+    assert (out2[:2].float() - ref[:2].float()).abs().max().item() <= 2e-2
