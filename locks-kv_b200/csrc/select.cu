@@ -95,7 +95,7 @@ constexpr int HCOPIES = 4;                        // histogram copies, by lane &
 
 constexpr int RBITS0 = 11, RBITS1 = 11, RBITS2 = 10;
 constexpr int NBINS = 1 << RBITS0;                // 2048 (largest digit)
-constexpr int MAX_CL = 8;
+constexpr int MAX_CL = 16;            // > 8 needs the non-portable cluster attribute
 
 struct SelSmem {
     int hist[NBINS];               // this CTA's histogram of the current digit
@@ -707,16 +707,20 @@ extern "C" int locks_topb_select(
         const int useful = (max_pages + 2047) / 2048;
         while (cl * 2 <= want && cl * 2 <= useful && cl < 4) cl *= 2;
     } else {
-        while (cl < MAX_CL && (max_pages + cl - 1) / cl > KEYS_PER_CTA) cl *= 2;
+        while (cl < 8 && (max_pages + cl - 1) / cl > KEYS_PER_CTA) cl *= 2;
         // more CTAs share the combine when SMs are free
         const int want = sm_count() / max(1, n_kv * n_req);
-        while (cl * 2 <= MAX_CL && cl * 2 <= want && max_pages / (cl * 2) >= 4096)
+        while (cl * 2 <= 8 && cl * 2 <= want && max_pages / (cl * 2) >= 4096)
             cl *= 2;
+        // 16-CTA clusters each need a whole GPC: only for a few rows
+        if (cl == 8 && 2 * 16 * n_kv * n_req <= sm_count() &&
+            max_pages / 16 >= 4096)
+            cl = 16;
     }
     LOCKS_REQUIRE(owner_mode || (max_pages + cl - 1) / cl <= KEYS_PER_CTA,
                   LOCKS_ERR_SIZE,
                   "locks_topb_select: max_pages %d beyond the supported %d",
-                  max_pages, MAX_CL * KEYS_PER_CTA);
+                  max_pages, 8 * KEYS_PER_CTA);
     p.owner_mode = owner_mode ? 1 : 0;
     // key slots per CTA (the compaction reads whole 128-key rows), followed by
     // the interleaved histogram copies
@@ -735,6 +739,8 @@ extern "C" int locks_topb_select(
         cudaFuncSetAttribute(topb_kernel<SEL_THREADS, false>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (KEYS_PER_CTA + 512 + HSLOTS * HCOPIES) * 4);
+        cudaFuncSetAttribute(topb_kernel<SEL_THREADS, false>,
+                             cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         attr_done[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
