@@ -177,7 +177,10 @@ rki4_score_kernel(const ScoreParams p) {
     // does not depend on the page count, so their block-table entries are fetched
     // together with it and the copies start one round trip earlier.
     const int W = NWARP * Z;
-    const int gw = z * NWARP + warp;
+    // warp-major numbering: when the chunks do not divide evenly, the warps that
+    // take one chunk more are spread over all CTAs (and SMs) instead of filling
+    // the first CTAs
+    const int gw = warp * Z + z;
     const int cap = min(p.max_pages, p.bt_width);
     const int32_t* bt = p.block_table + (int64_t)r * p.bt_stride;
     auto bt_at = [&](int page0) -> int {

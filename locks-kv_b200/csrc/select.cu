@@ -98,18 +98,12 @@ constexpr int NBINS = 1 << RBITS0;                // 2048 (largest digit)
 constexpr int MAX_CL = 16;            // > 8 needs the non-portable cluster attribute
 
 struct SelSmem {
-    int hist[NBINS];               // this CTA's histogram of the current digit
-    int tot[NBINS];                // cluster: summed bin slice; CL=1: unused
+    int tot[NBINS];                // sliced mode: cluster totals of the digit (CTA 0)
     int wtot[SEL_WARPS];           // per-warp totals (scans)
     int wtot2[SEL_WARPS];
     float wmax[SEL_WARPS][MAX_G];
     float xmax[MAX_G];             // this CTA's per-head maxima (cluster sweep)
     float hm_sh[MAX_G];
-    int x_slice_tot;               // cluster exchange: total of my bin slice
-    int x_eq;                      // ... ties in my page slice
-    int x_kept;                    // ... kept pages in my page slice
-    uint32_t sh_prefix;
-    int sh_k;
     int sh_i0, sh_i1, sh_i2;
     int x_eq_all[MAX_CL];          // sliced mode: per-CTA tie / sure-kept totals
     int x_sure_all[MAX_CL];
@@ -357,10 +351,6 @@ topb_kernel(const SelParams p) {
     const int c = owner ? 0 : c_phys, CL = owner ? 1 : CL_phys;
     const int s0 = owner ? 0 : cs0, s1 = owner ? span : cs1;
     const int n_loc = s1 - s0;
-    // warp w owns groups [w*gpw, (w+1)*gpw) of 32 consecutive pages
-    const int n_grp = (n_loc + 31) >> 5;
-    const int gpw = (n_grp + NW - 1) / NW;
-    const int g_beg = min(warp * gpw, n_grp), g_end = min(g_beg + gpw, n_grp);
 
     const bool selects = !owner || c_phys == 0;     // this CTA runs a selection
     int* h4 = reinterpret_cast<int*>(keys + p.key_cap);

@@ -123,3 +123,21 @@ def test_global_select_tie_rule():
     keep = par.global_select(s, p, 4)
     # 3, 2, then the two lowest pages among the ties at 1: pages 3 and 5
     assert sorted(p[0][keep[0]].tolist()) == [1, 3, 5, 10]
+
+
+def test_global_page_params_match_the_oracle_rule():
+    """The context-parallel driver derives (n_pages, n_sel_hi, b) of the whole
+    sequence on the host; it must be the per-request rule of the selector."""
+    import numpy as np
+    import locks_oracle as orc
+    from locks import LocksConfig
+    from locks.cp_hotpath import global_page_params
+    for seq_len in (1, 15, 16, 17, 4099, 131073, 1048577):
+        for kw in (dict(budget_pages=128), dict(budget_pages=1), dict(budget=0.1),
+                   dict(budget=0.03)):
+            cfg = LocksConfig(sink_pages=1, window_pages=8, **kw)
+            npg, nsh, b = global_page_params(seq_len, 16, cfg)
+            o = orc.derive_page_params(np.array([seq_len]), 16, 8, 1,
+                                       kw.get("budget_pages", 0),
+                                       kw.get("budget", 0.1))
+            assert (npg, nsh, b) == (int(o[0][0]), int(o[1][0]), int(o[2][0]))
