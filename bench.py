@@ -603,6 +603,134 @@ def run_gpu_cp(args, sh, seq_len):
     os._exit(0)
 
 
+def run_gpu_mla(args, seq_len):
+    """Workload c3: MLA decode, DeepSeek-V2-Lite shape (27 layers, 16 heads, one
+    latent KV head of 512 + 64 rope dims, page 16, batch 8, 128K tokens each,
+    budget 128 pages including 1 sink + 10 recent)."""
+    import dataclasses
+    from locks import synth
+    from locks.selection import mla_select as ms
+
+    sh = synth.CONFIG3
+    if args.layers:
+        sh = dataclasses.replace(sh, n_layers=args.layers)
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    B = 8
+    case = synth.make_mla_case(77, sh, [seq_len] * B, device=dev)
+    L, W = sh.n_layers, sh.width
+    MP = int(case.block_table.shape[1])
+    NB = int(case.caches[0].shape[0])
+
+    def state(budget):
+        st = ms.MlaState(dev, num_layers=L, num_blocks=NB, max_rows=B, max_pages=MP,
+                         budget_pages=budget, sink_pages=sh.sink_pages,
+                         window_pages=sh.window_pages)
+        ms.mla_derive(st, case.seq_lens, B)
+        return st
+    st = state(sh.budget_pages)
+    t_build = timed(lambda: ms.build_prompt_factors(st, case.caches, case.block_table,
+                                                    case.seq_lens), 1)
+    dense = state(MP)                      # budget >= pages: every page is kept
+    dense.n_cache.copy_(st.n_cache)
+    out = torch.zeros(L, B, sh.n_heads, sh.kv_lora_rank, device=dev,
+                      dtype=torch.bfloat16)
+    lse = torch.zeros(L, B, sh.n_heads, device=dev, dtype=torch.float32)
+    scale = case.scale
+
+    def layers():
+        for l in range(L):
+            ms.mla_forward(st, l, case.q[l], case.caches[l], case.block_table,
+                           case.seq_lens, out[l], lse[l], scale)
+
+    def graph_of(fn):
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        return g
+    g_step = graph_of(layers)
+    for _ in range(max(args.warmup, 3)):
+        g_step.replay()
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms_step = timed(g_step.replay, args.steps)
+    it = max(args.steps // 4, 8)
+    g_score = graph_of(lambda: [ms.mla_page_score(st, l, case.q[l], case.caches[l],
+                                                  case.block_table, B, scale)
+                                for l in range(L)])
+    g_sel = graph_of(lambda: [ms.mla_select_pages(st, B) for l in range(L)])
+    g_dec = graph_of(lambda: [ms.mla_decode(st, case.q[l], case.caches[l],
+                                            case.block_table, case.seq_lens, out[l],
+                                            lse[l], B, scale) for l in range(L)])
+    ms_score, ms_sel, ms_dec = (timed(g.replay, it) / L for g in (g_score, g_sel, g_dec))
+    ms.mla_select_pages(dense, B)
+    g_dense = graph_of(lambda: [ms.mla_decode(dense, case.q[l], case.caches[l],
+                                              case.block_table, case.seq_lens,
+                                              out[l], lse[l], B, scale)
+                                for l in range(L)])
+    ms_dense = timed(g_dense.replay, max(it // 4, 3))
+    # end to end: q from pinned host memory in, o and lse back
+    q_host = case.q.cpu().pin_memory()
+    o_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+
+    def e2e_step():
+        case.q.copy_(q_host, non_blocking=True)
+        g_step.replay()
+        o_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    for _ in range(3):
+        e2e_step()
+    ms_e2e = timed(e2e_step, args.steps)
+    clocks = sampler.stop()
+    st.check_status()
+    n_cached = seq_len // sh.page
+    npg = -(-seq_len // sh.page)
+    rec_b = 8448 + sh.page * sh.rope_dim * 2          # factors + rope keys per page
+    page_b = sh.page * W * 2
+    b_score = L * B * n_cached * rec_b
+    b_dec = L * B * min(sh.budget_pages, npg) * page_b
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak = (float(json.load(open(peaks_path))["hbm_gbs"])
+            if os.path.exists(peaks_path) else 6650.0)
+    ach = (b_score / L) / (ms_score * 1e-3) / 1e9
+    return {
+        "metric": "sparse_decode_tokens_per_s", "value": B / (ms_step * 1e-3),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "tpot_ms": ms_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"c3: MLA, {L} layers, {sh.n_heads} heads, latent "
+                               f"{W}, page {sh.page}, batch {B}, ctx {seq_len - 1}, "
+                               f"budget {sh.budget_pages} pages incl. "
+                               f"{sh.sink_pages} sink + {sh.window_pages} recent",
+                   "l2_policy": "inputs larger than L2 "
+                                f"({(b_score + b_dec) / 1e9:.2f} GB per step)"},
+        "clocks": clocks,
+        "e2e": {"value": B / (ms_e2e * 1e-3), "unit": "tokens/s",
+                "ms_per_step": ms_e2e, "h2d_bytes_per_step": q_host.numel() * 2,
+                "d2h_bytes_per_step": o_host.numel() * 2},
+        "gpu_launches": 3 * L * args.steps,
+        "roofline": {"kernel": "mla_score_kernel", "bound": "hbm", "achieved": ach,
+                     "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                     "traffic": None,
+                     "bytes_per_launch": b_score / L,
+                     "us_per_launch": ms_score * 1e3},
+        "step_roofline": {"algorithmic_bytes": b_score + b_dec,
+                          "achieved_gbs": (b_score + b_dec) / (ms_step * 1e-3) / 1e9,
+                          "frac_of_measured_peak":
+                              (b_score + b_dec) / (ms_step * 1e-3) / 1e9 / peak},
+        "stages_us_per_layer": {"score": ms_score * 1e3, "select": ms_sel * 1e3,
+                                "decode": ms_dec * 1e3},
+        "dense": {"ms_per_step": ms_dense, "bytes": L * B * npg * page_b,
+                  "gbs": L * B * npg * page_b / (ms_dense * 1e-3) / 1e9,
+                  "speedup_sparse_over_dense": ms_dense / ms_step},
+        "build": {"factors_ms": t_build},
+        "cpu_baseline": None,
+    }
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -615,6 +743,10 @@ def main():
     ap.add_argument("--layers", type=int, default=None,
                     help="override the layer count (quick experiments only)")
     args = ap.parse_args()
+    if args.workload_name == "c3":
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps(run_gpu_mla(args, (args.ctx or 131072) + 1)), flush=True)
+        return
     sh, ctx = workload(args.workload_name, args.ctx)
     if args.layers:
         import dataclasses

@@ -14,9 +14,9 @@
 //
 // Math per page, on warp-level tensor-core fragments whose 16 rows are the
 // query heads of the GQA group:  S = Q K^T (bf16, 16 m16n8k16 steps), online
-// softmax in fp32, O += P V with P split into two bf16 terms (32 steps), i.e.
-// P keeps 16 mantissa bits.  The warps' (m, l, O) are combined through
-// shared memory; the CTA then stores one split partial (split mode), or, in
+// softmax in fp32, O += P V as an fp16 product with fp32 accumulation (P in fp16,
+// V converted bf16 -> fp16 in registers: the reference decode's arithmetic).
+// The warps' (m, l, O) are combined through shared memory; the CTA then stores one split partial (split mode), or, in
 // fused mode, the CTAs of a thread-block cluster -- one cluster per (request,
 // kv-head), each CTA walking its share of the page list -- exchange their
 // (m, l, O) through distributed shared memory and write the normalised bf16
@@ -42,6 +42,25 @@ __device__ long long g_dec_ts[16];
 #else
 #define DEC_TS(i)
 #endif
+
+__device__ __forceinline__ uint32_t pack_f16x2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+// two bf16 (packed) -> two fp16 (packed); exact for |x| < 65504 with <= 11
+// significant bits, which bf16 values (8 bits) always have
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
+    return pack_f16x2(__uint_as_float(v << 16), __uint_as_float(v & 0xFFFF0000u));
+}
+// D(16x8,f32) += A(16x16,f16,row) * B(16x8,f16,col)
+__device__ __forceinline__ void mma_f16_k16(float (&d)[4], uint32_t a0, uint32_t a1,
+                                            uint32_t a2, uint32_t a3, uint32_t b0,
+                                            uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 
 constexpr int DW = 8;                 // warps per CTA
 constexpr int DTHREADS = DW * 32;
@@ -293,22 +312,14 @@ decode_kernel(const DecParams p) {
                 acc[i][0] *= al_lo; acc[i][1] *= al_lo;
                 if (G_HI) { acc[i][2] *= al_hi; acc[i][3] *= al_hi; }
             }
-            // ---- P as hi + lo bf16 (A operand, k = 16 tokens) ------------------
-            uint32_t ph[4], pl[4];
-            {
-                float hi[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    hi[i] = __bfloat162float(__float2bfloat16_rn(pr[i]));
-                ph[0] = pack_bf16x2(hi[0], hi[1]);           // row gid,   t 0-7
-                ph[1] = pack_bf16x2(hi[4], hi[5]);           // row gid+8, t 0-7
-                ph[2] = pack_bf16x2(hi[2], hi[3]);           // row gid,   t 8-15
-                ph[3] = pack_bf16x2(hi[6], hi[7]);           // row gid+8, t 8-15
-                pl[0] = pack_bf16x2(pr[0] - hi[0], pr[1] - hi[1]);
-                pl[1] = pack_bf16x2(pr[4] - hi[4], pr[5] - hi[5]);
-                pl[2] = pack_bf16x2(pr[2] - hi[2], pr[3] - hi[3]);
-                pl[3] = pack_bf16x2(pr[6] - hi[6], pr[7] - hi[7]);
-            }
+            // ---- P in fp16 (A operand, k = 16 tokens); V bf16 -> fp16 on the fly.
+            // Same arithmetic as the reference decode (fp16 P.V product with
+            // fp32 accumulation, attention/decode.py:314) --------------------------
+            uint32_t ph[4];
+            ph[0] = pack_f16x2(pr[0], pr[1]);                // row gid,   t 0-7
+            ph[1] = pack_f16x2(pr[4], pr[5]);                // row gid+8, t 0-7
+            ph[2] = pack_f16x2(pr[2], pr[3]);                // row gid,   t 8-15
+            ph[3] = pack_f16x2(pr[6], pr[7]);                // row gid+8, t 8-15
             // ---- O += P V ------------------------------------------------------
             {
                 const int t = (lane & 7) + 8 * ((lane >> 3) & 1);
@@ -317,10 +328,10 @@ decode_kernel(const DecParams p) {
                 for (int dp = 0; dp < 8; ++dp) {
                     uint32_t vb[4];
                     ldmatrix_x4_trans(vb, a0 + 32 * dp);
-                    mma_bf16_k16(acc[2 * dp], ph[0], ph[1], ph[2], ph[3], vb[0], vb[1]);
-                    mma_bf16_k16(acc[2 * dp], pl[0], pl[1], pl[2], pl[3], vb[0], vb[1]);
-                    mma_bf16_k16(acc[2 * dp + 1], ph[0], ph[1], ph[2], ph[3], vb[2], vb[3]);
-                    mma_bf16_k16(acc[2 * dp + 1], pl[0], pl[1], pl[2], pl[3], vb[2], vb[3]);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) vb[i] = bf16x2_to_f16x2(vb[i]);
+                    mma_f16_k16(acc[2 * dp], ph[0], ph[1], ph[2], ph[3], vb[0], vb[1]);
+                    mma_f16_k16(acc[2 * dp + 1], ph[0], ph[1], ph[2], ph[3], vb[2], vb[3]);
                 }
             }
         }

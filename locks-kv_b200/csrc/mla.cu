@@ -373,13 +373,16 @@ constexpr int MD_THREADS = MD_WARPS * 32;
 constexpr int MD_STAGES = 2;
 constexpr int KV_PITCH = WIDTH * 2 + 16;      // 1168 B per staged row
 constexpr int OUT_PITCH = LKV + 4;            // floats
-constexpr int MD_MAX_CL = 8;
+constexpr int MD_MAX_CL = 16;                // > 8 needs the non-portable cluster attribute
 
 struct __align__(128) MdSmem {
     uint8_t kv[MD_STAGES][PG][KV_PITCH];
     uint8_t q[NH][KV_PITCH];
-    float acc[NH][OUT_PITCH];
-    float cta_m[NH], cta_l[NH];
+    // cluster exchange: CTA c pushes its (m, l) to every CTA and the slice of
+    // its O that CTA d normalises into xacc[c * per_e ...] of CTA d
+    float xacc[NH * LKV + 64];
+    float xm[MD_MAX_CL][NH], xl[MD_MAX_CL][NH];
+    float sred[MD_WARPS][NH][PG + 1];   // per-warp partial logits of a page
     uint64_t full[MD_STAGES];
 };
 
@@ -400,6 +403,17 @@ struct MlaDecParams {
     int* status;
 };
 
+#ifdef LOCKS_MLA_TIMING
+__device__ long long g_mla_ts[64];
+#define MLA_TS(i)                                                             \
+    do {                                                                      \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && (i) < 64) \
+            g_mla_ts[i] = clock64();                                          \
+    } while (0)
+#else
+#define MLA_TS(i)
+#endif
+
 __global__ void __launch_bounds__(MD_THREADS) mla_decode_kernel(const MlaDecParams p) {
     extern __shared__ __align__(128) uint8_t md_raw[];
     MdSmem& sm = *reinterpret_cast<MdSmem*>(md_raw);
@@ -408,6 +422,7 @@ __global__ void __launch_bounds__(MD_THREADS) mla_decode_kernel(const MlaDecPara
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gid = lane >> 2, tig = lane & 3;
 
+    MLA_TS(0);
     const int seq_len = p.seq_lens[row];
     const int cnt = min(max(p.page_cnt[row], 0), p.max_pages);
     const int per = (cnt + CL - 1) / CL;
@@ -418,28 +433,41 @@ __global__ void __launch_bounds__(MD_THREADS) mla_decode_kernel(const MlaDecPara
         for (int s = 0; s < MD_STAGES; ++s) mbar_init(&sm.full[s], 1);
         mbar_fence_init();
     }
-    __syncthreads();
+    // remote shared memory may be written once every CTA of the cluster runs
+    cluster.sync();
 
     const int32_t* tab = p.page_table + (int64_t)row * p.max_pages;
     const int32_t* bt = p.block_table + (int64_t)row * p.bt_stride;
-    int nv[MD_STAGES] = {0, 0};
-    // every thread computes n_valid; warp 0 issues the row copies
+    int nv[MD_STAGES] = {};
+    // Page-table entry and physical block of this CTA's pages, 32 at a time (lane i
+    // of every warp holds entry i of the window): the two dependent index loads
+    // are paid once per window, not once per page.
+    int win_pt = -1, win_blk = 0;
+    auto load_window = [&](int k0) {
+        const int k = k0 + lane;
+        win_pt = -1; win_blk = 0;
+        if (k < np) {
+            win_pt = tab[j0 + k];
+            win_blk = bt[max(win_pt, 0)];
+        }
+    };
+    // every thread computes n_valid; the 16 row copies are issued by 4 lanes of
+    // each warp (a bulk-copy request costs its issuer ~80 cycles)
     auto issue = [&](int k) {
         const int stage = k % MD_STAGES;
-        int pt = tab[j0 + k];
+        const int pt = __shfl_sync(0xffffffffu, win_pt, k & 31);
+        const int blk = max(__shfl_sync(0xffffffffu, win_blk, k & 31), 0);
         const int n_valid = (pt >= 0) ? min(max(seq_len - pt * PG, 0), PG) : 0;
         nv[stage] = n_valid;
-        if (warp != 0) return;
-        pt = max(pt, 0);
-        const int blk = max(bt[pt], 0);
         uint64_t* bar = &sm.full[stage];
         fence_proxy_async();
-        if (lane == 0) mbar_expect_tx(bar, (uint32_t)n_valid * (WIDTH * 2));
-        __syncwarp();
-        if (lane < PG) {
-            uint8_t* dst = &sm.kv[stage][lane][0];
-            if (lane < n_valid) {
-                bulk_g2s(dst, p.cache + (int64_t)blk * p.sb + (int64_t)lane * p.st,
+        if (tid == 0) mbar_expect_tx(bar, (uint32_t)n_valid * (WIDTH * 2));
+        constexpr int RPW = PG / MD_WARPS;            // rows per warp
+        if (lane < RPW) {
+            const int t = warp * RPW + lane;
+            uint8_t* dst = &sm.kv[stage][t][0];
+            if (t < n_valid) {
+                bulk_g2s(dst, p.cache + (int64_t)blk * p.sb + (int64_t)t * p.st,
                          WIDTH * 2, bar);
             } else {
                 uint4* d4 = reinterpret_cast<uint4*>(dst);
@@ -447,19 +475,31 @@ __global__ void __launch_bounds__(MD_THREADS) mla_decode_kernel(const MlaDecPara
             }
         }
     };
+    MLA_TS(1);
+    load_window(0);
     for (int k = 0; k < MD_STAGES && k < np; ++k) issue(k);
 
-    // stage q (bf16, padded rows)
+    // stage q (bf16, padded rows): 16-byte loads, all in flight before the stores
     {
-        const __nv_bfloat16* q = p.q + (int64_t)row * p.q_stride_row;
-        for (int e = tid; e < NH * (WIDTH / 2); e += MD_THREADS) {
-            const int h = e / (WIDTH / 2), d2 = e % (WIDTH / 2);
-            *reinterpret_cast<uint32_t*>(&sm.q[h][4 * d2]) =
-                *reinterpret_cast<const uint32_t*>(q + h * WIDTH + 2 * d2);
+        const uint4* q4 = reinterpret_cast<const uint4*>(p.q + (int64_t)row * p.q_stride_row);
+        constexpr int C16 = WIDTH * 2 / 16;           // 72 chunks per head
+        constexpr int NQ = (NH * C16 + MD_THREADS - 1) / MD_THREADS;
+        uint4 v[NQ];
+#pragma unroll
+        for (int i = 0; i < NQ; ++i) {
+            const int e = tid + i * MD_THREADS;
+            v[i] = (e < NH * C16) ? q4[e] : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int i = 0; i < NQ; ++i) {
+            const int e = tid + i * MD_THREADS;
+            if (e < NH * C16)
+                *reinterpret_cast<uint4*>(&sm.q[e / C16][16 * (e % C16)]) = v[i];
         }
     }
     __syncthreads();
 
+    MLA_TS(2);
     const int a_row = (lane & 7) + 8 * ((lane >> 3) & 1);
     const uint32_t q_addr = smem_u32(&sm.q[a_row][0]) + 16 * (lane >> 4);
     // K operand (non-transposed): token = (lane&7) + 8*((lane>>4)&1), col half (lane>>3)&1
@@ -476,20 +516,45 @@ __global__ void __launch_bounds__(MD_THREADS) mla_decode_kernel(const MlaDecPara
 
     for (int k = 0; k < np; ++k) {
         const int stage = k % MD_STAGES;
+        MLA_TS(4 + 4 * k);
         mbar_wait(&sm.full[stage], (uint32_t)((k / MD_STAGES) & 1), p.status);
+        MLA_TS(5 + 4 * k);
         __syncthreads();                       // zero-filled rows are visible too
         const int n_valid = nv[stage];
         if (n_valid > 0) {
             const uint32_t kbase = smem_u32(&sm.kv[stage][0][0]);
+            // Q K^T: the 36 k-steps are split over the 4 warps (9 each); the
+            // partial 16 x 16 logit tiles meet in shared memory
             float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
             const uint32_t ka = kbase + kt * KV_PITCH + kcol;
-#pragma unroll 4
-            for (int s = 0; s < WIDTH / 16; ++s) {
+            constexpr int KS = (WIDTH / 16) / MD_WARPS;
+#pragma unroll
+            for (int si = 0; si < KS; ++si) {
+                const int s = warp * KS + si;
                 uint32_t qa[4], kb[4];
                 ldmatrix_x4(qa, q_addr + 32 * s);
                 ldmatrix_x4(kb, ka + 32 * s);
                 mma_bf16_k16(s0, qa[0], qa[1], qa[2], qa[3], kb[0], kb[1]);
                 mma_bf16_k16(s1, qa[0], qa[1], qa[2], qa[3], kb[2], kb[3]);
+            }
+            {
+                float (*sr)[PG + 1] = sm.sred[warp];
+                sr[gid][2 * tig] = s0[0];         sr[gid][2 * tig + 1] = s0[1];
+                sr[gid + 8][2 * tig] = s0[2];     sr[gid + 8][2 * tig + 1] = s0[3];
+                sr[gid][2 * tig + 8] = s1[0];     sr[gid][2 * tig + 9] = s1[1];
+                sr[gid + 8][2 * tig + 8] = s1[2]; sr[gid + 8][2 * tig + 9] = s1[3];
+            }
+            __syncthreads();
+            MLA_TS(6 + 4 * k);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s0[i] = s1[i] = 0.f;
+#pragma unroll
+            for (int w = 0; w < MD_WARPS; ++w) {
+                const float (*sr)[PG + 1] = sm.sred[w];
+                s0[0] += sr[gid][2 * tig];         s0[1] += sr[gid][2 * tig + 1];
+                s0[2] += sr[gid + 8][2 * tig];     s0[3] += sr[gid + 8][2 * tig + 1];
+                s1[0] += sr[gid][2 * tig + 8];     s1[1] += sr[gid][2 * tig + 9];
+                s1[2] += sr[gid + 8][2 * tig + 8]; s1[3] += sr[gid + 8][2 * tig + 9];
             }
             const int ta = 2 * tig, tb = 2 * tig + 1;
             const float scale = p.scale;
@@ -550,54 +615,94 @@ __global__ void __launch_bounds__(MD_THREADS) mla_decode_kernel(const MlaDecPara
                 mma_bf16_k16(acc[2 * dp + 1], pl[0], pl[1], pl[2], pl[3], vb[2], vb[3]);
             }
         }
+        MLA_TS(7 + 4 * k);
         __syncthreads();                       // the stage is free again
-        if (k + MD_STAGES < np) issue(k + MD_STAGES);
+        if (k + MD_STAGES < np) {
+            if (((k + MD_STAGES) & 31) == 0) load_window(k + MD_STAGES);
+            issue(k + MD_STAGES);
+        }
     }
 
-    // ---- CTA result (every warp holds the same m, l; its own 128 channels) ---
+    // ---- cluster merge, push style: every warp holds the same (m, l) and its own
+    // 128 output channels in registers; each value goes straight into the shared
+    // memory of the CTA that normalises it (CTA d owns output elements
+    // [d * per_e, (d + 1) * per_e)); one cluster barrier, then a local finish ----
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    const int n_el = NH * LKV;
+    const int per_e = (((n_el + CL - 1) / CL) + 3) & ~3;      // multiple of 4: 16-byte pushes
     if (warp == 0 && tig == 0) {
-        sm.cta_m[gid] = m_lo; sm.cta_l[gid] = l_lo;
-        sm.cta_m[gid + 8] = m_hi; sm.cta_l[gid + 8] = l_hi;
+        for (int d = 0; d < CL; ++d) {
+            float* rm = cluster.map_shared_rank(&sm.xm[c][0], d);
+            float* rl = cluster.map_shared_rank(&sm.xl[c][0], d);
+            rm[gid] = m_lo; rm[gid + 8] = m_hi;
+            rl[gid] = l_lo; rl[gid + 8] = l_hi;
+        }
     }
+    // O goes through local shared memory so that every push instruction sends 512
+    // contiguous bytes of ONE head to ONE CTA (a fragment-shaped push would
+    // scatter 32-byte pieces over 16 CTAs per instruction)
+    // (the page ring is idle after the loop's last barrier: it is the staging area)
+    static_assert(sizeof(sm.kv) >= NH * OUT_PITCH * sizeof(float), "staging fits the ring");
+    float (*stage_o)[OUT_PITCH] = reinterpret_cast<float (*)[OUT_PITCH]>(&sm.kv[0][0][0]);
 #pragma unroll
     for (int nt = 0; nt < 16; ++nt) {
         const int col = warp * 128 + 8 * nt + 2 * tig;
-        *reinterpret_cast<float2*>(&sm.acc[gid][col]) = make_float2(acc[nt][0], acc[nt][1]);
-        *reinterpret_cast<float2*>(&sm.acc[gid + 8][col]) = make_float2(acc[nt][2], acc[nt][3]);
+        *reinterpret_cast<float2*>(&stage_o[gid][col]) = make_float2(acc[nt][0], acc[nt][1]);
+        *reinterpret_cast<float2*>(&stage_o[gid + 8][col]) = make_float2(acc[nt][2], acc[nt][3]);
     }
-    cluster.sync();
-    {
-        const int n_el = NH * LKV;
-        const int per_e = (n_el + CL - 1) / CL;
-        for (int e = c * per_e + tid; e < min((c + 1) * per_e, n_el); e += MD_THREADS) {
-            const int h = e / LKV, d = e % LKV;
-            float M = -INFINITY;
-            for (int cc = 0; cc < CL; ++cc)
-                M = fmaxf(M, *cluster.map_shared_rank(&sm.cta_m[h], cc));
-            float Ls = 0.f, o = 0.f;
-            for (int cc = 0; cc < CL; ++cc) {
-                const float lw = *cluster.map_shared_rank(&sm.cta_l[h], cc);
-                const float mw = *cluster.map_shared_rank(&sm.cta_m[h], cc);
-                const float wt = (lw > 0.f) ? __expf(mw - M) : 0.f;
-                Ls += wt * lw;
-                o += wt * (*cluster.map_shared_rank(&sm.acc[h][d], cc));
-            }
-            p.out[((int64_t)row * NH + h) * LKV + d] =
-                __float2bfloat16_rn(Ls > 0.f ? o / Ls : 0.f);
-            if (d == 0) p.lse[(int64_t)row * NH + h] = (Ls > 0.f) ? M + __logf(Ls) : 0.f;
+    __syncthreads();
+    for (int i = tid; i < NH * (LKV / 4); i += MD_THREADS) {
+        const int h = i / (LKV / 4), c4 = i % (LKV / 4);
+        const float4 val = *reinterpret_cast<const float4*>(&stage_o[h][4 * c4]);
+        const int e = h * LKV + 4 * c4;
+        const int d = e / per_e;
+        float* dst = cluster.map_shared_rank(&sm.xacc[0], d) + c * per_e +
+                     (e - d * per_e);
+        *reinterpret_cast<float4*>(dst) = val;
+    }
+    MLA_TS(60);
+    cluster.sync();                              // every CTA's pushes have landed
+    MLA_TS(61);
+    // merge weights once per (CTA, head): w[cc][h] = exp(m - M) / sum, lse[h]
+    for (int h = tid; h < NH; h += MD_THREADS) {
+        float M = -INFINITY;
+        for (int cc = 0; cc < CL; ++cc) M = fmaxf(M, sm.xm[cc][h]);
+        float Ls = 0.f;
+        for (int cc = 0; cc < CL; ++cc) {
+            const float lw = sm.xl[cc][h];
+            const float wt = (lw > 0.f) ? __expf(sm.xm[cc][h] - M) : 0.f;
+            sm.xm[cc][h] = wt;                       // reuse: now the weight
+            Ls += wt * lw;
         }
+        const float inv = (Ls > 0.f) ? 1.f / Ls : 0.f;
+        for (int cc = 0; cc < CL; ++cc) sm.xm[cc][h] *= inv;
+        if (c == 0) p.lse[(int64_t)row * NH + h] = (Ls > 0.f) ? M + __logf(Ls) : 0.f;
     }
-    cluster.sync();
+    __syncthreads();
+    for (int el = tid; el < per_e; el += MD_THREADS) {
+        const int e = c * per_e + el;
+        if (e >= n_el) break;
+        const int h = e / LKV, d = e % LKV;
+        float o = 0.f;
+        for (int cc = 0; cc < CL; ++cc) o += sm.xm[cc][h] * sm.xacc[cc * per_e + el];
+        p.out[((int64_t)row * NH + h) * LKV + d] = __float2bfloat16_rn(o);
+    }
+    MLA_TS(62);
 }
 
 }  // namespace
 }  // namespace locks
 
 using namespace locks;
+
+#ifdef LOCKS_MLA_TIMING
+extern "C" int locks_debug_mla_timing(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, locks::g_mla_ts, sizeof(long long) * 64);
+}
+#endif
 
 extern "C" int locks_mla_build_factors(const void* cache, int64_t stride_block,
                                        int64_t stride_tok, void* records,
@@ -711,9 +816,9 @@ extern "C" int locks_mla_decode(const void* q, int64_t q_stride_row,
     LOCKS_REQUIRE(n_rows >= 0 && n_rows <= 65535 && max_pages >= 1, LOCKS_ERR_ARG,
                   "locks_mla_decode: bad size argument");
     LOCKS_REQUIRE(stride_block % 8 == 0 && stride_tok % 8 == 0 &&
-                      q_stride_row % 2 == 0 &&
+                      q_stride_row % 8 == 0 &&
                       (reinterpret_cast<uintptr_t>(cache) & 15) == 0 &&
-                      (reinterpret_cast<uintptr_t>(q) & 3) == 0,
+                      (reinterpret_cast<uintptr_t>(q) & 15) == 0,
                   LOCKS_ERR_ARG, "locks_mla_decode: misaligned argument");
     if (n_rows == 0) return LOCKS_OK;
     const int smem = (int)sizeof(MdSmem);
@@ -723,12 +828,16 @@ extern "C" int locks_mla_decode(const void* q, int64_t q_stride_row,
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
         cudaFuncSetAttribute(mla_decode_kernel,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaFuncSetAttribute(mla_decode_kernel,
+                             cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         attr_done[dev] = true;
     }
     int cl = 1;
     {
         const int want = sm_count() / max(1, n_rows);
-        while (cl * 2 <= want && cl < MD_MAX_CL) cl *= 2;
+        while (cl * 2 <= want && cl < 8) cl *= 2;
+        // 16-CTA clusters each need a whole GPC: only for a few rows
+        if (cl == 8 && 16 * n_rows <= sm_count()) cl = MD_MAX_CL;
     }
     MlaDecParams p;
     p.q = static_cast<const __nv_bfloat16*>(q); p.q_stride_row = q_stride_row;
