@@ -272,7 +272,10 @@ int locks_cp_select(const float* cand, int64_t cand_stride, int32_t* page_table,
  * this process (peers[rank] = the local pointer).  All ranks must issue the same
  * sequence of exchanges on a region, at most 8 ranks.  nbytes, slot_bytes:
  * multiples of 16, nbytes <= slot_bytes.  mode 0: out = (world, nbytes);
- * mode 1: out = nbytes.  A rank that does not see all peers within about two
+ * mode 1: out = nbytes.  Modes 2 and 3 are the same two operations through
+ * 8-byte {word, epoch} packets that the receiver polls directly (no fence, no
+ * flag: lower latency for payloads of a few KB; 2 * nbytes <= slot_bytes; a
+ * region must be used with one of the two transports only).  A rank that does not see all peers within about two
  * seconds sets *status to LOCKS_ST_WAIT_TIMEOUT and returns (out undefined). */
 int locks_cp_region_bytes(int slot_bytes, int64_t* out);
 int locks_cp_alloc(int64_t bytes, void** out);

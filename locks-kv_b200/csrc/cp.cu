@@ -46,14 +46,25 @@ cp_select_kernel(const float* __restrict__ cand, int32_t* __restrict__ page_tabl
                  int32_t* __restrict__ page_cnt, int64_t rank_stride, int world,
                  int rank, int n_kv, int cap, int max_pages, int b, int sink_loc,
                  int nsh_loc) {
-    extern __shared__ int keep_sh[];                      // cap flags, then scan
+    extern __shared__ int keep_sh[];       // cap flags | world * cap keys | pages
     __shared__ int wsum[32];
     const int kh = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nw = blockDim.x >> 5;
     int32_t* tab = page_table + (int64_t)kh * max_pages;
-    const float* my_s = cand + rank * rank_stride + (int64_t)kh * cap;
-    const float* my_p = my_s + (int64_t)n_kv * cap;
+    uint32_t* ckey = reinterpret_cast<uint32_t*>(keep_sh + cap);
+    float* cpage = reinterpret_cast<float*>(ckey + world * cap);
+    // all candidates of this kv-head into shared memory (coalesced, all in
+    // flight): the counting loop below would otherwise pay an L2 round trip per
+    // candidate.  Key 0 = "no candidate" (a real score's key is never 0).
+    for (int i = tid; i < world * cap; i += blockDim.x) {
+        const int r = i / cap, c = i - r * cap;
+        const float* s = cand + r * rank_stride + (int64_t)kh * cap;
+        const float sc = s[c];
+        ckey[i] = (sc > -INFINITY) ? max(f2key(sc), 1u) : 0u;
+        cpage[i] = s[(int64_t)n_kv * cap + c];
+    }
+    __syncthreads();
 
     for (int j = warp; j < cap; j += nw) {
         const int e = tab[j];
@@ -61,23 +72,17 @@ cp_select_kernel(const float* __restrict__ cand, int32_t* __restrict__ page_tabl
         const bool sel = live && e >= sink_loc && e < nsh_loc;
         int keep = live ? 1 : 0;
         if (sel) {                                        // warp-uniform
-            const uint32_t key = f2key(my_s[j]);
-            const float pg = my_p[j];
+            const uint32_t key = ckey[rank * cap + j];
+            const float pg = cpage[rank * cap + j];
             int beat = 0;
-            for (int r = 0; r < world; ++r) {
-                const float* s = cand + r * rank_stride + (int64_t)kh * cap;
-                const float* pp = s + (int64_t)n_kv * cap;
-                for (int c = lane; c < cap; c += 32) {
-                    const float sc = s[c];
-                    const uint32_t k2 = f2key(sc);
-                    const bool real = sc > -INFINITY;
-                    beat += (real && (k2 > key || (k2 == key && pp[c] < pg))) ? 1 : 0;
-                }
+            for (int c = lane; c < world * cap; c += 32) {
+                const uint32_t k2 = ckey[c];
+                beat += (k2 > key || (k2 == key && k2 != 0u && cpage[c] < pg)) ? 1 : 0;
             }
 #pragma unroll
             for (int o = 16; o >= 1; o >>= 1)
                 beat += __shfl_xor_sync(0xffffffffu, beat, o);
-            keep = (beat < b && my_s[j] > -INFINITY) ? 1 : 0;
+            keep = (beat < b && key != 0u) ? 1 : 0;
         }
         if (lane == 0) keep_sh[j] = keep;
     }
@@ -140,10 +145,19 @@ extern "C" int locks_cp_select(const float* cand, int64_t cand_stride,
                       n_kv <= 65535 && cap >= 1 && cap <= max_pages && b >= 0 &&
                       cand_stride >= (int64_t)2 * n_kv * cap,
                   LOCKS_ERR_ARG, "locks_cp_select: bad size argument");
-    LOCKS_REQUIRE(cap <= 48 * 1024 / 4, LOCKS_ERR_SIZE,
-                  "locks_cp_select: %d entries per rank beyond the supported %d",
-                  cap, 48 * 1024 / 4);
-    cp_select_kernel<<<n_kv, 1024, cap * sizeof(int),
+    const size_t smem = ((size_t)cap + 2 * (size_t)world * cap) * sizeof(int);
+    LOCKS_REQUIRE(smem <= 200 * 1024, LOCKS_ERR_SIZE,
+                  "locks_cp_select: %d entries per rank x %d ranks beyond the "
+                  "shared-memory staging area", cap, world);
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        cudaFuncSetAttribute(cp_select_kernel,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        attr_done[dev] = true;
+    }
+    cp_select_kernel<<<n_kv, 1024, smem,
                        static_cast<cudaStream_t>(stream)>>>(
         cand, page_table, page_cnt, cand_stride, world, rank, n_kv, cap,
         max_pages, b, sink_loc, nsh_loc);
@@ -193,7 +207,9 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
 }
 
 // mode 0: out = (world, nbytes) gathered payloads; mode 1: out = element-wise
-// unsigned maximum of the ranks' uint32 payloads (nbytes / 4 words)
+// unsigned maximum of the ranks' uint32 payloads (nbytes / 4 words); modes 2, 3:
+// the same two through 8-byte {word, epoch} packets (small payloads; a region
+// is used with ONE of the two transports for its whole life)
 __global__ void __launch_bounds__(1024)
 cp_exchange_kernel(XchgPeers peers, int world, int rank, const uint4* payload,
                    int nbytes, int slot_bytes, uint8_t* out, int mode,
@@ -213,6 +229,45 @@ cp_exchange_kernel(XchgPeers peers, int world, int rank, const uint4* payload,
     const int par = (int)(e & 1u);
     const int n16 = nbytes >> 4;
     const int64_t slot_off = X_DATA + ((int64_t)par * XMAX + rank) * slot_bytes;
+    if (mode & 2) {
+        // ---- flag-in-packet transport for small payloads: every 32-bit word
+        // travels as an 8-byte packet {word, epoch} (one store, atomic), the
+        // receiver polls the packet itself: no fence, no separate flag ----------
+        const int nwords = nbytes >> 2;
+        const uint32_t* pw = reinterpret_cast<const uint32_t*>(payload);
+        for (int r = 0; r < world; ++r) {
+            uint2* dst = reinterpret_cast<uint2*>(peers.base[r] + slot_off);
+            for (int i = tid; i < nwords; i += blockDim.x)
+                asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};"
+                             ::"l"(dst + i), "r"(pw[i]), "r"(e) : "memory");
+        }
+        const uint8_t* half = me + X_DATA + (int64_t)par * XMAX * slot_bytes;
+        const unsigned long long t0 = gtime_ns();
+        bool late = false;
+        for (int i = tid; i < nwords; i += blockDim.x) {
+            uint32_t m = 0u;
+            for (int r = 0; r < world; ++r) {
+                const uint2* src =
+                    reinterpret_cast<const uint2*>(half + (int64_t)r * slot_bytes) + i;
+                uint32_t x, y;
+                for (;;) {
+                    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];"
+                                 : "=r"(x), "=r"(y) : "l"(src) : "memory");
+                    if (y == e) break;
+                    if (gtime_ns() - t0 > X_WAIT_NS) { late = true; break; }
+                }
+                if (late) break;
+                if (mode == 2)
+                    reinterpret_cast<uint32_t*>(out)[(int64_t)r * nwords + i] = x;
+                else
+                    m = max(m, x);
+            }
+            if (late) break;
+            if (mode == 3) reinterpret_cast<uint32_t*>(out)[i] = m;
+        }
+        if (late && status) atomicExch(status, LOCKS_ST_WAIT_TIMEOUT);
+        return;
+    }
     for (int r = 0; r < world; ++r) {
         uint4* dst = reinterpret_cast<uint4*>(peers.base[r] + slot_off);
         for (int i = tid; i < n16; i += blockDim.x) dst[i] = payload[i];
@@ -324,7 +379,8 @@ extern "C" int locks_cp_exchange(void* const* peers, int world, int rank,
     LOCKS_REQUIRE(world >= 1 && world <= XMAX && rank >= 0 && rank < world,
                   LOCKS_ERR_ARG, "locks_cp_exchange: supports 1..%d ranks", XMAX);
     LOCKS_REQUIRE(nbytes > 0 && (nbytes & 15) == 0 && nbytes <= slot_bytes &&
-                      (slot_bytes & 15) == 0 && (mode == 0 || mode == 1) &&
+                      (slot_bytes & 15) == 0 && mode >= 0 && mode <= 3 &&
+                      (!(mode & 2) || 2 * nbytes <= slot_bytes) &&
                       (reinterpret_cast<uintptr_t>(payload) & 15) == 0 &&
                       (reinterpret_cast<uintptr_t>(out) & 15) == 0,
                   LOCKS_ERR_ARG,

@@ -62,8 +62,8 @@ class ContextParallelHotPath:
 
     def __init__(self, kv_caches: List[torch.Tensor], block_table: torch.Tensor,
                  *, seq_len: int, p0: int, p1: int, n_kv: int, G: int,
-                 scale: float, cfg: LocksConfig, group=None, split: int = 2,
-                 transport: str = "peer"):
+                 scale: float, cfg: LocksConfig, group=None,
+                 split: Optional[int] = None, transport: str = "peer"):
         dev = kv_caches[0].device
         self.device, self.cfg, self.group = dev, cfg, group
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -105,6 +105,11 @@ class ContextParallelHotPath:
         self.cap = min(n_loc, b + cfg.sink_pages + cfg.window_pages + 1)
         # split-K partials of all ranks: [world][m | l | acc], this rank writes
         # (and all-gathers in place) its own set
+        # a rank attends about (b + sink + window) / world pages per kv head: one
+        # CTA (8 warps) per head is enough from 4 ranks on, and every split less
+        # halves the partial set that has to travel
+        if split is None:
+            split = 1 if self.world >= 4 else 2
         self.split = int(split)
         n_ml = n_kv * self.split * G
         self.n_ml = n_ml
@@ -133,8 +138,13 @@ class ContextParallelHotPath:
         self.hm_pad = None
         if self.transport == "peer":
             from .peer import PeerExchange
-            slot = max(self.pack_len * 4, self.cand[0].numel() * 4, 64 * 4)
-            self.px = PeerExchange(slot, group)
+            # keys and candidates (a few KB): flag-in-packet transport; partial
+            # sets: the same up to 20 KB (measured cross-over), fenced bulk
+            # transport beyond; one region per payload family
+            self.px = PeerExchange(self.pack_len * 4, group,
+                                   packets=self.pack_len * 4 <= 20 * 1024)
+            self.px_small = PeerExchange(max(self.cand[0].numel() * 4, 64 * 4),
+                                         group, packets=True)
             # the keys padded to a multiple of 16 bytes
             n_hm = (st.hmax.numel() + 3) // 4 * 4
             self.hm_pad = torch.zeros(n_hm, device=dev, dtype=torch.int32)
@@ -156,10 +166,10 @@ class ContextParallelHotPath:
         if self.transport == "peer":
             n = hm.numel()
             if self.hm_pad.numel() == n:
-                self.px.all_max_u32(hm.view(-1), self.st.status)
+                self.px_small.all_max_u32(hm.view(-1), self.st.status)
             else:
                 self.hm_pad[:n].copy_(hm.view(-1))
-                self.px.all_max_u32(self.hm_pad, self.st.status)
+                self.px_small.all_max_u32(self.hm_pad, self.st.status)
                 hm.view(-1).copy_(self.hm_pad[:n])
             return
         hm.bitwise_xor_(_SIGN)
@@ -175,7 +185,7 @@ class ContextParallelHotPath:
                    int(self.sink_loc), int(self.nsh_loc), int(self.p0),
                    _cabi.stream())
         if self.transport == "peer":
-            self.px.all_gather(self.cand_mine, self.cand, self.st.status)
+            self.px_small.all_gather(self.cand_mine, self.cand, self.st.status)
         elif self.world > 1:
             dist.all_gather_into_tensor(self.cand.view(-1), mine.reshape(-1),
                                         group=self.group)

@@ -21,13 +21,18 @@ MAX_RANKS = 8
 
 
 class PeerExchange:
-    def __init__(self, slot_bytes: int, group=None):
+    def __init__(self, slot_bytes: int, group=None, packets: bool = False):
+        """``packets``: small-payload transport -- every 32-bit word travels as an
+        8-byte {word, epoch} packet and the receiver polls the packets themselves
+        (no fence, no separate flag; needs 2 x the payload per slot).  A region
+        uses one transport for its whole life."""
         assert dist.is_initialized(), "PeerExchange needs an initialised process group"
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         assert self.world <= MAX_RANKS, f"at most {MAX_RANKS} ranks"
-        self.slot_bytes = (int(slot_bytes) + 15) // 16 * 16
+        self.packets = bool(packets)
+        self.slot_bytes = (int(slot_bytes) * (2 if packets else 1) + 15) // 16 * 16
         nb = ctypes.c_int64()
         _cabi.call("locks_cp_region_bytes", self.slot_bytes, ctypes.byref(nb))
         nbytes = int(nb.value)
@@ -55,8 +60,10 @@ class PeerExchange:
              status: Optional[torch.Tensor]) -> None:
         nbytes = payload.numel() * payload.element_size()
         assert payload.is_contiguous() and out.is_contiguous()
-        assert nbytes % 16 == 0 and nbytes <= self.slot_bytes, \
+        need = nbytes * (2 if self.packets else 1)
+        assert nbytes % 16 == 0 and need <= self.slot_bytes, \
             f"payload of {nbytes} B does not fit the {self.slot_bytes} B slot"
+        mode += 2 if self.packets else 0
         _cabi.call("locks_cp_exchange", self._peers, int(self.world),
                    int(self.rank), _cabi.ptr(payload), int(nbytes),
                    int(self.slot_bytes), _cabi.ptr(out), int(mode),
