@@ -50,20 +50,33 @@ def workload(name: str, ctx: int | None):
         sh, c = synth.CONFIG1, 131072
     elif name in ("c4", "c4cp"):
         sh, c = synth.CONFIG4, 1048576
+    elif name == "c2":
+        # ragged continuous batch: 8 sequences, log-uniform in [4096, 262144]
+        sh = synth.CONFIG1
+        rng = np.random.default_rng(20260202)
+        c = [int(x) for x in np.exp(rng.uniform(np.log(4096), np.log(262144), 8))]
+        return sh, c
     else:
         raise SystemExit(f"unknown workload {name}")
     return sh, (ctx or c)
 
 
 def algo_bytes(sh, seq_len):
-    """Algorithmic bytes of one step: summaries scanned + selected K/V pages."""
-    npg = -(-seq_len // sh.page)
-    nsh = npg - sh.window_pages
-    A = min(sh.budget_pages, nsh - sh.sink_pages) + sh.sink_pages + sh.window_pages
-    score = sh.n_layers * sh.n_kv * nsh * REC_ALGO_BYTES
-    dec = sh.n_layers * sh.n_kv * A * PAGE_KV_BYTES
-    dense = sh.n_layers * sh.n_kv * npg * PAGE_KV_BYTES
-    return score, dec, dense, nsh, A
+    """Algorithmic bytes of one step: summaries scanned + selected K/V pages
+    (summed over the sequences of a ragged batch)."""
+    lens = seq_len if isinstance(seq_len, (list, tuple)) else [seq_len]
+    score = dec = dense = nsh_t = A_t = 0
+    for sl in lens:
+        npg = -(-sl // sh.page)
+        nsh = npg - sh.window_pages
+        A = min(sh.budget_pages, max(nsh - sh.sink_pages, 0)) + sh.sink_pages \
+            + sh.window_pages
+        score += sh.n_layers * sh.n_kv * nsh * REC_ALGO_BYTES
+        dec += sh.n_layers * sh.n_kv * A * PAGE_KV_BYTES
+        dense += sh.n_layers * sh.n_kv * npg * PAGE_KV_BYTES
+        nsh_t += nsh
+        A_t = max(A_t, A)
+    return score, dec, dense, nsh_t, A_t
 
 
 class ClockSampler:
@@ -198,35 +211,47 @@ def run_reference(args, sh, seq_len):
 # GPU arm                                                                      #
 # --------------------------------------------------------------------------- #
 def make_device_case(sh, seq_len, dev, seed, return_needles=False):
-    """Paged caches for ONE sequence of `seq_len` tokens, generated on the
-    device layer by layer (the full-size cache does not fit a CPU round trip)."""
+    """Paged caches for one sequence (or a ragged batch: a list of lengths),
+    generated on the device layer by layer (the full-size cache does not fit a
+    CPU round trip).  All sequences share one block pool; block ids are a seeded
+    permutation."""
     from locks import synth
     page = sh.page
-    npg = -(-seq_len // page)
-    NB = npg + 3
+    lens = list(seq_len) if isinstance(seq_len, (list, tuple)) else [seq_len]
+    npgs = [-(-sl // page) for sl in lens]
+    NB = sum(npgs) + 3
     g = torch.Generator().manual_seed(seed * 7 + 3)
     perm = torch.randperm(NB, generator=g)
-    bt = perm[:npg].to(torch.int32)[None].contiguous().to(dev)
+    bt_cpu = torch.zeros(len(lens), max(npgs), dtype=torch.int32)
+    o = 0
+    for r, n in enumerate(npgs):
+        bt_cpu[r, :n] = perm[o:o + n].to(torch.int32)
+        o += n
+    bt = bt_cpu.contiguous().to(dev)
     caches, qs, needles = [], [], []
-    blocks = bt[0].long()
-    pad = npg * page - seq_len
     for l in range(sh.n_layers):
-        K, V, q, nd = synth.gqa_tokens(seed, l, 0, seq_len, sh, dev)
-        needles.append(nd)
         kvc = torch.zeros(NB, 2, page, sh.n_kv, sh.d, device=dev,
                           dtype=torch.bfloat16)
-        if pad:
-            z = torch.zeros(pad, sh.n_kv, sh.d, device=dev, dtype=torch.bfloat16)
-            K, V = torch.cat([K, z]), torch.cat([V, z])
-        kvc[blocks, 0] = K.view(npg, page, sh.n_kv, sh.d)
-        kvc[blocks, 1] = V.view(npg, page, sh.n_kv, sh.d)
-        del K, V
+        ql, ndl = [], []
+        for r, sl in enumerate(lens):
+            K, V, q, nd = synth.gqa_tokens(seed, l, r, sl, sh, dev)
+            pad = npgs[r] * page - sl
+            if pad:
+                z = torch.zeros(pad, sh.n_kv, sh.d, device=dev, dtype=torch.bfloat16)
+                K, V = torch.cat([K, z]), torch.cat([V, z])
+            blocks = bt[r, :npgs[r]].long()
+            kvc[blocks, 0] = K.view(npgs[r], page, sh.n_kv, sh.d)
+            kvc[blocks, 1] = V.view(npgs[r], page, sh.n_kv, sh.d)
+            del K, V
+            ql.append(q)
+            ndl.append(nd)
+        needles.append(ndl[0] if len(lens) == 1 else ndl)
         caches.append(kvc)
-        qs.append(q[None])
-    sl = torch.tensor([seq_len], dtype=torch.int32, device=dev)
+        qs.append(torch.stack(ql))
+    sl_t = torch.tensor(lens, dtype=torch.int32, device=dev)
     if return_needles:
-        return caches, torch.stack(qs), bt, sl, needles
-    return caches, torch.stack(qs), bt, sl
+        return caches, torch.stack(qs), bt, sl_t, needles
+    return caches, torch.stack(qs), bt, sl_t
 
 
 def timed(fn, iters, stream=None):
@@ -416,7 +441,8 @@ def run_gpu(args, sh, seq_len):
     step_bytes = b_score + b_dec
 
     cpu = None
-    if not args.no_cpu_baseline and world == 1:
+    ragged = isinstance(seq_len, (list, tuple))
+    if not args.no_cpu_baseline and world == 1 and not ragged:
         try:
             cores = os.cpu_count() or 1
             arm = CpuArm(sh, seq_len)
@@ -438,12 +464,16 @@ def run_gpu(args, sh, seq_len):
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{args.workload_name}: {L} layers, "
                                f"{sh.n_kv * sh.G}q/{sh.n_kv}kv, d{sh.d}, page "
-                               f"{sh.page}, bs1 per GPU, ctx {seq_len - 1}, "
+                               f"{sh.page}, "
+                               + (f"ragged batch of {len(seq_len)} per GPU, ctx "
+                                  f"{min(seq_len) - 1}..{max(seq_len) - 1}, "
+                                  if isinstance(seq_len, (list, tuple)) else
+                                  f"bs1 per GPU, ctx {seq_len - 1}, ") +
                                f"budget {sh.budget_pages}+{sh.sink_pages} sink+"
                                f"{sh.window_pages} recent = {A} pages attended",
                    "l2_policy": "inputs larger than L2 "
                                 f"({step_bytes / 1e9:.2f} GB touched per step)",
-                   "sharding": "one sequence per GPU, no collective"},
+                   "sharding": "whole sequences per GPU, no collective"},
         "clocks": clocks,
         "e2e": {"value": world * R / (ms_e2e * 1e-3), "unit": "tokens/s",
                 "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
@@ -751,7 +781,7 @@ def main():
     if args.layers:
         import dataclasses
         sh = dataclasses.replace(sh, n_layers=args.layers)
-    seq_len = ctx + 1
+    seq_len = [c + 1 for c in ctx] if isinstance(ctx, list) else ctx + 1
     rank = int(os.environ.get("RANK", "0"))
     if args.impl == "reference":
         if rank != 0:

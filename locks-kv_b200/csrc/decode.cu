@@ -526,10 +526,11 @@ int check_geometry(const char* who, int G, int head_dim, int page) {
     return LOCKS_OK;
 }
 
-// cluster size of the fused decode: enough CTAs to cover the SMs about twice,
-// a power of two, at most 8 (the portable cluster limit)
+// cluster size of the fused decode: as many CTAs as fit in ONE wave (a CTA's
+// rings take more than half an SM's shared memory, so one CTA per SM), a power
+// of two, at most 8 (the portable cluster limit)
 int fused_cluster_size(int n_req, int n_kv) {
-    const int want = (2 * sm_count()) / max(1, n_req * n_kv);
+    const int want = sm_count() / max(1, n_req * n_kv);
     int cl = 1;
     while (cl * 2 <= want && cl < 8) cl *= 2;
     return cl;

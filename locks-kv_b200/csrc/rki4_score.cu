@@ -55,6 +55,7 @@ struct ScoreParams {
     float* score_h;
     uint32_t* hmax;
     int n_kv, G, max_pages, bt_width, num_blocks;
+    int n_req, ragged;
     float scale;
     int* status;
 };
@@ -167,9 +168,28 @@ rki4_score_kernel(const ScoreParams p) {
 
     SC_TS(0);
     TL_MARK(g_score_tl, 0);
-    const int z = blockIdx.x, Z = gridDim.x;
-    const int kh = blockIdx.y, r = blockIdx.z;
+    const int kh = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int z = blockIdx.x, Z = gridDim.x, r = blockIdx.z;
+    if (p.ragged) {
+        // Ragged batch: the gridDim.x CTAs of a kv-head are dealt to the requests
+        // in proportion to their chunk counts (every request gets one, the rest
+        // go by share), so a 4K-token row and a 70K-token row finish together.
+        const int R = p.n_req, Zt = (int)gridDim.x, cap0 = min(p.max_pages, p.bt_width);
+        int total = 0;
+        for (int i = 0; i < R; ++i)
+            total += (min(max(p.n_sel_hi[i], 0), cap0) + CHUNK - 1) / CHUNK;
+        const int extra = Zt - R, b = (int)blockIdx.x;
+        int acc = 0;
+        r = -1;
+        for (int i = 0; i < R; ++i) {
+            const int ci = (min(max(p.n_sel_hi[i], 0), cap0) + CHUNK - 1) / CHUNK;
+            const int Zi = 1 + (int)(((int64_t)extra * ci) / max(total, 1));
+            if (b < acc + Zi) { r = i; z = b - acc; Z = Zi; break; }
+            acc += Zi;
+        }
+        if (r < 0) return;                       // CTAs left over by the rounding
+    }
     const int gid = lane >> 2, tig = lane & 3;
     const int G = p.G;
 
@@ -529,6 +549,10 @@ extern "C" int locks_rki4_score_bt(
         Z = (CTAS_PER_SM * sm_count() + base - 1) / base;
     }
     Z = max(1, min(Z, min(max_z, 65535)));
+    // several requests (of possibly very different lengths) and room for at least
+    // two CTAs each: share the CTAs of a kv-head by length
+    const int Zt = (CTAS_PER_SM * sm_count()) / max(1, n_kv);
+    const bool ragged = zsplit <= 0 && n_req > 1 && n_req <= 64 && 2 * n_req <= Zt;
 
     ScoreParams p;
     p.q = static_cast<const __nv_bfloat16*>(q);
@@ -541,8 +565,9 @@ extern "C" int locks_rki4_score_bt(
     p.hmax = hmax;
     p.n_kv = n_kv; p.G = G; p.max_pages = max_pages; p.bt_width = bt_width;
     p.num_blocks = num_blocks; p.scale = scale; p.status = status;
+    p.n_req = n_req; p.ragged = ragged ? 1 : 0;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(Z, n_kv, n_req);
+    cfg.gridDim = ragged ? dim3(Zt, n_kv, 1) : dim3(Z, n_kv, n_req);
     cfg.blockDim = dim3(NTHREADS, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = static_cast<cudaStream_t>(stream);

@@ -697,7 +697,7 @@ extern "C" int locks_topb_select(
         const int useful = (max_pages + 2047) / 2048;
         while (cl * 2 <= want && cl * 2 <= useful && cl < 4) cl *= 2;
     } else {
-        while (cl < 8 && (max_pages + cl - 1) / cl > KEYS_PER_CTA) cl *= 2;
+        while (cl < MAX_CL && (max_pages + cl - 1) / cl > KEYS_PER_CTA) cl *= 2;
         // more CTAs share the combine when SMs are free
         const int want = sm_count() / max(1, n_kv * n_req);
         while (cl * 2 <= 8 && cl * 2 <= want && max_pages / (cl * 2) >= 4096)
@@ -710,7 +710,7 @@ extern "C" int locks_topb_select(
     LOCKS_REQUIRE(owner_mode || (max_pages + cl - 1) / cl <= KEYS_PER_CTA,
                   LOCKS_ERR_SIZE,
                   "locks_topb_select: max_pages %d beyond the supported %d",
-                  max_pages, 8 * KEYS_PER_CTA);
+                  max_pages, MAX_CL * KEYS_PER_CTA);
     p.owner_mode = owner_mode ? 1 : 0;
     // key slots per CTA (the compaction reads whole 128-key rows), followed by
     // the interleaved histogram copies

@@ -363,7 +363,8 @@ def test_topb_long_context(MP, combine):
 
 
 @pytest.mark.parametrize("MP,kind", [(40000, "equal"), (131072, "coarse"),
-                                     (16385, "equal"), (65536, "fine")])
+                                     (16385, "equal"), (65536, "fine"),
+                                     (200000, "coarse")])
 def test_topb_sliced_rows_ties_and_fraction_budget(MP, kind):
     """Rows kept as per-CTA slices: a 10 % budget (thousands of pages), all-equal
     scores (every page ties: the lowest pages win, across slice borders) and
