@@ -24,7 +24,10 @@ import sys
 os.environ.setdefault("TRITON_INTERPRET", "1")
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("LOCKS_REFERENCE_SRC", "/root/reference/src")
+REF = os.environ.get("LOCKS_REFERENCE_SRC")
+if not REF:
+    raise SystemExit("set LOCKS_REFERENCE_SRC to the reference checkout's src/ "
+                     "directory (the package `locks` v0.1.3 is imported from it)")
 sys.path.insert(0, REF)
 
 import numpy as np  # noqa: E402
