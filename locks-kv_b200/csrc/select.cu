@@ -304,7 +304,9 @@ __device__ __forceinline__ void sweep_max_groups(
 // NT threads per CTA.  OWNER: CTA 0 selects the whole row, the other CTAs of the
 // cluster only combine (or there is no cluster); otherwise every CTA of the
 // cluster keeps and selects the keys of its page slice.
-template <int NT, bool OWNER>
+// GT: the GQA group size rounded up to a power of two (a kernel per value keeps
+// the once-through instruction stream short).
+template <int NT, bool OWNER, int GT>
 __global__ void __launch_bounds__(NT)
 topb_kernel(const SelParams p) {
     constexpr int NW = NT / 32;
@@ -384,8 +386,8 @@ topb_kernel(const SelParams p) {
         if (published) {
             if (tid < G) sm.hm_sh[tid] = key2f(p.hmax[row * G + tid]);
         } else {
-            LOCKS_DISPATCH_GT(G, (sweep_max_groups<GT>(
-                sh, sm.wmax[warp], G, MP, cs0, cn_loc, n_comb, cg_beg, cg_end, lane)));
+            sweep_max_groups<GT>(sh, sm.wmax[warp], G, MP, cs0, cn_loc, n_comb, cg_beg,
+                                 cg_end, lane);
             __syncthreads();
             if (tid < G) {
                 float m = -INFINITY;
@@ -409,9 +411,9 @@ topb_kernel(const SelParams p) {
         // the barrier below publishes hm_sh; the scorer's keys are re-armed
         // further down, behind a cluster barrier every CTA passes after this read
         auto sync_hm = [&]() { __syncthreads(); };
-        LOCKS_DISPATCH_GT(G, LOCKS_DISPATCH_CB(cgpw, (combine_nrm_groups<GT, CBW>(
+        LOCKS_DISPATCH_CB(cgpw, (combine_nrm_groups<GT, CBW>(
             sh, score, kdst, sm.hm_sh, G, MP, cs0, cn_loc, n_comb, cg_beg, cg_end,
-            lane, sync_hm, fin_key))));
+            lane, sync_hm, fin_key)));
         SEL_TS(21);
     } else if (p.combine == LOCKS_COMBINE_MAX && n_comb > 0) {
         const float* sh = p.score_h + row * (int64_t)G * MP;
@@ -719,18 +721,21 @@ extern "C" int locks_topb_select(
     const int per_cta = ((slice + 127) & ~127) + 128;
     p.key_cap = per_cta;
     const int dyn_smem = (per_cta + HSLOTS * HCOPIES) * 4;
+    const int smem_max = (KEYS_PER_CTA + 512 + HSLOTS * HCOPIES) * 4;
     static bool attr_done[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        cudaFuncSetAttribute(topb_kernel<SEL_THREADS, true>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (KEYS_PER_CTA + 512 + HSLOTS * HCOPIES) * 4);
-        cudaFuncSetAttribute(topb_kernel<SEL_THREADS, false>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (KEYS_PER_CTA + 512 + HSLOTS * HCOPIES) * 4);
-        cudaFuncSetAttribute(topb_kernel<SEL_THREADS, false>,
+#define LOCKS_SEL_ATTR(GTV)                                                        \
+        cudaFuncSetAttribute(topb_kernel<SEL_THREADS, true, GTV>,                  \
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);\
+        cudaFuncSetAttribute(topb_kernel<SEL_THREADS, false, GTV>,                 \
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);\
+        cudaFuncSetAttribute(topb_kernel<SEL_THREADS, false, GTV>,                 \
                              cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        LOCKS_SEL_ATTR(1) LOCKS_SEL_ATTR(2) LOCKS_SEL_ATTR(4) LOCKS_SEL_ATTR(8)
+        LOCKS_SEL_ATTR(16)
+#undef LOCKS_SEL_ATTR
         attr_done[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
@@ -747,9 +752,10 @@ extern "C" int locks_topb_select(
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
-    cudaError_t e = owner_mode
-        ? cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, true>, p)
-        : cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, false>, p);
+    cudaError_t e = cudaSuccess;
+    LOCKS_DISPATCH_GT(G, (e = owner_mode
+        ? cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, true, GT>, p)
+        : cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, false, GT>, p)));
     if (e != cudaSuccess)
         return fail(LOCKS_ERR_LAUNCH, "locks_topb_select: %s",
                     cudaGetErrorString(e));

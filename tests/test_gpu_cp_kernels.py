@@ -115,3 +115,42 @@ def test_merge_gathered_equals_merge_of_all_partials():
     want = (w[..., None] * aa).sum(2) / (w * ll).sum(-1, keepdim=True)
     np.testing.assert_allclose(out[0].float().cpu().numpy().reshape(n_kv, G, d),
                                want.float().numpy(), atol=2e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("mode", [0, 2])
+def test_exchange_wait_runs_out_and_reports(mode):
+    """A peer that never shows up: the exchange kernel gives up after its time
+    limit, raises the status word and returns -- nothing hangs and the context
+    stays usable.  (Rank 1 is a second region on the same GPU that no kernel
+    ever writes flags into.)"""
+    import ctypes
+    from locks import _cabi
+    slot = 4096
+    nb = ctypes.c_int64()
+    _cabi.call("locks_cp_region_bytes", slot, ctypes.byref(nb))
+    r0, r1 = ctypes.c_void_p(), ctypes.c_void_p()
+    _cabi.call("locks_cp_alloc", int(nb.value), ctypes.byref(r0))
+    _cabi.call("locks_cp_alloc", int(nb.value), ctypes.byref(r1))
+    peers = (ctypes.c_void_p * 8)()
+    peers[0], peers[1] = r0.value, r1.value
+    payload = torch.arange(64, device=DEV, dtype=torch.int32)
+    out = torch.zeros(2, 64, device=DEV, dtype=torch.int32)
+    status = torch.zeros(1, device=DEV, dtype=torch.int32)
+    try:
+        _cabi.call("locks_cp_exchange", peers, 2, 0, _cabi.ptr(payload), 256, slot,
+                   _cabi.ptr(out), mode, _cabi.ptr(status), _cabi.stream())
+        torch.cuda.synchronize()                     # returns after ~2 s
+        assert int(status.item()) == 1               # LOCKS_ST_WAIT_TIMEOUT
+        # the context is alive: a normal single-rank exchange works afterwards
+        status.zero_()
+        peers1 = (ctypes.c_void_p * 8)()
+        peers1[0] = r0.value
+        out1 = torch.zeros(1, 64, device=DEV, dtype=torch.int32)
+        _cabi.call("locks_cp_exchange", peers1, 1, 0, _cabi.ptr(payload), 256, slot,
+                   _cabi.ptr(out1), mode, _cabi.ptr(status), _cabi.stream())
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        assert torch.equal(out1[0], payload)
+    finally:
+        _cabi.call("locks_cp_free", r0)
+        _cabi.call("locks_cp_free", r1)
