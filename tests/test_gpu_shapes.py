@@ -197,3 +197,44 @@ def test_decode_reads_v_from_pinned_host_memory():
                                 case.seq_lens, hp.st, out2, host_v, scale=hp.scale)
     torch.cuda.synchronize()
     assert (out2[:2].float() - ref[:2].float()).abs().max().item() <= 2e-2
+
+
+def test_ragged_batch_scores_equal_single_request_scores():
+    """The scorer deals the CTAs of a kv-head to the requests of a batch by
+    length; whatever the split, a request's scores must be bit-identical to the
+    ones it gets when it is scored alone."""
+    from locks import synth
+    from locks.selection import Rki4State, derive_page_params, rki4_build_bulk, \
+        rki4_score_only
+    sh = synth.GqaShape(n_layers=1, n_kv=8, G=4, d=128, page=16, budget_pages=32,
+                        sink_pages=1, window_pages=4, n_needles=0, n_outlier=4)
+    lens = [40, 5000, 300, 70001, 129, 16 * 700]
+    case = synth.make_gqa_case(9, sh, lens, device=DEV)
+    R, MP, NB = len(lens), int(case.block_table.shape[1]), int(case.kv_caches[0].shape[0])
+
+    def state(n):
+        st = Rki4State(DEV, num_layers=1, num_blocks=NB, n_kv=8, G=4, head_dim=128,
+                       page=16, max_reqs=n, max_pages=MP, budget_pages=32,
+                       sink_pages=1, window_pages=4)
+        st.scale = case.scale
+        return st
+    st = state(R)
+    K = [case.kv_caches[0][:, 0]]
+    rki4_build_bulk(st, K, case.block_table, case.seq_lens - 1, R, MP)
+    derive_page_params(st, case.seq_lens, R)
+    rki4_score_only(st, 0, case.q[0], case.block_table, case.seq_lens, R, case.scale)
+    torch.cuda.synchronize()
+    batch = st.score_h.clone()
+    nsh = t2n(st.n_sel_hi)
+    for r in range(R):
+        one = state(1)
+        one.pp_rec.copy_(st.pp_rec)
+        sl = case.seq_lens[r:r + 1].contiguous()
+        bt = case.block_table[r:r + 1].contiguous()
+        derive_page_params(one, sl, 1)
+        rki4_score_only(one, 0, case.q[0, r:r + 1].contiguous(), bt, sl, 1, case.scale)
+        torch.cuda.synchronize()
+        n = max(int(nsh[r]), 0)
+        assert torch.equal(one.score_h[0, :, :, :n], batch[r, :, :, :n]), r
+        # the published per-head maxima agree as well
+        assert torch.equal(one.hmax[0], st.hmax[r]), r
