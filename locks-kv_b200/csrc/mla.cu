@@ -240,9 +240,13 @@ mla_score_kernel(const MlaScoreParams p) {
     const int n_pg = min(max(p.n_pages[row], 0), p.max_pages);
     const int n_c = min(max(p.n_cache[row], 0), n_pg);
     float* score = p.score + (int64_t)row * p.max_pages;
-    if (z == 0)                       // pages without factors score -inf
-        for (int i = n_c + tid; i < n_pg; i += SC_WARPS * 32) score[i] = -INFINITY;
-    if (n_c <= 0) return;
+    pdl_trigger();                    // the selector may be scheduled; it waits for us
+    if (n_c <= 0) {
+        pdl_wait();                   // the score row belongs to the kernels before
+        if (z == 0)                   // pages without factors score -inf
+            for (int i = tid; i < n_pg; i += SC_WARPS * 32) score[i] = -INFINITY;
+        return;
+    }
     const int cg0 = (int)(((int64_t)n_c * z) / Z);
     const int cg1 = (int)(((int64_t)n_c * (z + 1)) / Z);
     if (cg1 <= cg0) return;
@@ -280,19 +284,42 @@ mla_score_kernel(const MlaScoreParams p) {
     };
     for (int k = 0; k < SC_STAGES && k < np; ++k) issue(k);
 
-    // ---- stage q: q_c as fp16, q_rope as bf16 --------------------------------
+    // Everything above reads per-step constants (page counts, block table, factor
+    // records, rope keys); q and the score row belong to the kernels before.
+    pdl_wait();
+    if (z == 0)                       // pages without factors score -inf
+        for (int i = n_c + tid; i < n_pg; i += SC_WARPS * 32) score[i] = -INFINITY;
+
+    // ---- stage q: q_c as fp16, q_rope as bf16; 16-byte loads, all in flight ----
     {
-        const __nv_bfloat16* q = p.q + (int64_t)row * p.q_stride_row;
-        for (int e = tid; e < NH * (LKV / 2); e += SC_WARPS * 32) {
-            const int h = e / (LKV / 2), d2 = e % (LKV / 2);
-            const float2 v = __bfloat1622float2(
-                *reinterpret_cast<const __nv_bfloat162*>(q + h * WIDTH + 2 * d2));
-            *reinterpret_cast<__half2*>(&sm.qc[h][4 * d2]) = __floats2half2_rn(v.x, v.y);
+        const uint4* q4 = reinterpret_cast<const uint4*>(p.q + (int64_t)row * p.q_stride_row);
+        constexpr int C16 = WIDTH * 2 / 16;               // 72 chunks of 8 bf16 per head
+        constexpr int NQ = (NH * C16 + SC_WARPS * 32 - 1) / (SC_WARPS * 32);
+        uint4 v[NQ];
+#pragma unroll
+        for (int i = 0; i < NQ; ++i) {
+            const int e = tid + i * SC_WARPS * 32;
+            v[i] = (e < NH * C16) ? q4[e] : make_uint4(0, 0, 0, 0);
         }
-        for (int e = tid; e < NH * (ROPE / 2); e += SC_WARPS * 32) {
-            const int h = e / (ROPE / 2), d2 = e % (ROPE / 2);
-            *reinterpret_cast<uint32_t*>(&sm.qr[h][4 * d2]) =
-                *reinterpret_cast<const uint32_t*>(q + h * WIDTH + LKV + 2 * d2);
+#pragma unroll
+        for (int i = 0; i < NQ; ++i) {
+            const int e = tid + i * SC_WARPS * 32;
+            if (e >= NH * C16) continue;
+            const int h = e / C16, c = e % C16;
+            if (c < LKV * 2 / 16) {                        // latent part -> fp16
+                const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+                uint32_t o[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const __half2 hh = __floats2half2_rn(
+                        __uint_as_float(w[j] << 16), __uint_as_float(w[j] & 0xFFFF0000u));
+                    o[j] = *reinterpret_cast<const uint32_t*>(&hh);
+                }
+                *reinterpret_cast<uint4*>(&sm.qc[h][16 * c]) =
+                    make_uint4(o[0], o[1], o[2], o[3]);
+            } else {                                       // rope part stays bf16
+                *reinterpret_cast<uint4*>(&sm.qr[h][16 * (c - LKV * 2 / 16)]) = v[i];
+            }
         }
     }
     __syncthreads();
@@ -423,18 +450,19 @@ __global__ void __launch_bounds__(MD_THREADS) mla_decode_kernel(const MlaDecPara
     const int gid = lane >> 2, tig = lane & 3;
 
     MLA_TS(0);
+    if (tid == 0) {
+        for (int s = 0; s < MD_STAGES; ++s) mbar_init(&sm.full[s], 1);
+        mbar_fence_init();
+    }
+    pdl_trigger();                     // the next layer's scorer may start prefetching
+    // remote shared memory may be written once every CTA of the cluster runs
+    cluster.sync();
+    pdl_wait();                        // the page table comes from the selector
     const int seq_len = p.seq_lens[row];
     const int cnt = min(max(p.page_cnt[row], 0), p.max_pages);
     const int per = (cnt + CL - 1) / CL;
     const int j0 = min(c * per, cnt), j1 = min(j0 + per, cnt);
     const int np = j1 - j0;
-
-    if (tid == 0) {
-        for (int s = 0; s < MD_STAGES; ++s) mbar_init(&sm.full[s], 1);
-        mbar_fence_init();
-    }
-    // remote shared memory may be written once every CTA of the cluster runs
-    cluster.sync();
 
     const int32_t* tab = p.page_table + (int64_t)row * p.max_pages;
     const int32_t* bt = p.block_table + (int64_t)row * p.bt_stride;
@@ -735,6 +763,7 @@ extern "C" int locks_mla_build_factors(const void* cache, int64_t stride_block,
     p.blocks = blocks; p.n_blocks = n_blocks; p.num_blocks = num_blocks;
     mla_factor_kernel<<<(n_blocks + FB_WARPS - 1) / FB_WARPS, FB_WARPS * 32, smem,
                         static_cast<cudaStream_t>(stream)>>>(p);
+    pdl_break();                       // the scorer prefetches factor records before its wait
     return check_launch("locks_mla_build_factors");
 }
 
@@ -753,6 +782,7 @@ extern "C" int locks_mla_derive(const int32_t* seq_lens, int n_rows,
                         static_cast<cudaStream_t>(stream)>>>(
         seq_lens, n_rows, budget_pages, sink_pages, window_pages, n_pages,
         n_sel_hi, b_fix);
+    pdl_break();                       // the scorer reads the page counts before its wait
     return check_launch("locks_mla_derive");
 }
 
@@ -771,10 +801,10 @@ extern "C" int locks_mla_score(const void* q, int64_t q_stride_row,
                       num_blocks >= 1 && scale > 0.f,
                   LOCKS_ERR_ARG, "locks_mla_score: bad size argument");
     LOCKS_REQUIRE(stride_block % 8 == 0 && stride_tok % 8 == 0 &&
-                      q_stride_row % 2 == 0 &&
+                      q_stride_row % 8 == 0 &&
                       (reinterpret_cast<uintptr_t>(cache) & 15) == 0 &&
                       (reinterpret_cast<uintptr_t>(records) & 15) == 0 &&
-                      (reinterpret_cast<uintptr_t>(q) & 3) == 0,
+                      (reinterpret_cast<uintptr_t>(q) & 15) == 0,
                   LOCKS_ERR_ARG, "locks_mla_score: misaligned argument");
     if (n_rows == 0) return LOCKS_OK;
     const int smem = (int)sizeof(ScSmem);
@@ -798,8 +828,19 @@ extern "C" int locks_mla_score(const void* q, int64_t q_stride_row,
     p.n_cache = n_cache; p.n_pages = n_pages; p.score = score;
     p.max_pages = max_pages; p.num_blocks = num_blocks; p.scale = scale;
     p.status = status;
-    mla_score_kernel<<<dim3(Z, n_rows), SC_WARPS * 32, smem,
-                       static_cast<cudaStream_t>(stream)>>>(p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(Z, n_rows, 1);
+    cfg.blockDim = dim3(SC_WARPS * 32, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (pdl_enabled() && !pdl_take_break()) ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, mla_score_kernel, p);
+    if (e != cudaSuccess)
+        return fail(LOCKS_ERR_LAUNCH, "locks_mla_score: %s", cudaGetErrorString(e));
     return check_launch("locks_mla_score");
 }
 
@@ -852,13 +893,15 @@ extern "C" int locks_mla_decode(const void* q, int64_t q_stride_row,
     cfg.blockDim = dim3(MD_THREADS, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = static_cast<cudaStream_t>(stream);
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = cl;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, mla_decode_kernel, p);
     if (e != cudaSuccess)
         return fail(LOCKS_ERR_LAUNCH, "locks_mla_decode: %s", cudaGetErrorString(e));
