@@ -210,7 +210,7 @@ def run_reference(args, sh, seq_len):
 # --------------------------------------------------------------------------- #
 # GPU arm                                                                      #
 # --------------------------------------------------------------------------- #
-def make_device_case(sh, seq_len, dev, seed, return_needles=False):
+def make_device_case(sh, seq_len, dev, seed, return_needles=False, extra_pages=4):
     """Paged caches for one sequence (or a ragged batch: a list of lengths),
     generated on the device layer by layer (the full-size cache does not fit a
     CPU round trip).  All sequences share one block pool; block ids are a seeded
@@ -219,14 +219,16 @@ def make_device_case(sh, seq_len, dev, seed, return_needles=False):
     page = sh.page
     lens = list(seq_len) if isinstance(seq_len, (list, tuple)) else [seq_len]
     npgs = [-(-sl // page) for sl in lens]
-    NB = sum(npgs) + 3
+    # every sequence also owns `extra_pages` blocks for the tokens it will
+    # decode (the block-table entries after its last page)
+    NB = sum(npgs) + extra_pages * len(lens) + 3
     g = torch.Generator().manual_seed(seed * 7 + 3)
     perm = torch.randperm(NB, generator=g)
-    bt_cpu = torch.zeros(len(lens), max(npgs), dtype=torch.int32)
+    bt_cpu = torch.zeros(len(lens), max(npgs) + extra_pages, dtype=torch.int32)
     o = 0
     for r, n in enumerate(npgs):
-        bt_cpu[r, :n] = perm[o:o + n].to(torch.int32)
-        o += n
+        bt_cpu[r, :n + extra_pages] = perm[o:o + n + extra_pages].to(torch.int32)
+        o += n + extra_pages
     bt = bt_cpu.contiguous().to(dev)
     caches, qs, needles = [], [], []
     for l in range(sh.n_layers):
@@ -381,6 +383,44 @@ def run_gpu(args, sh, seq_len):
     from locks.selection import rki4_build_slots
     ms_slots = timed(lambda: rki4_build_slots(st, hp.K_layers, slot_end), 10)
 
+    # ---- decode loop: the step as a model runs it -- the new token's K/V are
+    # rotated and written, page parameters follow the grown lengths, and the
+    # summaries of pages completed by the PREVIOUS step are built on a forked
+    # branch while this step's layers run (the page stays inside the recent
+    # window for many steps, so nothing waits for its summary) -----------------
+    loop = None
+    try:
+        KS = 48                                     # 3 page completions per sequence
+        lens0 = hp.seq_lens.clone()
+        P = int(lens0.max().item()) + KS + 2
+        ang = torch.arange(P, device=dev, dtype=torch.float32)[:, None] * \
+            (500000.0 ** (-torch.arange(sh.d // 2, device=dev) / (sh.d // 2)))[None]
+        hp.enable_append(torch.cat([ang.cos(), ang.sin()], 1).to(torch.bfloat16))
+        hp.new_k.copy_(torch.randn(L, R, sh.n_kv, sh.d, device=dev))
+        hp.new_v.copy_(torch.randn(L, R, sh.n_kv, sh.d, device=dev))
+        for _ in range(4):                           # capture + 3 warm replays
+            hp.append_step()
+        ms_loop = timed(hp.append_step, KS - 4)
+        torch.cuda.synchronize()
+        st.check_status()
+        # the pages completed on the way have summaries in every layer
+        done = []
+        for r in range(R):
+            a, b = int(lens0[r].item()) // sh.page, int(hp.seq_lens[r].item() - 1) // sh.page
+            done += [int(hp.block_table[r, pg].item()) for pg in range(a, b)]
+        built = all(not bool(torch.isnan(st.pp_tag[:, blk].float()).any())
+                    for blk in done)
+        loop = {"ms_per_step": ms_loop, "steps": KS, "pages_completed": len(done),
+                "summaries_of_completed_pages_built": built,
+                "note": "graph of: slot/position update, derive, per layer KV write "
+                        "+ score + select + decode, slot-driven summary build of the "
+                        "previous step's completed pages on a forked branch"}
+        hp.flush_builds()
+        hp.seq_lens.copy_(lens0)
+        hp.derive()
+    except Exception as e:       # an optional measurement must not sink the bench line
+        loop = {"failed": f"{type(e).__name__}: {e}"}
+
     # ---- dense full-KV baseline on the same caches ----------------------------
     dsplit = max(1, min(512, (4 * 148) // (sh.n_kv * R)))
     dbuf = DenseDecodeBuffers(dev, R, sh.n_kv, sh.G, sh.d, dsplit)
@@ -509,6 +549,7 @@ def run_gpu(args, sh, seq_len):
                      "note": "rotate K + store K,V (+ summary build of the "
                              "completed page in the same launch); or one "
                              "slot-driven build launch per step for all layers"},
+        "decode_loop": loop,
         "cpu_baseline": cpu,
     }
     if world > 1:

@@ -19,7 +19,7 @@ from .attention import ResidentVSource, ensure_stage_b_buffers
 from .backend import _runtime
 from .config import LocksConfig
 from .selection import (Rki4State, derive_page_params, rki4_build_bulk,
-                        rki4_build_tail)
+                        rki4_build_slots, rki4_build_tail)
 
 
 class HotPath:
@@ -110,3 +110,84 @@ class HotPath:
             self.capture()
         self.graph.replay()
         return self.out
+
+    # ---- decode loop: append one token per request, then attend --------------
+    def enable_append(self, cos_sin: Optional[torch.Tensor] = None,
+                      neox: bool = True) -> None:
+        """Allocate what ``append_step`` needs: the new token's K/V per layer
+        (``new_k`` / ``new_v``, (L, R, n_kv, d) bf16, filled by the caller
+        before each step), the slot and position vectors it derives on the
+        device, and the side stream of the summary build.  ``cos_sin`` is the
+        (positions, rot_dim) cos|sin table of the rotation, or None for K that
+        arrives rotated.  The block table must hold a block for every page the
+        appended tokens reach."""
+        from .attention import rope_and_cache
+        dev, R, L = self.device, self.n_req, len(self.kv_caches)
+        self._rope_and_cache = rope_and_cache
+        self.cos_sin, self.neox = cos_sin, neox
+        self.new_k = torch.zeros(L, R, self.n_kv, self.d, device=dev,
+                                 dtype=torch.bfloat16)
+        self.new_v = torch.zeros_like(self.new_k)
+        self.pos = torch.zeros(R, dtype=torch.int64, device=dev)
+        self.slot = torch.full((R,), -1, dtype=torch.int64, device=dev)
+        self.slot_prev = torch.full((R,), -1, dtype=torch.int64, device=dev)
+        self._side = torch.cuda.Stream(device=dev)
+        self.append_graph: Optional[torch.cuda.CUDAGraph] = None
+
+    def _append_step(self) -> None:
+        """One decode step as a model runs it, every decision on the device:
+        the token index is the current length; its slot comes from the block
+        table; lengths grow by one and the page parameters follow; each layer
+        rotates and stores the token, scores, selects and decodes.  Summaries
+        of the pages the PREVIOUS step completed are built on a forked branch
+        meanwhile -- such a page stays inside the recent window for
+        ``window_pages`` more pages, so no step scores it before the join at
+        the end of this one."""
+        cur = torch.cuda.current_stream()
+        self._side.wait_stream(cur)
+        with torch.cuda.stream(self._side):
+            rki4_build_slots(self.st, self.K_layers, self.slot_prev)
+        self.pos.copy_(self.seq_lens)
+        blk = self.block_table.gather(1, (self.pos // self.page)[:, None])
+        self.slot.copy_(blk.squeeze(1).to(torch.int64) * self.page
+                        + self.pos % self.page)
+        self.seq_lens.add_(1)
+        self.derive()
+        st, R = self.st, self.n_req
+        for l, kvc in enumerate(self.kv_caches):
+            self._rope_and_cache(self.new_k[l], self.new_v[l], kvc, self.slot,
+                                 self.pos if self.cos_sin is not None else None,
+                                 self.cos_sin, neox=self.neox)
+            q = self.q[l, :R]
+            _runtime._rki4_select_adapter(q, kvc, self.block_table,
+                                          self.seq_lens, st, R, self.scale,
+                                          self.cfg)
+            _runtime.decode_dispatch(q, kvc, self.block_table, self.seq_lens, st,
+                                     self.out[l], self.vsources[l], self.scale,
+                                     self.cfg)
+        cur.wait_stream(self._side)
+        self.slot_prev.copy_(self.slot)
+
+    def append_step(self) -> torch.Tensor:
+        """Replay the captured append-and-attend step (captured on first use;
+        the capture's warm-up run is itself one real step)."""
+        if self.append_graph is None:
+            s = torch.cuda.Stream(device=self.device)
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._append_step()
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._append_step()
+            self.append_graph = g
+            return self.out
+        self.append_graph.replay()
+        return self.out
+
+    def flush_builds(self) -> None:
+        """Build the summaries of pages completed by the last appended token
+        (``append_step`` leaves them to the following step)."""
+        rki4_build_slots(self.st, self.K_layers, self.slot_prev)
+        self.slot_prev.fill_(-1)
