@@ -395,14 +395,23 @@ def run_gpu(args, sh, seq_len):
         P = int(lens0.max().item()) + KS + 2
         ang = torch.arange(P, device=dev, dtype=torch.float32)[:, None] * \
             (500000.0 ** (-torch.arange(sh.d // 2, device=dev) / (sh.d // 2)))[None]
-        hp.enable_append(torch.cat([ang.cos(), ang.sin()], 1).to(torch.bfloat16))
-        hp.new_k.copy_(torch.randn(L, R, sh.n_kv, sh.d, device=dev))
-        hp.new_v.copy_(torch.randn(L, R, sh.n_kv, sh.d, device=dev))
-        for _ in range(4):                           # capture + 3 warm replays
-            hp.append_step()
-        ms_loop = timed(hp.append_step, KS - 4)
-        torch.cuda.synchronize()
-        st.check_status()
+        cs_tab = torch.cat([ang.cos(), ang.sin()], 1).to(torch.bfloat16)
+
+        def run_loop(fuse_write):
+            hp.seq_lens.copy_(lens0)
+            hp.enable_append(cs_tab, fuse_write=fuse_write)
+            hp.new_k.copy_(torch.randn(L, R, sh.n_kv, sh.d, device=dev))
+            hp.new_v.copy_(torch.randn(L, R, sh.n_kv, sh.d, device=dev))
+            for _ in range(4):                       # capture + 3 warm replays
+                hp.append_step()
+            ms = timed(hp.append_step, KS - 4)
+            torch.cuda.synchronize()
+            st.check_status()
+            return ms
+
+        ms_sep = run_loop(False)
+        hp.flush_builds()
+        ms_loop = run_loop(True)
         # the pages completed on the way have summaries in every layer
         done = []
         for r in range(R):
@@ -410,11 +419,13 @@ def run_gpu(args, sh, seq_len):
             done += [int(hp.block_table[r, pg].item()) for pg in range(a, b)]
         built = all(not bool(torch.isnan(st.pp_tag[:, blk].float()).any())
                     for blk in done)
-        loop = {"ms_per_step": ms_loop, "steps": KS, "pages_completed": len(done),
+        loop = {"ms_per_step": ms_loop, "ms_per_step_separate_kv_write": ms_sep,
+                "steps": KS, "pages_completed": len(done),
                 "summaries_of_completed_pages_built": built,
-                "note": "graph of: slot/position update, derive, per layer KV write "
-                        "+ score + select + decode, slot-driven summary build of the "
-                        "previous step's completed pages on a forked branch"}
+                "note": "graph of: slot/position update, derive, per layer score + "
+                        "select (its launch also rotates and stores the new token's "
+                        "K/V) + decode, slot-driven summary build of the previous "
+                        "step's completed pages on a forked branch"}
         hp.flush_builds()
         hp.seq_lens.copy_(lens0)
         hp.derive()

@@ -240,6 +240,37 @@ int locks_kv_write(const void* key, int64_t k_row_stride, int64_t k_head_stride,
                    int n_kv, int head_dim, int page, int num_blocks,
                    locks_stream_t stream);
 
+/* ---- Selection that also carries the layer's KV write -------------------------
+ * The store of locks_kv_write (same arguments, same arithmetic, no summary
+ * build), one token per request row: row r of key / val goes to slot_mapping[r].
+ * It rides in the selector's grid -- in a helper CTA of the row's cluster that
+ * has nothing left to do while CTA 0 selects -- so the step has no separate
+ * KV-write launch; the sparse decode that follows on the stream reads the new
+ * token from the cache as usual.  The reference hides the same write behind its
+ * select launch (backend/_runtime.py fixc_flush, tier/k5_cuda.py:660-687). */
+typedef struct locks_kv_append {
+    const void* key;                 /* bf16 (n_req, n_kv, head_dim) */
+    int64_t k_row_stride, k_head_stride;
+    const void* val;
+    int64_t v_row_stride, v_head_stride;
+    void* k_cache;
+    void* v_cache;
+    int64_t kv_stride_block, kv_stride_tok, kv_stride_head;
+    const int64_t* slot_mapping;     /* (n_req,), < 0 skips the row */
+    const int64_t* positions;        /* (n_req,), needed with cos_sin */
+    const void* cos_sin;             /* optional bf16 (P, rot_dim) */
+    int64_t cos_sin_row_stride;
+    int32_t rot_dim, neox, head_dim, page, num_blocks;
+} locks_kv_append_t;
+
+int locks_topb_select_append(int combine, const float* score_h, float* score,
+                             uint32_t* hmax, const int32_t* n_pages,
+                             const int32_t* n_sel_hi, const int32_t* b_fix,
+                             int32_t* page_table, int32_t* page_cnt, int n_req,
+                             int n_kv, int G, int max_pages, int sink_pages,
+                             const locks_kv_append_t* append,
+                             locks_stream_t stream);
+
 /* ---- Context parallel (one sequence over several GPUs) -------------------------
  * No counterpart in the reference (single GPU).  Every rank scores and selects
  * on its own page range with the GLOBAL budget b (locks_rki4_score_bt after an

@@ -20,6 +20,7 @@
 // latency matters, pass no summary slab here and launch locks_rki4_build_slots
 // once per step on a forked graph branch instead (same slot_mapping, same
 // result; the page is not scored before it leaves the recent window).
+#include "kv_append.cuh"
 #include "rki4_build.cuh"
 
 namespace locks {
@@ -29,72 +30,32 @@ constexpr int KW_THREADS = 256;
 constexpr int KW_BUILD_WARPS = 4;     // measured: 4 builders finish 8 heads sooner than 8
 
 struct KvWriteParams {
-    const __nv_bfloat16* key;
-    const __nv_bfloat16* val;
-    int64_t k_row, k_head, v_row, v_head;          // element strides of key / val
-    __nv_bfloat16* k_cache;
-    __nv_bfloat16* v_cache;
-    int64_t cb, ct, ch;                            // element strides of the cache planes
-    const int64_t* slot;
-    const int64_t* pos;
-    const __nv_bfloat16* cos_sin;                  // (P, rot_dim): cos half | sin half
-    int64_t cs_row;
+    KvAppend a;
     uint8_t* records;                              // this layer's (NB, n_kv, 832) or null
     __nv_bfloat16* tags;
-    int rot_dim, neox, n_kv, page, num_blocks;
+    int n_kv;
 };
-
-__device__ __forceinline__ float rope_elem(const __nv_bfloat16* x,
-                                           const __nv_bfloat16* crow, int dd,
-                                           int rot_dim, int neox) {
-    const int half = rot_dim >> 1;
-    if (neox) {
-        const int lo = (dd < half) ? dd : dd - half;
-        const float c = __bfloat162float(crow[lo]);
-        const float s = __bfloat162float(crow[half + lo]);
-        const float e = __bfloat162float(x[lo]);
-        const float o = __bfloat162float(x[lo + half]);
-        return (dd < half) ? __fsub_rn(__fmul_rn(e, c), __fmul_rn(o, s))
-                           : __fadd_rn(__fmul_rn(o, c), __fmul_rn(e, s));
-    }
-    const int pr = dd >> 1;
-    const float c = __bfloat162float(crow[pr]);
-    const float s = __bfloat162float(crow[half + pr]);
-    const float me = __bfloat162float(x[dd]);
-    const float pa = __bfloat162float(x[dd ^ 1]);
-    return (dd & 1) ? __fadd_rn(__fmul_rn(me, c), __fmul_rn(pa, s))
-                    : __fsub_rn(__fmul_rn(me, c), __fmul_rn(pa, s));
-}
 
 __global__ void __launch_bounds__(KW_THREADS) kv_write_kernel(const KvWriteParams p) {
     __shared__ __align__(16) BuildWarpScratch scratch[KW_BUILD_WARPS];
     const int r = blockIdx.x;
-    const int64_t s = p.slot[r];
+    const int64_t s = p.a.slot[r];
     if (s < 0) return;
-    const int64_t blk = s / p.page;
-    const int t = (int)(s % p.page);
-    if (blk >= p.num_blocks) return;
+    const int64_t blk = s / p.a.page;
+    const int t = (int)(s % p.a.page);
+    if (blk >= p.a.num_blocks) return;
     const int tid = threadIdx.x;
-    const int64_t base = blk * p.cb + (int64_t)t * p.ct;
-    const __nv_bfloat16* crow =
-        p.cos_sin ? p.cos_sin + p.pos[r] * p.cs_row : nullptr;
-    for (int i = tid; i < p.n_kv * BUILD_HD; i += KW_THREADS) {
-        const int kh = i / BUILD_HD, dd = i % BUILD_HD;
-        const int64_t dst = base + (int64_t)kh * p.ch + dd;
-        p.v_cache[dst] = p.val[(int64_t)r * p.v_row + (int64_t)kh * p.v_head + dd];
-        const __nv_bfloat16* krow = p.key + (int64_t)r * p.k_row + (int64_t)kh * p.k_head;
-        p.k_cache[dst] = (crow && dd < p.rot_dim)
-            ? __float2bfloat16_rn(rope_elem(krow, crow, dd, p.rot_dim, p.neox))
-            : krow[dd];
-    }
-    if (p.records == nullptr || t != p.page - 1) return;
+    for (int i = tid; i < p.n_kv * BUILD_HD; i += KW_THREADS)
+        kv_append_elem(p.a, r, i / BUILD_HD, i % BUILD_HD);
+    if (p.records == nullptr || t != p.a.page - 1) return;
     __syncthreads();                   // the page's last row is in the cache
     const int warp = tid >> 5, lane = tid & 31;
     if (warp >= KW_BUILD_WARPS) return;
     for (int kh = warp; kh < p.n_kv; kh += KW_BUILD_WARPS) {
         const int64_t cell = blk * p.n_kv + kh;
-        rki4_build_one(scratch[warp], p.k_cache + blk * p.cb + (int64_t)kh * p.ch,
-                       p.ct, p.records + cell * REC_BYTES,
+        rki4_build_one(scratch[warp],
+                       p.a.k_cache + blk * p.a.cb + (int64_t)kh * p.a.ch, p.a.ct,
+                       p.records + cell * REC_BYTES,
                        p.tags + cell * LOCKS_TAG_WIDTH, lane);
         __syncwarp();
     }
@@ -135,20 +96,21 @@ extern "C" int locks_kv_write(
                   "aligned K rows");
     if (n_tok == 0) return LOCKS_OK;
     KvWriteParams p;
-    p.key = static_cast<const __nv_bfloat16*>(key);
-    p.val = static_cast<const __nv_bfloat16*>(val);
-    p.k_row = k_row_stride; p.k_head = k_head_stride;
-    p.v_row = v_row_stride; p.v_head = v_head_stride;
-    p.k_cache = static_cast<__nv_bfloat16*>(k_cache);
-    p.v_cache = static_cast<__nv_bfloat16*>(v_cache);
-    p.cb = kv_stride_block; p.ct = kv_stride_tok; p.ch = kv_stride_head;
-    p.slot = slot_mapping; p.pos = positions;
-    p.cos_sin = static_cast<const __nv_bfloat16*>(cos_sin);
-    p.cs_row = cos_sin_row_stride;
+    p.a.key = static_cast<const __nv_bfloat16*>(key);
+    p.a.val = static_cast<const __nv_bfloat16*>(val);
+    p.a.k_row = k_row_stride; p.a.k_head = k_head_stride;
+    p.a.v_row = v_row_stride; p.a.v_head = v_head_stride;
+    p.a.k_cache = static_cast<__nv_bfloat16*>(k_cache);
+    p.a.v_cache = static_cast<__nv_bfloat16*>(v_cache);
+    p.a.cb = kv_stride_block; p.a.ct = kv_stride_tok; p.a.ch = kv_stride_head;
+    p.a.slot = slot_mapping; p.a.pos = positions;
+    p.a.cos_sin = static_cast<const __nv_bfloat16*>(cos_sin);
+    p.a.cs_row = cos_sin_row_stride;
+    p.a.rot_dim = rot_dim; p.a.neox = neox; p.a.page = page;
+    p.a.num_blocks = num_blocks; p.a.head_dim = head_dim;
     p.records = static_cast<uint8_t*>(records_layer);
     p.tags = static_cast<__nv_bfloat16*>(tags_layer);
-    p.rot_dim = rot_dim; p.neox = neox; p.n_kv = n_kv; p.page = page;
-    p.num_blocks = num_blocks;
+    p.n_kv = n_kv;
     kv_write_kernel<<<n_tok, KW_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(p);
     if (records_layer) pdl_break();    // the scorer prefetches summaries before its wait
     return check_launch("locks_kv_write");

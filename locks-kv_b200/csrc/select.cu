@@ -25,6 +25,7 @@
 #include <cooperative_groups.h>
 
 #include "common.cuh"
+#include "kv_append.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -71,6 +72,7 @@ struct SelParams {
     int n_kv, G, max_pages, sink;
     int owner_mode;     // keys of a whole row fit one CTA: helpers only combine
     int key_cap;        // key slots per CTA (the histogram copies follow them)
+    KvAppend app;       // optional: the new token's K/V store of this layer (key != null)
 };
 
 TL_DECL(g_sel_tl)
@@ -306,7 +308,8 @@ __device__ __forceinline__ void sweep_max_groups(
 // cluster keeps and selects the keys of its page slice.
 // GT: the GQA group size rounded up to a power of two (a kernel per value keeps
 // the once-through instruction stream short).
-template <int NT, bool OWNER, int GT>
+// APPEND: the launch also stores the new token's K/V of its rows (p.app).
+template <int NT, bool OWNER, int GT, bool APPEND>
 __global__ void __launch_bounds__(NT)
 topb_kernel(const SelParams p) {
     constexpr int NW = NT / 32;
@@ -449,6 +452,13 @@ topb_kernel(const SelParams p) {
             for (int i = cnt_max + (c_phys - 1) * NT + tid; i < MP;
                  i += (CL_phys - 1) * NT)
                 tabp[i] = -1;
+            // the last helper also stores the row's new token (K rotated) into
+            // the cache: it is done here long before CTA 0 has selected, and the
+            // decode that reads the cache starts only when this grid has ended
+            if constexpr (APPEND) {
+                if (c_phys == CL_phys - 1 && tid < p.app.head_dim)
+                    kv_append_elem(p.app, r, kh, tid);
+            }
             return;
         }
     } else {
@@ -634,6 +644,11 @@ topb_kernel(const SelParams p) {
         for (int i = cnt + c * NT + tid; i < pad_end; i += CL * NT) tab[i] = -1;
     }
     if (c == 0 && tid == 0) p.page_cnt[row] = cnt;
+    // without helper CTAs the last CTA of the row stores the new token
+    if constexpr (APPEND) {
+        if (!owner && c_phys == CL_phys - 1 && tid < p.app.head_dim)
+            kv_append_elem(p.app, r, kh, tid);
+    }
     SEL_TS(18);
     SEL_TS(19);
     TL_MARK(g_sel_tl, 2);
@@ -667,11 +682,12 @@ extern "C" int locks_derive_page_params(
     return check_launch("locks_derive_page_params");
 }
 
-extern "C" int locks_topb_select(
+static int topb_select_impl(
     int combine, const float* score_h, float* score, uint32_t* hmax,
     const int32_t* n_pages, const int32_t* n_sel_hi, const int32_t* b_fix,
     int32_t* page_table, int32_t* page_cnt, int n_req, int n_kv, int G,
-    int max_pages, int sink_pages, locks_stream_t stream) {
+    int max_pages, int sink_pages, const locks_kv_append_t* app,
+    locks_stream_t stream) {
     using namespace locks;
     LOCKS_REQUIRE(combine >= 0 && combine <= 2, LOCKS_ERR_ARG,
                   "locks_topb_select: combine must be 0, 1 or 2, got %d", combine);
@@ -690,6 +706,39 @@ extern "C" int locks_topb_select(
     p.n_pages = n_pages; p.n_sel_hi = n_sel_hi; p.b_fix = b_fix;
     p.page_table = page_table; p.page_cnt = page_cnt;
     p.n_kv = n_kv; p.G = G; p.max_pages = max_pages; p.sink = sink_pages;
+    p.app = KvAppend{};
+    if (app != nullptr) {
+        LOCKS_REQUIRE(app->key && app->val && app->k_cache && app->v_cache &&
+                          app->slot_mapping,
+                      LOCKS_ERR_ARG, "locks_topb_select_append: null pointer in the "
+                      "append description");
+        LOCKS_REQUIRE(app->head_dim >= 1 && app->head_dim <= SEL_THREADS &&
+                          app->page >= 1 && app->num_blocks >= 1,
+                      LOCKS_ERR_GEOMETRY,
+                      "locks_topb_select_append: head_dim %d / page %d unsupported",
+                      app->head_dim, app->page);
+        LOCKS_REQUIRE(app->cos_sin == nullptr ||
+                          (app->positions && app->rot_dim >= 2 &&
+                           app->rot_dim <= app->head_dim && (app->rot_dim & 1) == 0 &&
+                           app->cos_sin_row_stride >= app->rot_dim),
+                      LOCKS_ERR_ARG,
+                      "locks_topb_select_append: rotation needs positions and an "
+                      "even rot_dim <= head_dim");
+        p.app.key = static_cast<const __nv_bfloat16*>(app->key);
+        p.app.val = static_cast<const __nv_bfloat16*>(app->val);
+        p.app.k_row = app->k_row_stride; p.app.k_head = app->k_head_stride;
+        p.app.v_row = app->v_row_stride; p.app.v_head = app->v_head_stride;
+        p.app.k_cache = static_cast<__nv_bfloat16*>(app->k_cache);
+        p.app.v_cache = static_cast<__nv_bfloat16*>(app->v_cache);
+        p.app.cb = app->kv_stride_block; p.app.ct = app->kv_stride_tok;
+        p.app.ch = app->kv_stride_head;
+        p.app.slot = app->slot_mapping; p.app.pos = app->positions;
+        p.app.cos_sin = static_cast<const __nv_bfloat16*>(app->cos_sin);
+        p.app.cs_row = app->cos_sin_row_stride;
+        p.app.rot_dim = app->rot_dim; p.app.neox = app->neox;
+        p.app.page = app->page; p.app.num_blocks = app->num_blocks;
+        p.app.head_dim = app->head_dim;
+    }
     // Short rows (keys fit one CTA): owner mode, up to 4 CTAs share the combine.
     // Long rows: the smallest power-of-two cluster whose CTAs hold the keys.
     int cl = 1;
@@ -726,16 +775,18 @@ extern "C" int locks_topb_select(
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-#define LOCKS_SEL_ATTR(GTV)                                                        \
-        cudaFuncSetAttribute(topb_kernel<SEL_THREADS, true, GTV>,                  \
+#define LOCKS_SEL_ATTR_A(GTV, AP)                                                  \
+        cudaFuncSetAttribute(topb_kernel<SEL_THREADS, true, GTV, AP>,              \
                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);\
-        cudaFuncSetAttribute(topb_kernel<SEL_THREADS, false, GTV>,                 \
+        cudaFuncSetAttribute(topb_kernel<SEL_THREADS, false, GTV, AP>,             \
                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);\
-        cudaFuncSetAttribute(topb_kernel<SEL_THREADS, false, GTV>,                 \
+        cudaFuncSetAttribute(topb_kernel<SEL_THREADS, false, GTV, AP>,             \
                              cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+#define LOCKS_SEL_ATTR(GTV) LOCKS_SEL_ATTR_A(GTV, false) LOCKS_SEL_ATTR_A(GTV, true)
         LOCKS_SEL_ATTR(1) LOCKS_SEL_ATTR(2) LOCKS_SEL_ATTR(4) LOCKS_SEL_ATTR(8)
         LOCKS_SEL_ATTR(16)
 #undef LOCKS_SEL_ATTR
+#undef LOCKS_SEL_ATTR_A
         attr_done[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
@@ -753,11 +804,41 @@ extern "C" int locks_topb_select(
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
     cudaError_t e = cudaSuccess;
-    LOCKS_DISPATCH_GT(G, (e = owner_mode
-        ? cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, true, GT>, p)
-        : cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, false, GT>, p)));
+    if (app == nullptr) {
+        LOCKS_DISPATCH_GT(G, (e = owner_mode
+            ? cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, true, GT, false>, p)
+            : cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, false, GT, false>, p)));
+    } else {
+        LOCKS_DISPATCH_GT(G, (e = owner_mode
+            ? cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, true, GT, true>, p)
+            : cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, false, GT, true>, p)));
+    }
     if (e != cudaSuccess)
         return fail(LOCKS_ERR_LAUNCH, "locks_topb_select: %s",
                     cudaGetErrorString(e));
     return check_launch("locks_topb_select");
+}
+
+extern "C" int locks_topb_select(
+    int combine, const float* score_h, float* score, uint32_t* hmax,
+    const int32_t* n_pages, const int32_t* n_sel_hi, const int32_t* b_fix,
+    int32_t* page_table, int32_t* page_cnt, int n_req, int n_kv, int G,
+    int max_pages, int sink_pages, locks_stream_t stream) {
+    return topb_select_impl(combine, score_h, score, hmax, n_pages, n_sel_hi, b_fix,
+                            page_table, page_cnt, n_req, n_kv, G, max_pages,
+                            sink_pages, nullptr, stream);
+}
+
+extern "C" int locks_topb_select_append(
+    int combine, const float* score_h, float* score, uint32_t* hmax,
+    const int32_t* n_pages, const int32_t* n_sel_hi, const int32_t* b_fix,
+    int32_t* page_table, int32_t* page_cnt, int n_req, int n_kv, int G,
+    int max_pages, int sink_pages, const locks_kv_append_t* append,
+    locks_stream_t stream) {
+    using namespace locks;
+    LOCKS_REQUIRE(append != nullptr, LOCKS_ERR_ARG,
+                  "locks_topb_select_append: null append description");
+    return topb_select_impl(combine, score_h, score, hmax, n_pages, n_sel_hi, b_fix,
+                            page_table, page_cnt, n_req, n_kv, G, max_pages,
+                            sink_pages, append, stream);
 }

@@ -32,6 +32,8 @@ _SIGNATURES = {
                              _I, _I, _I, _I, _F, _I, _P, _P], 1),
     "locks_topb_select": ([_I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I,
                            _I, _P], 1),
+    "locks_topb_select_append": ([_I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I,
+                                  _I, _I, _P, _P], 1),
     "locks_decode_split": ([_P, _L, _P, _P, _L, _L, _L, _P, _L, _P, _P, _P, _P,
                             _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P,
                             _P], 1),
@@ -122,6 +124,18 @@ def ptr(t) -> c_void_p:
                            f"memory the GPU reads in place), got {t.device}: "
                            "there is no CPU path")
     return c_void_p(t.data_ptr())
+
+
+class KvAppendDesc(ctypes.Structure):
+    """``locks_kv_append_t`` of the header, field for field."""
+    _fields_ = [("key", _P), ("k_row_stride", _L), ("k_head_stride", _L),
+                ("val", _P), ("v_row_stride", _L), ("v_head_stride", _L),
+                ("k_cache", _P), ("v_cache", _P), ("kv_stride_block", _L),
+                ("kv_stride_tok", _L), ("kv_stride_head", _L),
+                ("slot_mapping", _P), ("positions", _P), ("cos_sin", _P),
+                ("cos_sin_row_stride", _L), ("rot_dim", ctypes.c_int32),
+                ("neox", ctypes.c_int32), ("head_dim", ctypes.c_int32),
+                ("page", ctypes.c_int32), ("num_blocks", ctypes.c_int32)]
 
 
 def stream() -> c_void_p:

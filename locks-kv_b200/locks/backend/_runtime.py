@@ -43,7 +43,7 @@ def _layer_index(st, kv_cache) -> int:
 
 
 def _rki4_select_adapter(q, kv_cache, block_table, seq_lens, st, n_req, scale,
-                         cfg) -> None:
+                         cfg, append=None) -> None:
     """Stage A of one layer: score every selectable page from the packed
     summaries into ``st.score_h``, combine over the GQA group and keep the
     top-b pages (``st.page_table`` / ``st.page_cnt``).  The builder already
@@ -56,7 +56,8 @@ def _rki4_select_adapter(q, kv_cache, block_table, seq_lens, st, n_req, scale,
               f"{st.zsplit or 'auto'}, combine={st.combine}) + radix top-b",
               file=sys.stderr, flush=True)
     lidx = _layer_index(st, kv_cache)
-    rki4_score_state(st, lidx, q, block_table, seq_lens, n_req, scale)
+    rki4_score_state(st, lidx, q, block_table, seq_lens, n_req, scale,
+                     append=append)
 
 
 def decode_dispatch(q, kv_cache, block_table, seq_lens, st, out, vsource,

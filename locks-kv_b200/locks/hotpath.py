@@ -113,17 +113,20 @@ class HotPath:
 
     # ---- decode loop: append one token per request, then attend --------------
     def enable_append(self, cos_sin: Optional[torch.Tensor] = None,
-                      neox: bool = True) -> None:
+                      neox: bool = True, fuse_write: bool = True) -> None:
         """Allocate what ``append_step`` needs: the new token's K/V per layer
         (``new_k`` / ``new_v``, (L, R, n_kv, d) bf16, filled by the caller
         before each step), the slot and position vectors it derives on the
         device, and the side stream of the summary build.  ``cos_sin`` is the
         (positions, rot_dim) cos|sin table of the rotation, or None for K that
         arrives rotated.  The block table must hold a block for every page the
-        appended tokens reach."""
-        from .attention import rope_and_cache
+        appended tokens reach.  ``fuse_write``: the selector's launch stores
+        the token (no KV-write launch); otherwise ``locks_kv_write`` runs in
+        front of every layer."""
+        from .attention import kv_append_desc, rope_and_cache
         dev, R, L = self.device, self.n_req, len(self.kv_caches)
         self._rope_and_cache = rope_and_cache
+        self._fuse_write = bool(fuse_write)
         self.cos_sin, self.neox = cos_sin, neox
         self.new_k = torch.zeros(L, R, self.n_kv, self.d, device=dev,
                                  dtype=torch.bfloat16)
@@ -133,6 +136,11 @@ class HotPath:
         self.slot_prev = torch.full((R,), -1, dtype=torch.int64, device=dev)
         self._side = torch.cuda.Stream(device=dev)
         self.append_graph: Optional[torch.cuda.CUDAGraph] = None
+        pos = self.pos if cos_sin is not None else None
+        self._append_desc = [
+            kv_append_desc(self.new_k[l], self.new_v[l], kvc, self.slot, pos,
+                           cos_sin, neox=neox)
+            for l, kvc in enumerate(self.kv_caches)] if fuse_write else None
 
     def _append_step(self) -> None:
         """One decode step as a model runs it, every decision on the device:
@@ -155,13 +163,15 @@ class HotPath:
         self.derive()
         st, R = self.st, self.n_req
         for l, kvc in enumerate(self.kv_caches):
-            self._rope_and_cache(self.new_k[l], self.new_v[l], kvc, self.slot,
-                                 self.pos if self.cos_sin is not None else None,
-                                 self.cos_sin, neox=self.neox)
+            if not self._fuse_write:
+                self._rope_and_cache(self.new_k[l], self.new_v[l], kvc, self.slot,
+                                     self.pos if self.cos_sin is not None else None,
+                                     self.cos_sin, neox=self.neox)
             q = self.q[l, :R]
-            _runtime._rki4_select_adapter(q, kvc, self.block_table,
-                                          self.seq_lens, st, R, self.scale,
-                                          self.cfg)
+            _runtime._rki4_select_adapter(
+                q, kvc, self.block_table, self.seq_lens, st, R, self.scale,
+                self.cfg,
+                append=self._append_desc[l] if self._fuse_write else None)
             _runtime.decode_dispatch(q, kvc, self.block_table, self.seq_lens, st,
                                      self.out[l], self.vsources[l], self.scale,
                                      self.cfg)

@@ -30,13 +30,15 @@ def rki4_score_only(st, lidx: int, q, block_table, seq_lens, n_req: int,
                _cabi.stream())
 
 
-def rki4_select_only(st, n_req: int, has_hmax: bool = True) -> None:
-    """GQA combine (``st.combine``) + exact top-b from ``st.score_h``."""
-    nrmtopb_select(st, n_req, has_hmax=has_hmax)
+def rki4_select_only(st, n_req: int, has_hmax: bool = True, append=None) -> None:
+    """GQA combine (``st.combine``) + exact top-b from ``st.score_h``.
+    ``append`` (``attention.kv_append_desc``): the layer's KV write rides in the
+    same launch."""
+    nrmtopb_select(st, n_req, has_hmax=has_hmax, append=append)
 
 
 def rki4_score_state(st, lidx: int, q, block_table, seq_lens, n_req: int,
-                     scale: float) -> None:
+                     scale: float, append=None) -> None:
     """Score then select: the whole Stage A of one layer (2 launches)."""
     rki4_score_only(st, lidx, q, block_table, seq_lens, n_req, scale)
-    rki4_select_only(st, n_req)
+    rki4_select_only(st, n_req, append=append)

@@ -21,14 +21,20 @@ def derive_page_params(st, seq_lens, n_req: int) -> None:
                _cabi.ptr(st.b_fix), _cabi.stream())
 
 
-def _select(st, n_req: int, combine: int, use_hmax: bool) -> None:
-    _cabi.call("locks_topb_select", int(combine), _cabi.ptr(st.score_h),
-               _cabi.ptr(st.score),
-               _cabi.ptr(st.hmax if (use_hmax and st.hmax is not None) else None),
-               _cabi.ptr(st.n_pages), _cabi.ptr(st.n_sel_hi),
-               _cabi.ptr(st.b_fix), _cabi.ptr(st.page_table),
-               _cabi.ptr(st.page_cnt), int(n_req), int(st.n_kv), int(st.G),
-               int(st.max_pages), int(st.sink_pages), _cabi.stream())
+def _select(st, n_req: int, combine: int, use_hmax: bool, append=None) -> None:
+    args = (int(combine), _cabi.ptr(st.score_h), _cabi.ptr(st.score),
+            _cabi.ptr(st.hmax if (use_hmax and st.hmax is not None) else None),
+            _cabi.ptr(st.n_pages), _cabi.ptr(st.n_sel_hi),
+            _cabi.ptr(st.b_fix), _cabi.ptr(st.page_table),
+            _cabi.ptr(st.page_cnt), int(n_req), int(st.n_kv), int(st.G),
+            int(st.max_pages), int(st.sink_pages))
+    if append is None:
+        _cabi.call("locks_topb_select", *args, _cabi.stream())
+    else:       # a KvAppendDesc (attention.kv_append_desc): the layer's KV write
+        import ctypes
+        _cabi.call("locks_topb_select_append", *args,
+                   ctypes.cast(ctypes.pointer(append), ctypes.c_void_p),
+                   _cabi.stream())
 
 
 def topb_select(st, n_req: int) -> None:
@@ -37,8 +43,9 @@ def topb_select(st, n_req: int) -> None:
     _select(st, n_req, COMBINE_NONE, False)
 
 
-def nrmtopb_select(st, n_req: int, has_hmax: bool = False) -> None:
+def nrmtopb_select(st, n_req: int, has_hmax: bool = False, append=None) -> None:
     """Fused GQA combine + top-b from ``st.score_h`` using the state's combine
-    mode (reference ``selection/select_cuda.py:3614-3731``)."""
+    mode (reference ``selection/select_cuda.py:3614-3731``).  ``append``: the
+    layer's KV write, stored by the same launch."""
     _select(st, n_req, COMBINE_NRM if st.combine == "nrm" else COMBINE_MAX,
-            has_hmax and st.combine == "nrm")
+            has_hmax and st.combine == "nrm", append)

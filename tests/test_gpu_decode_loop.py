@@ -45,7 +45,8 @@ def _case(extra):
     return cpu, shape, bt, lens
 
 
-def test_append_loop_leaves_the_state_of_a_fresh_build():
+@pytest.mark.parametrize("fuse_write", [True, False])
+def test_append_loop_leaves_the_state_of_a_fresh_build(fuse_write):
     from locks.config import LocksConfig
     from locks.hotpath import HotPath
     steps, extra = 40, 3
@@ -65,7 +66,7 @@ def test_append_loop_leaves_the_state_of_a_fresh_build():
     P = max(lens) + steps + 1
     ang = torch.rand(P, sh.d // 2, generator=g) * 6.28
     cs = torch.cat([ang.cos(), ang.sin()], 1).to(torch.bfloat16)
-    hp.enable_append(cs.to(DEV), neox=True)
+    hp.enable_append(cs.to(DEV), neox=True, fuse_write=fuse_write)
     new_k = torch.randn(steps, L, R, sh.n_kv, sh.d, generator=g).to(torch.bfloat16)
     new_v = torch.randn(steps, L, R, sh.n_kv, sh.d, generator=g).to(torch.bfloat16)
     for s in range(steps):

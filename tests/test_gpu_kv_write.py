@@ -129,3 +129,53 @@ def test_slot_driven_build_matches_block_list_build():
     for blk in (0, 1, 3, 4, 6, 7):
         assert bool(torch.isnan(st.pp_tag[:, blk].float()).all())
         assert int(st.pp_rec[:, blk].abs().sum()) == 0
+
+
+@pytest.mark.parametrize("MP,R,n_kv", [(48, 3, 2),       # one CTA per row
+                                       (8200, 1, 8),     # owner CTA + helper CTAs
+                                       (40000, 2, 2)])   # a cluster of slices
+def test_selector_carries_the_kv_write(MP, R, n_kv):
+    """``rki4_select_only(..., append=desc)`` leaves the cache exactly as
+    ``rope_and_cache`` does (and as the oracle says), for every way the selector
+    spreads a row over CTAs, and selects exactly what it selects without the
+    write.  One row carries slot -1: nothing may be stored for it."""
+    from locks.attention import kv_append_desc, rope_and_cache
+    from locks.selection import Rki4State, derive_page_params, rki4_select_only
+    G, d, page, NB = 4, 128, 16, 9
+    g = torch.Generator().manual_seed(MP + R)
+    cache = torch.randn(NB, 2, page, n_kv, d, generator=g).to(torch.bfloat16)
+    key = torch.randn(R, n_kv, d, generator=g).to(torch.bfloat16)
+    val = torch.randn(R, n_kv, d, generator=g).to(torch.bfloat16)
+    cs = _table(512, 64, 3)
+    slots = torch.tensor([5 * page + 15, -1, 2 * page + 4][:R], dtype=torch.int64)
+    pos = torch.tensor([300, 7, 511][:R], dtype=torch.int64)
+    kc = cache[:, 0].float().numpy().copy()
+    vc = cache[:, 1].float().numpy().copy()
+    orc.rope_and_cache(key.float().numpy(), val.float().numpy(), kc, vc,
+                       slots.numpy(), pos.numpy(), cs.float().numpy(), 64, False,
+                       page)
+    st = Rki4State(DEV, num_layers=1, num_blocks=NB, n_kv=n_kv, G=G, head_dim=d,
+                   page=page, max_reqs=R, max_pages=MP, budget_pages=20,
+                   sink_pages=1, window_pages=2)
+    sl = torch.tensor([MP * 16 - 3, 40, (MP // 2) * 16 + 1][:R], dtype=torch.int32)
+    derive_page_params(st, sl.to(DEV), R)
+    st.score_h.copy_(torch.randn(R, n_kv, G, MP, generator=g).to(DEV))
+    rki4_select_only(st, R, has_hmax=False)
+    torch.cuda.synchronize()
+    tab0, cnt0 = st.page_table.clone(), st.page_cnt.clone()
+    st.page_table.fill_(-7)
+    dev_key, dev_val, dev_cache = key.to(DEV), val.to(DEV), cache.to(DEV)
+    dev_slots, dev_pos, dev_cs = slots.to(DEV), pos.to(DEV), cs.to(DEV)
+    desc = kv_append_desc(dev_key, dev_val, dev_cache, dev_slots, dev_pos, dev_cs,
+                          neox=False)
+    rki4_select_only(st, R, has_hmax=False, append=desc)
+    torch.cuda.synchronize()
+    assert torch.equal(st.page_table, tab0) and torch.equal(st.page_cnt, cnt0)
+    assert np.array_equal(t2n(dev_cache[:, 0].float()), kc)
+    assert np.array_equal(t2n(dev_cache[:, 1].float()), vc)
+    # and the stand-alone kernel agrees
+    ref_cache = cache.to(DEV)
+    rope_and_cache(dev_key, dev_val, ref_cache, dev_slots, dev_pos, dev_cs,
+                   neox=False)
+    torch.cuda.synchronize()
+    assert torch.equal(ref_cache, dev_cache)
