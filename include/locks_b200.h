@@ -240,6 +240,21 @@ int locks_kv_write(const void* key, int64_t k_row_stride, int64_t k_head_stride,
                    int n_kv, int head_dim, int page, int num_blocks,
                    locks_stream_t stream);
 
+/* ---- Decode-step bookkeeping on the device ------------------------------------
+ * For every request row: positions[r] = seq_lens[r] (index of the token this
+ * step appends), slot_prev[r] = slot_mapping[r], slot_mapping[r] = block_table[r,
+ * tok / page] * page + tok % page (-1 when the table has no such column),
+ * seq_lens[r] += 1, then the page parameters of locks_derive_page_params for the
+ * new length.  One launch, so a captured decode loop carries no host decision.
+ * (The reference gets slot_mapping / positions from the engine's host-side
+ * scheduler and derives the page parameters in selection/select.py:51-58.) */
+int locks_append_advance(int32_t* seq_lens, const int32_t* block_table,
+                         int64_t bt_stride, int bt_width, int n_req, int page,
+                         int window_pages, int sink_pages, int budget_pages,
+                         double budget, int64_t* slot_mapping, int64_t* slot_prev,
+                         int64_t* positions, int32_t* n_pages, int32_t* n_sel_hi,
+                         int32_t* b_fix, locks_stream_t stream);
+
 /* ---- Selection that also carries the layer's KV write -------------------------
  * The store of locks_kv_write (same arguments, same arithmetic, no summary
  * build), one token per request row: row r of key / val goes to slot_mapping[r].

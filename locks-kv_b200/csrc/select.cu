@@ -59,6 +59,49 @@ __global__ void derive_kernel(const int32_t* __restrict__ seq_lens, int n_req,
     b_fix[i] = b;
 }
 
+// One decode step's bookkeeping for every request row, then its page parameters:
+// the appended token's index is the current length, its slot comes from the block
+// table, the length grows by one.  slot_prev keeps the slot of the step before
+// (the summary build of pages that step completed reads it).
+__global__ void advance_kernel(int32_t* __restrict__ seq_lens,
+                               const int32_t* __restrict__ block_table,
+                               int64_t bt_stride, int bt_width, int n_req, int page,
+                               int window, int sink, int budget_pages, double budget,
+                               int64_t* __restrict__ slot,
+                               int64_t* __restrict__ slot_prev,
+                               int64_t* __restrict__ pos,
+                               int32_t* __restrict__ n_pages,
+                               int32_t* __restrict__ n_sel_hi,
+                               int32_t* __restrict__ b_fix) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_req) return;
+    const int tok = seq_lens[i];
+    const int pg = tok / page;
+    slot_prev[i] = slot[i];
+    if (tok < 0 || pg >= bt_width) {             // no block for the token: no write
+        slot[i] = -1;
+        pos[i] = max(tok, 0);
+    } else {
+        slot[i] = (int64_t)block_table[(int64_t)i * bt_stride + pg] * page + tok % page;
+        pos[i] = tok;
+    }
+    const int sl = tok + 1;
+    seq_lens[i] = sl;
+    const int npg = (sl + page - 1) / page;
+    const int nsh = npg - window;
+    const int s = nsh - sink;
+    int b;
+    if (budget_pages > 0) {
+        b = max(min(budget_pages, max(s, 1)), 1);
+    } else {
+        const double bf = ceil((double)s * budget);
+        b = min(max((int)bf, 1), max(s, 1));
+    }
+    n_pages[i] = npg;
+    n_sel_hi[i] = nsh;
+    b_fix[i] = b;
+}
+
 struct SelParams {
     int combine;
     const float* score_h;
@@ -680,6 +723,27 @@ extern "C" int locks_derive_page_params(
         n_pages, n_sel_hi, b_fix);
     pdl_break();
     return check_launch("locks_derive_page_params");
+}
+
+extern "C" int locks_append_advance(
+    int32_t* seq_lens, const int32_t* block_table, int64_t bt_stride, int bt_width,
+    int n_req, int page, int window_pages, int sink_pages, int budget_pages,
+    double budget, int64_t* slot_mapping, int64_t* slot_prev, int64_t* positions,
+    int32_t* n_pages, int32_t* n_sel_hi, int32_t* b_fix, locks_stream_t stream) {
+    using namespace locks;
+    LOCKS_REQUIRE(seq_lens && block_table && slot_mapping && slot_prev && positions &&
+                      n_pages && n_sel_hi && b_fix,
+                  LOCKS_ERR_ARG, "locks_append_advance: null pointer argument");
+    LOCKS_REQUIRE(n_req >= 0 && page > 0 && bt_width >= 1 && window_pages >= 0 &&
+                      sink_pages >= 0,
+                  LOCKS_ERR_ARG, "locks_append_advance: bad size argument");
+    if (n_req == 0) return LOCKS_OK;
+    advance_kernel<<<(n_req + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        seq_lens, block_table, bt_stride, bt_width, n_req, page, window_pages,
+        sink_pages, budget_pages, budget, slot_mapping, slot_prev, positions, n_pages,
+        n_sel_hi, b_fix);
+    pdl_break();
+    return check_launch("locks_append_advance");
 }
 
 static int topb_select_impl(

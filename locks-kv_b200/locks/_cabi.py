@@ -32,6 +32,8 @@ _SIGNATURES = {
                              _I, _I, _I, _I, _F, _I, _P, _P], 1),
     "locks_topb_select": ([_I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I,
                            _I, _P], 1),
+    "locks_append_advance": ([_P, _P, _L, _I, _I, _I, _I, _I, _I, _D, _P, _P, _P,
+                              _P, _P, _P, _P], 1),
     "locks_topb_select_append": ([_I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I,
                                   _I, _I, _P, _P], 1),
     "locks_decode_split": ([_P, _L, _P, _P, _L, _L, _L, _P, _L, _P, _P, _P, _P,

@@ -18,8 +18,8 @@ from . import _cabi
 from .attention import ResidentVSource, ensure_stage_b_buffers
 from .backend import _runtime
 from .config import LocksConfig
-from .selection import (Rki4State, derive_page_params, rki4_build_bulk,
-                        rki4_build_slots, rki4_build_tail)
+from .selection import (Rki4State, append_advance, derive_page_params,
+                        rki4_build_bulk, rki4_build_slots, rki4_build_tail)
 
 
 class HotPath:
@@ -152,15 +152,11 @@ class HotPath:
         ``window_pages`` more pages, so no step scores it before the join at
         the end of this one."""
         cur = torch.cuda.current_stream()
+        append_advance(self.st, self.seq_lens, self.block_table, self.n_req,
+                       self.slot, self.slot_prev, self.pos)
         self._side.wait_stream(cur)
         with torch.cuda.stream(self._side):
             rki4_build_slots(self.st, self.K_layers, self.slot_prev)
-        self.pos.copy_(self.seq_lens)
-        blk = self.block_table.gather(1, (self.pos // self.page)[:, None])
-        self.slot.copy_(blk.squeeze(1).to(torch.int64) * self.page
-                        + self.pos % self.page)
-        self.seq_lens.add_(1)
-        self.derive()
         st, R = self.st, self.n_req
         for l, kvc in enumerate(self.kv_caches):
             if not self._fuse_write:
@@ -176,7 +172,6 @@ class HotPath:
                                      self.out[l], self.vsources[l], self.scale,
                                      self.cfg)
         cur.wait_stream(self._side)
-        self.slot_prev.copy_(self.slot)
 
     def append_step(self) -> torch.Tensor:
         """Replay the captured append-and-attend step (captured on first use;
@@ -199,5 +194,5 @@ class HotPath:
     def flush_builds(self) -> None:
         """Build the summaries of pages completed by the last appended token
         (``append_step`` leaves them to the following step)."""
-        rki4_build_slots(self.st, self.K_layers, self.slot_prev)
-        self.slot_prev.fill_(-1)
+        rki4_build_slots(self.st, self.K_layers, self.slot)
+        self.slot.fill_(-1)

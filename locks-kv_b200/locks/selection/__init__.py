@@ -15,7 +15,8 @@ from .rki4_build import (rki4_build_bulk, rki4_build_delta,
                          rki4_build_tail)
 from .rki4_score import rki4_score_only, rki4_score_state, rki4_select_only
 from .rki4_state import TAGW, Rki4State
-from .select import derive_page_params, nrmtopb_select, topb_select
+from .select import (append_advance, derive_page_params, nrmtopb_select,
+                     topb_select)
 from .mla_select import (MlaState, build_page_factors, build_prompt_factors,
                          mla_decode, mla_derive, mla_forward, mla_page_score,
                          mla_select_pages)
@@ -23,7 +24,7 @@ from .mla_select import (MlaState, build_page_factors, build_prompt_factors,
 __all__ = [
     "Rki4State", "TAGW", "rki4_build_refresh", "rki4_build_slots",
     "rki4_build_tail",
-    "rki4_build_bulk", "rki4_build_delta", "derive_page_params", "topb_select",
+    "rki4_build_bulk", "rki4_build_delta", "append_advance", "derive_page_params", "topb_select",
     "nrmtopb_select", "rki4_score_only", "rki4_select_only", "rki4_score_state",
     "MlaState", "build_page_factors", "build_prompt_factors", "mla_derive",
     "mla_page_score", "mla_select_pages", "mla_decode", "mla_forward",

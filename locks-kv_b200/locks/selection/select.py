@@ -6,6 +6,8 @@ fixed-shape, allocation-free and sync-free.
 """
 from __future__ import annotations
 
+import torch
+
 from .. import _cabi
 
 COMBINE_NONE, COMBINE_NRM, COMBINE_MAX = 0, 1, 2
@@ -19,6 +21,24 @@ def derive_page_params(st, seq_lens, n_req: int) -> None:
                int(getattr(st, "budget_abs", 0)), float(st.budget),
                _cabi.ptr(st.n_pages), _cabi.ptr(st.n_sel_hi),
                _cabi.ptr(st.b_fix), _cabi.stream())
+
+
+def append_advance(st, seq_lens, block_table, n_req: int, slot, slot_prev,
+                   positions) -> None:
+    """One decode step's bookkeeping on the device: ``positions`` <- lengths,
+    ``slot_prev`` <- ``slot``, ``slot`` <- the appended token's cache slot,
+    lengths grow by one, then :func:`derive_page_params` for the new lengths."""
+    assert n_req <= st.max_reqs
+    assert seq_lens.dtype == torch.int32 and block_table.dtype == torch.int32
+    assert slot.dtype == slot_prev.dtype == positions.dtype == torch.int64
+    assert block_table.stride(1) == 1
+    _cabi.call("locks_append_advance", _cabi.ptr(seq_lens), _cabi.ptr(block_table),
+               block_table.stride(0), int(block_table.shape[1]), int(n_req),
+               int(st.page), int(st.window_pages), int(st.sink_pages),
+               int(getattr(st, "budget_abs", 0)), float(st.budget),
+               _cabi.ptr(slot), _cabi.ptr(slot_prev), _cabi.ptr(positions),
+               _cabi.ptr(st.n_pages), _cabi.ptr(st.n_sel_hi), _cabi.ptr(st.b_fix),
+               _cabi.stream())
 
 
 def _select(st, n_req: int, combine: int, use_hmax: bool, append=None) -> None:
