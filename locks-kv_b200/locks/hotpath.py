@@ -111,6 +111,50 @@ class HotPath:
         self.graph.replay()
         return self.out
 
+    # ---- one step fed from, and read back to, host memory ----------------------
+    def enable_host_io(self) -> None:
+        """Pinned host staging for a caller whose tensors live in host memory:
+        ``host_q`` (L, R, H, d), ``host_seq_lens``, ``host_block_table`` are
+        written by the caller before ``step_host``; ``host_out`` holds the
+        result after it."""
+        R = self.n_req
+        pin = lambda t: torch.empty(t.shape, dtype=t.dtype).pin_memory()
+        self.host_q = pin(self.q[:, :R])
+        self.host_seq_lens = pin(self.seq_lens)
+        self.host_block_table = pin(self.block_table)
+        self.host_out = pin(self.out[:, :R])
+        self.io_graph: Optional[torch.cuda.CUDAGraph] = None
+
+    def _io_step(self) -> None:
+        R = self.n_req
+        self.q[:, :R].copy_(self.host_q, non_blocking=True)
+        self.seq_lens.copy_(self.host_seq_lens, non_blocking=True)
+        self.block_table.copy_(self.host_block_table, non_blocking=True)
+        self.derive()
+        self._layers()
+        self.host_out.copy_(self.out[:, :R], non_blocking=True)
+
+    def step_host(self) -> torch.Tensor:
+        """Host buffers in, host buffer out: the three host-to-device copies,
+        the page parameters, the L-layer step and the device-to-host copy are
+        ONE graph replay (copy nodes read and write the pinned buffers in
+        place), followed by a stream synchronise -- ``host_out`` is valid on
+        return."""
+        if self.io_graph is None:
+            s = torch.cuda.Stream(device=self.device)
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._io_step()
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._io_step()
+            self.io_graph = g
+        self.io_graph.replay()
+        torch.cuda.current_stream().synchronize()
+        return self.host_out
+
     # ---- decode loop: append one token per request, then attend --------------
     def enable_append(self, cos_sin: Optional[torch.Tensor] = None,
                       neox: bool = True, fuse_write: bool = True) -> None:

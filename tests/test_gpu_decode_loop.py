@@ -130,3 +130,38 @@ def test_append_loop_leaves_the_state_of_a_fresh_build(fuse_write):
     assert np.isfinite(a).all()
     # same kernels over the same bytes; the decode tolerance (2e-2 abs, 1e-2 rel)
     np.testing.assert_allclose(a, b, atol=2e-2, rtol=1e-2)
+
+
+def test_step_host_equals_step():
+    """``HotPath.step_host`` (host buffers in and out, copies inside the graph)
+    returns what ``step`` leaves on the device, also after the host inputs
+    change between replays."""
+    from locks.config import LocksConfig
+    from locks.hotpath import HotPath
+    cpu, sh, bt_cpu, lens = _case(2)
+    L, R = sh.n_layers, len(lens)
+    caches = [k.to(DEV) for k in cpu.kv_caches]
+    cfg = LocksConfig(budget_pages=sh.budget_pages, sink_pages=sh.sink_pages,
+                      window_pages=sh.window_pages)
+    hp = HotPath(caches, bt_cpu.to(DEV), cpu.seq_lens.to(DEV).clone(),
+                 n_kv=sh.n_kv, G=sh.G, scale=cpu.scale, cfg=cfg)
+    hp.build_all()
+    hp.enable_host_io()
+    hp.host_block_table.copy_(bt_cpu)
+    g = torch.Generator().manual_seed(3)
+    for trial, shorten in enumerate((0, 0, 33)):
+        q = torch.randn(L, R, sh.n_kv * sh.G, sh.d, generator=g).to(torch.bfloat16)
+        sl = cpu.seq_lens.clone()
+        sl[1] -= shorten                     # the lengths travel with the step too
+        hp.host_q.copy_(q)
+        hp.host_seq_lens.copy_(sl)
+        got = hp.step_host().clone()
+        hp.st.check_status()
+        # the same step through the device-side API
+        hp.q[:, :R].copy_(q.to(DEV))
+        hp.seq_lens.copy_(sl.to(DEV))
+        hp.derive()
+        want = hp.step_eager()[:, :R].cpu()
+        torch.cuda.synchronize()
+        assert torch.isfinite(got.float()).all()
+        assert torch.equal(got, want), trial
