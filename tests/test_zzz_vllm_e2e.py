@@ -52,23 +52,45 @@ def _run(mode, model_dir, out, budget=None):
         return json.load(fh), log
 
 
-def test_plugin_reproduces_stock_tokens_inside_vllm(tmp_path):
+@pytest.fixture(scope="module")
+def stock(tmp_path_factory):
+    """(model_dir, stock result): one stock engine for both tests."""
     pytest.importorskip("vllm")
-    model_dir = str(tmp_path / "tiny_llama")
+    tmp = tmp_path_factory.mktemp("vllm_e2e")
+    model_dir = str(tmp / "tiny_llama")
     os.makedirs(model_dir)
     with open(os.path.join(model_dir, "config.json"), "w") as fh:
         json.dump(CONFIG, fh)
-    stock, log = _run("stock", model_dir, str(tmp_path / "stock.json"))
-    if stock is None:
+    res, log = _run("stock", model_dir, str(tmp / "stock.json"))
+    if res is None:
         pytest.skip("stock vLLM did not start here: " + log[-300:])
-    got, log = _run("locks", model_dir, str(tmp_path / "locks.json"))
+    return model_dir, res, tmp
+
+
+def _check(got, log, want):
     assert got is not None, log[-3000:]
     assert "[locks] ACTIVE" in log and "[locks] sparse decode ACTIVE" in log, \
         log[-3000:]
     assert "[locks] state allocated" in log
     assert [len(x) for x in got["ids"]] == [40, 40]
-    assert got["ids"] == stock["ids"]
+    assert got["ids"] == want["ids"]
     # every page kept: the sparse decode is the dense attention up to bf16
     # rounding of a different summation order
-    for a, b in zip(got["logprobs"], stock["logprobs"]):
+    for a, b in zip(got["logprobs"], want["logprobs"]):
         assert max(abs(x - y) for x, y in zip(a, b)) < 0.05, (a[:5], b[:5])
+
+
+def test_plugin_reproduces_stock_tokens_inside_vllm(stock):
+    model_dir, want, tmp = stock
+    got, log = _run("locks", model_dir, str(tmp / "locks.json"))
+    _check(got, log, want)
+
+
+def test_plugin_inside_full_cuda_graphs(stock):
+    """Same, with CUDA graphs on: vLLM captures FULL decode graphs with the
+    LOCKS launches inside (the builder reports single-token-decode graph
+    support) and the 40 decode steps replay them."""
+    model_dir, want, tmp = stock
+    got, log = _run("locks-graph", model_dir, str(tmp / "locks_graph.json"))
+    _check(got, log, want)
+    assert "decode, FULL" in log, log[-2000:]

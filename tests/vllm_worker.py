@@ -2,7 +2,9 @@
 random-weight Llama (no tokenizer, no files beyond a generated config.json),
 with or without the LOCKS plugin, greedy-decoding two prompts.
 
-usage: vllm_worker.py <stock|locks> <model_dir> <out.json> [budget_pages]
+usage: vllm_worker.py <stock|locks|locks-graph> <model_dir> <out.json> [budget_pages]
+(``locks-graph``: CUDA graphs on, so the decode steps replay FULL graphs that
+hold the LOCKS launches; the other modes run eagerly)
 """
 import json
 import os
@@ -22,7 +24,7 @@ sys.path.insert(0, os.path.join(ROOT, "locks-kv_b200"))
 
 import torch  # noqa: E402
 
-if mode == "locks":
+if mode.startswith("locks"):
     from locks.backend.register import register
     register({"variant": "fast", "budget_pages": budget_pages, "sink_pages": 1,
               "window_pages": 2})
@@ -30,7 +32,7 @@ if mode == "locks":
 from vllm import LLM, SamplingParams  # noqa: E402
 
 llm = LLM(model=model_dir, load_format="dummy", skip_tokenizer_init=True,
-          dtype="bfloat16", max_model_len=8192, block_size=16, enforce_eager=True,
+          dtype="bfloat16", max_model_len=8192, block_size=16, enforce_eager=(mode != "locks-graph"),
           gpu_memory_utilization=0.08, enable_prefix_caching=False, seed=0,
           max_num_seqs=4, attention_backend="FLASH_ATTN")
 g = torch.Generator().manual_seed(1)
