@@ -188,32 +188,4 @@ __device__ __forceinline__ float bf16_bits_to_f32(uint32_t b16) {
 #endif  // __CUDACC__
 
 
-// ---- optional per-CTA wall-clock marks (debug builds only) -----------------------
-#ifdef LOCKS_TIMELINE
-#define TL_DECL(name) __device__ unsigned long long name[3][1024];
-#define TL_MARK(name, k)                                                        \
-    do {                                                                        \
-        if (threadIdx.x == 0) {                                                 \
-            const unsigned lin_ = blockIdx.x + gridDim.x * (blockIdx.y +        \
-                                  gridDim.y * blockIdx.z);                      \
-            if (lin_ < 1024) {                                                  \
-                unsigned long long t_;                                          \
-                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));          \
-                name[k][lin_] = t_;                                             \
-            }                                                                   \
-        }                                                                       \
-    } while (0)
-#define TL_GETTER(fn, name)                                                     \
-    extern "C" int fn(unsigned long long* out) {                                \
-        int e = (int)cudaMemcpyFromSymbol(out, name, sizeof(name));             \
-        static unsigned long long z_[3 * 1024];                                 \
-        cudaMemcpyToSymbol(name, z_, sizeof(name));                             \
-        return e;                                                               \
-    }
-#else
-#define TL_DECL(name)
-#define TL_MARK(name, k)
-#define TL_GETTER(fn, name)
-#endif
-
 }  // namespace locks

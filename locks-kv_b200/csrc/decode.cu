@@ -30,18 +30,6 @@ namespace cg = cooperative_groups;
 namespace locks {
 namespace {
 
-TL_DECL(g_dec_tl)
-#ifdef LOCKS_DEC_TIMING
-__device__ long long g_dec_ts[16];
-#define DEC_TS(i)                                                             \
-    do {                                                                      \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 &&          \
-            threadIdx.x == 0)                                                 \
-            g_dec_ts[i] = clock64();                                          \
-    } while (0)
-#else
-#define DEC_TS(i)
-#endif
 
 __device__ __forceinline__ uint32_t pack_f16x2(float a, float b) {
     const __half2 h = __floats2half2_rn(a, b);
@@ -159,16 +147,12 @@ decode_kernel(const DecParams p) {
     const int gid = lane >> 2, tig = lane & 3;
     const int G = p.G;
     const int64_t row = (int64_t)r * p.n_kv + kh;
-    DEC_TS(0);
-    TL_MARK(g_dec_tl, 0);
     pdl_trigger();            // the next layer's scorer may start prefetching
     // remote shared memory may be written once every CTA of the cluster runs;
     // this barrier costs nothing while the selector is still at work
     if (CLUSTER) cg::this_cluster().sync();
     const int seq_len = p.seq_lens[r];            // per-step constant
     pdl_wait();               // page tables / counts come from the selector
-    DEC_TS(1);
-    TL_MARK(g_dec_tl, 1);
 
     // Cluster mode deals the list out round-robin over all warps of the cluster
     // (entry j -> CTA (j / DW) % CL, warp j % DW): which entries a warp reads
@@ -219,9 +203,7 @@ decode_kernel(const DecParams p) {
                    nv[it % DSTAGES]);
     };
     if (!CLUSTER) load_window(0);
-    DEC_TS(2);
     for (int it = 0; it < DSTAGES && it < n_mine; ++it) issue_it(it);
-    DEC_TS(3);
 
     // ---- Q fragments (A operand), rows gid and gid+8 -------------------------
     uint32_t qa[8][4];
@@ -342,7 +324,6 @@ decode_kernel(const DecParams p) {
         }
     }
 
-    DEC_TS(4);
     // ---- combine the warps of the CTA --------------------------------------------
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
@@ -417,9 +398,7 @@ decode_kernel(const DecParams p) {
             cluster.map_shared_rank(&sm.xl[sp][g], d)[0] = Lsum;
         }
     }
-    DEC_TS(5);
     cluster.sync();                               // every CTA's pushes have landed
-    DEC_TS(6);
     for (int e = sp * per_e + tid; e < min((sp + 1) * per_e, n_el); e += DTHREADS) {
         const int g = e / HD, dd = e % HD;
         float mw[8], lw[8];
@@ -443,9 +422,6 @@ decode_kernel(const DecParams p) {
         p.out[(int64_t)r * p.out_stride_req + (int64_t)(kh * G + g) * HD + dd] =
             __float2bfloat16_rn(val);
     }
-    DEC_TS(7);
-    DEC_TS(8);
-    TL_MARK(g_dec_tl, 2);
 }
 
 struct MergeParams {
@@ -602,12 +578,6 @@ int check_kv(const char* who, const void* q, const void* k, const void* v,
 
 using namespace locks;
 
-TL_GETTER(locks_debug_dec_tl, locks::g_dec_tl)
-#ifdef LOCKS_DEC_TIMING
-extern "C" int locks_debug_dec_timing(long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_dec_ts, sizeof(long long) * 16);
-}
-#endif
 
 extern "C" int locks_decode_split(
     const void* q, int64_t q_stride_req, const void* k_cache,

@@ -430,16 +430,6 @@ struct MlaDecParams {
     int* status;
 };
 
-#ifdef LOCKS_MLA_TIMING
-__device__ long long g_mla_ts[64];
-#define MLA_TS(i)                                                             \
-    do {                                                                      \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && (i) < 64) \
-            g_mla_ts[i] = clock64();                                          \
-    } while (0)
-#else
-#define MLA_TS(i)
-#endif
 
 __global__ void __launch_bounds__(MD_THREADS) mla_decode_kernel(const MlaDecParams p) {
     extern __shared__ __align__(128) uint8_t md_raw[];
@@ -449,7 +439,6 @@ __global__ void __launch_bounds__(MD_THREADS) mla_decode_kernel(const MlaDecPara
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gid = lane >> 2, tig = lane & 3;
 
-    MLA_TS(0);
     if (tid == 0) {
         for (int s = 0; s < MD_STAGES; ++s) mbar_init(&sm.full[s], 1);
         mbar_fence_init();
@@ -503,7 +492,6 @@ __global__ void __launch_bounds__(MD_THREADS) mla_decode_kernel(const MlaDecPara
             }
         }
     };
-    MLA_TS(1);
     load_window(0);
     for (int k = 0; k < MD_STAGES && k < np; ++k) issue(k);
 
@@ -527,7 +515,6 @@ __global__ void __launch_bounds__(MD_THREADS) mla_decode_kernel(const MlaDecPara
     }
     __syncthreads();
 
-    MLA_TS(2);
     const int a_row = (lane & 7) + 8 * ((lane >> 3) & 1);
     const uint32_t q_addr = smem_u32(&sm.q[a_row][0]) + 16 * (lane >> 4);
     // K operand (non-transposed): token = (lane&7) + 8*((lane>>4)&1), col half (lane>>3)&1
@@ -544,9 +531,7 @@ __global__ void __launch_bounds__(MD_THREADS) mla_decode_kernel(const MlaDecPara
 
     for (int k = 0; k < np; ++k) {
         const int stage = k % MD_STAGES;
-        MLA_TS(4 + 4 * k);
         mbar_wait(&sm.full[stage], (uint32_t)((k / MD_STAGES) & 1), p.status);
-        MLA_TS(5 + 4 * k);
         __syncthreads();                       // zero-filled rows are visible too
         const int n_valid = nv[stage];
         if (n_valid > 0) {
@@ -573,7 +558,6 @@ __global__ void __launch_bounds__(MD_THREADS) mla_decode_kernel(const MlaDecPara
                 sr[gid + 8][2 * tig + 8] = s1[2]; sr[gid + 8][2 * tig + 9] = s1[3];
             }
             __syncthreads();
-            MLA_TS(6 + 4 * k);
 #pragma unroll
             for (int i = 0; i < 4; ++i) s0[i] = s1[i] = 0.f;
 #pragma unroll
@@ -643,7 +627,6 @@ __global__ void __launch_bounds__(MD_THREADS) mla_decode_kernel(const MlaDecPara
                 mma_bf16_k16(acc[2 * dp + 1], pl[0], pl[1], pl[2], pl[3], vb[2], vb[3]);
             }
         }
-        MLA_TS(7 + 4 * k);
         __syncthreads();                       // the stage is free again
         if (k + MD_STAGES < np) {
             if (((k + MD_STAGES) & 31) == 0) load_window(k + MD_STAGES);
@@ -691,9 +674,7 @@ __global__ void __launch_bounds__(MD_THREADS) mla_decode_kernel(const MlaDecPara
                      (e - d * per_e);
         *reinterpret_cast<float4*>(dst) = val;
     }
-    MLA_TS(60);
     cluster.sync();                              // every CTA's pushes have landed
-    MLA_TS(61);
     // merge weights once per (CTA, head): w[cc][h] = exp(m - M) / sum, lse[h]
     for (int h = tid; h < NH; h += MD_THREADS) {
         float M = -INFINITY;
@@ -718,7 +699,6 @@ __global__ void __launch_bounds__(MD_THREADS) mla_decode_kernel(const MlaDecPara
         for (int cc = 0; cc < CL; ++cc) o += sm.xm[cc][h] * sm.xacc[cc * per_e + el];
         p.out[((int64_t)row * NH + h) * LKV + d] = __float2bfloat16_rn(o);
     }
-    MLA_TS(62);
 }
 
 }  // namespace
@@ -726,11 +706,6 @@ __global__ void __launch_bounds__(MD_THREADS) mla_decode_kernel(const MlaDecPara
 
 using namespace locks;
 
-#ifdef LOCKS_MLA_TIMING
-extern "C" int locks_debug_mla_timing(long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, locks::g_mla_ts, sizeof(long long) * 64);
-}
-#endif
 
 extern "C" int locks_mla_build_factors(const void* cache, int64_t stride_block,
                                        int64_t stride_tok, void* records,

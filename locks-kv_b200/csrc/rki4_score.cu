@@ -146,18 +146,6 @@ __device__ __forceinline__ float quad_lse2(float t0, float t1, float t2,
     return mx + lg2_approx(sum);
 }
 
-TL_DECL(g_score_tl)
-#ifdef LOCKS_SCORE_TIMING
-__device__ long long g_score_ts[64];
-#define SC_TS(i)                                                              \
-    do {                                                                      \
-        if (blockIdx.x == 5 && blockIdx.y == 0 && blockIdx.z == 0 &&          \
-            threadIdx.x == 0 && (i) < 64)                                     \
-            g_score_ts[i] = clock64();                                        \
-    } while (0)
-#else
-#define SC_TS(i)
-#endif
 
 // GP = 4 : G <= 4, two pages per pass;  GP = 8 : G <= 8;  GP = 16 : G <= 16
 template <int GP>
@@ -166,8 +154,6 @@ rki4_score_kernel(const ScoreParams p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     ScoreSmem& sm = *reinterpret_cast<ScoreSmem*>(smem_raw);
 
-    SC_TS(0);
-    TL_MARK(g_score_tl, 0);
     const int kh = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int z = blockIdx.x, Z = gridDim.x, r = blockIdx.z;
@@ -240,7 +226,6 @@ rki4_score_kernel(const ScoreParams p) {
     };
     if (n_items > 0) issue(0, item_len(0), blk0);
     if (n_items > 1) issue(1, item_len(1), blk1);
-    SC_TS(1);
 
     // Everything above touches only per-step constants (block table, page
     // counts, summaries); q and the score buffers belong to the kernels before.
@@ -248,8 +233,6 @@ rki4_score_kernel(const ScoreParams p) {
     // prologue then overlaps the scorer's tail (it waits for the whole grid).
     pdl_trigger();
     pdl_wait();
-    SC_TS(2);
-    TL_MARK(g_score_tl, 1);
 
     // ---- per-head int8 round trip of q (overlaps the first copies) ----------
     for (int g = warp; g < G; g += NWARP) {
@@ -276,7 +259,6 @@ rki4_score_kernel(const ScoreParams p) {
         if (lane == 0) sm.qs[g] = qs;
     }
     __syncthreads();
-    SC_TS(3);
 
     // ---- A fragments of q.  Row gid holds head gid % GP (the group is repeated
     // when it is shorter than 8 rows); rows 8..15 are used only for GP = 16. ----
@@ -320,9 +302,7 @@ rki4_score_kernel(const ScoreParams p) {
         const int n = item_len(k);
         // block-table entries of the item that will reuse this stage
         const int next_blk = (k + 2 < n_items) ? bt_at(item_page0(k + 2)) : 0;
-        SC_TS(4 + 2 * k);
         mbar_wait(&sm.full[warp][stage], (uint32_t)((k >> 1) & 1), p.status);
-        SC_TS(5 + 2 * k);
         const uint8_t* crec = &sm.rec[warp][stage][0][0];
 
         // mu . q for the chunk's 8 pages: column (n) = page slot gid
@@ -480,8 +460,6 @@ rki4_score_kernel(const ScoreParams p) {
         if (k + 2 < n_items) issue(stage, item_len(k + 2), next_blk);
     }
 
-    SC_TS(30);
-    TL_MARK(g_score_tl, 2);
     if (p.hmax != nullptr && tig == 0) {
 #pragma unroll
         for (int h = 0; h < NR; ++h) {
@@ -496,12 +474,6 @@ rki4_score_kernel(const ScoreParams p) {
 }  // namespace
 }  // namespace locks
 
-TL_GETTER(locks_debug_score_tl, locks::g_score_tl)
-#ifdef LOCKS_SCORE_TIMING
-extern "C" int locks_debug_score_timing(long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, locks::g_score_ts, sizeof(long long) * 64);
-}
-#endif
 
 extern "C" int locks_rki4_score_bt(
     const void* q, int64_t q_stride_req, const void* records_layer,

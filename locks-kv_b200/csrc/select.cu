@@ -118,18 +118,6 @@ struct SelParams {
     KvAppend app;       // optional: the new token's K/V store of this layer (key != null)
 };
 
-TL_DECL(g_sel_tl)
-#ifdef LOCKS_SEL_TIMING
-__device__ long long g_sel_ts[32];
-#define SEL_TS(i)                                                          \
-    do {                                                                   \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 &&       \
-            threadIdx.x == 0)                                              \
-            g_sel_ts[i] = clock64();                                       \
-    } while (0)
-#else
-#define SEL_TS(i)
-#endif
 
 constexpr int KEYS_PER_CTA = 16384;               // shared-memory key capacity
 // single-CTA selection: the latency-bound radix / compaction steps run on a few
@@ -272,16 +260,10 @@ __device__ __forceinline__ void combine_nrm_groups(
                 v[u][g] = __ldcg(&sh[(int64_t)min(g, G - 1) * MP + i]);
         }
         if (first) {
-            SEL_TS(23);
             sync_hm();
-            SEL_TS(24);
 #pragma unroll
             for (int g = 0; g < GT; ++g) hm[g] = hm_sh[min(g, G - 1)];
             first = false;
-#ifdef LOCKS_SEL_TIMING
-            if (v[0][0] == 12345.f) hm[0] = 0.f;   // wait for the loads (timing only)
-#endif
-            SEL_TS(25);
         }
 #pragma unroll
         for (int u = 0; u < CB; ++u) {
@@ -360,8 +342,6 @@ topb_kernel(const SelParams p) {
     extern __shared__ __align__(16) uint32_t keys[];   // keys of my page slice
     cg::cluster_group cluster = cg::this_cluster();
 
-    SEL_TS(0);
-    TL_MARK(g_sel_tl, 0);
     pdl_trigger();               // the decode may be scheduled; it waits for us
     const int c_phys = blockIdx.x, CL_phys = gridDim.x;   // rank / size of cluster
     const int kh = blockIdx.y, r = blockIdx.z;
@@ -411,8 +391,6 @@ topb_kernel(const SelParams p) {
     // this barrier costs nothing while the scorer is still at work
     if (CL_phys > 1) cluster.sync();
     pdl_wait();                  // score_h / hmax / score come from the scorer
-    SEL_TS(22);
-    TL_MARK(g_sel_tl, 1);
 
     // The page classes are folded into the keys: 0 = not a page of the row,
     // 0xFFFFFFFF = always kept (sink / recent pages, short rows), anything
@@ -453,14 +431,12 @@ topb_kernel(const SelParams p) {
                 if (tid < G) sm.hm_sh[tid] = sm.xmax[tid];
             }
         }
-        SEL_TS(20);
         // the barrier below publishes hm_sh; the scorer's keys are re-armed
         // further down, behind a cluster barrier every CTA passes after this read
         auto sync_hm = [&]() { __syncthreads(); };
         LOCKS_DISPATCH_CB(cgpw, (combine_nrm_groups<GT, CBW>(
             sh, score, kdst, sm.hm_sh, G, MP, cs0, cn_loc, n_comb, cg_beg, cg_end,
             lane, sync_hm, fin_key)));
-        SEL_TS(21);
     } else if (p.combine == LOCKS_COMBINE_MAX && n_comb > 0) {
         const float* sh = p.score_h + row * (int64_t)G * MP;
         for (int grp = cg_beg; grp < cg_end; ++grp) {
@@ -510,7 +486,6 @@ topb_kernel(const SelParams p) {
         // behind the exchange of the compaction totals below
         if (rearm && CL_phys == 1 && tid < G) p.hmax[row * G + tid] = 0u;
     }
-    SEL_TS(1);
 
     // ============ selection over keys[0, n_loc) (local index j = page - s0) ======
     // The per-key loops run on all warps, 4 consecutive keys per lane; the digit
@@ -544,12 +519,9 @@ topb_kernel(const SelParams p) {
                                       (lane & 3)], 1);
                 }
             }
-            SEL_TS(2 + 4 * pass);
             __syncthreads();
-            SEL_TS(3 + 4 * pass);
             if (CL == 1) {
                 if (warp < AW) find_digit_active<true>(sm, h4, nb, k);
-                SEL_TS(4 + 4 * pass);
                 __syncthreads();
             } else {
                 if (warp < AW) push_bins(h4, nb, tot0);
@@ -570,12 +542,10 @@ topb_kernel(const SelParams p) {
             mask |= dmask << shift;
             // the bin is taken whole: no finer digit and no tie rule needed
             whole_bin = (sm.sh_i2 == k);
-            SEL_TS(5 + 4 * pass);
         }
         if (whole_bin) { tau_key = prefix ? prefix - 1u : 0u; quota = 0; }
         else { tau_key = prefix; quota = k; }
     }
-    SEL_TS(13);
 
     // ---- 3. keep flags + ascending compaction.  Warp w owns a contiguous run of
     // keys and walks it 128 keys at a time.
@@ -597,7 +567,6 @@ topb_kernel(const SelParams p) {
         c_sure += __shfl_xor_sync(0xffffffffu, c_sure, o);
     }
     if (lane == 0) { sm.wtot[warp] = c_eq; sm.wtot2[warp] = c_sure; }
-    SEL_TS(15);
     __syncthreads();
     // every warp derives all warps' tie ranks and output slots by itself
     const int e_w = (lane < NW) ? sm.wtot[lane] : 0;
@@ -641,7 +610,6 @@ topb_kernel(const SelParams p) {
     int pos = pos_before + __shfl_sync(0xffffffffu, kinc - k_w, warp);
     int eqr = eq_before + __shfl_sync(0xffffffffu, einc - e_w, warp);
     const int cnt = (CL > 1) ? cnt_all : __shfl_sync(0xffffffffu, kinc, 31);
-    SEL_TS(17);
     for (int it = w0; it < w1; it += 128) {
         const int base = it + 4 * lane;
         const uint4 kv = *reinterpret_cast<const uint4*>(&keys[base]);
@@ -692,20 +660,11 @@ topb_kernel(const SelParams p) {
         if (!owner && c_phys == CL_phys - 1 && tid < p.app.head_dim)
             kv_append_elem(p.app, r, kh, tid);
     }
-    SEL_TS(18);
-    SEL_TS(19);
-    TL_MARK(g_sel_tl, 2);
 }
 
 }  // namespace
 }  // namespace locks
 
-TL_GETTER(locks_debug_sel_tl, locks::g_sel_tl)
-#ifdef LOCKS_SEL_TIMING
-extern "C" int locks_debug_sel_timing(long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, locks::g_sel_ts, sizeof(long long) * 32);
-}
-#endif
 
 extern "C" int locks_derive_page_params(
     const int32_t* seq_lens, int n_req, int page, int window_pages,

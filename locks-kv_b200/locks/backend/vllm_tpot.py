@@ -1,6 +1,6 @@
 """End-to-end decode time per token inside vLLM, stock against the LOCKS plugin.
 
-usage: python tests/vllm_tpot.py <stock|locks> [context_tokens=130560] [decode_tokens=513]
+usage: python locks-kv_b200/locks/backend/vllm_tpot.py <stock|locks> [context_tokens=130560] [decode_tokens=513]
 
 Starts one vLLM engine (in-process engine core, CUDA graphs on) on a
 Llama-3.1-8B-shaped model with random weights (32 layers, 32 query / 8 KV heads
@@ -10,8 +10,7 @@ times greedy generation of 1 token (prefill, best of two) and of
 over ``decode_tokens - 1``.  ``stock`` leaves vLLM's own backend choice alone;
 ``locks`` applies ``register()`` (budget 128 pages + 1 sink + 8 recent, the
 benchmark's config 1) and starts vLLM on the FlashAttention backend the plugin
-replaces.  Prints one ``RESULT {json}`` line.  Not a test: the file name keeps
-it out of collection.
+replaces.  Prints one ``RESULT {json}`` line.
 """
 import json
 import os
@@ -28,8 +27,8 @@ mode = sys.argv[1]
 ctx = int(sys.argv[2]) if len(sys.argv) > 2 else 130560
 n_tok = int(sys.argv[3]) if len(sys.argv) > 3 else 513
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-sys.path.insert(0, os.path.join(ROOT, "locks-kv_b200"))
+PKG_PARENT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, PKG_PARENT)
 
 import torch  # noqa: E402
 
