@@ -229,7 +229,11 @@ int locks_rki4_build_slots(const void* const* k_layers, int64_t k_stride_block,
  * records and (NB, n_kv, 8) tags; when the row lands on token page-1 of its block
  * the block's summaries are rebuilt from the cache in the same launch -- the
  * arithmetic of locks_rki4_build (selection/rki4_build.py:45-225), which replaces
- * the separate tail refresh of selection/rki4_tailgraph.py. */
+ * the separate tail refresh of selection/rki4_tailgraph.py.  A launch of several
+ * rows may hold more than one row of the same page (a prefill chunk, speculative
+ * tokens): with n_tok > 1 all rows are stored by a first launch and the pages
+ * they completed are summarised by a second one behind it, so a summary never
+ * reads a row a sibling has yet to store. */
 int locks_kv_write(const void* key, int64_t k_row_stride, int64_t k_head_stride,
                    const void* val, int64_t v_row_stride, int64_t v_head_stride,
                    void* k_cache, void* v_cache, int64_t kv_stride_block,
@@ -346,7 +350,10 @@ int locks_cp_exchange(void* const* peers, int world, int rank, const void* paylo
  *     LOCKS_ERR_SIZE is returned and nothing is launched;
  *   - the first call on a device resolves the array's device address (a CUDA
  *     runtime query, not a stream operation): make that first call before any
- *     stream capture begins on that device, with the device current;
+ *     stream capture begins on that device, with the device current; the
+ *     address is kept for the life of the device's primary context (after a
+ *     cudaDeviceReset the library must be reloaded), and the look-up is
+ *     serialised between host threads;
  *   - all calls share the one array and it keeps the previous call's contents;
  *     nothing in it has to start at zero (only partials written by the current
  *     call are read back), but two calls whose kernels overlap on the GPU --

@@ -22,6 +22,7 @@
 // (m, l, O) through distributed shared memory and write the normalised bf16
 // output row directly: no partial buffers in HBM and no merge launch.
 #include <cooperative_groups.h>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -758,8 +759,11 @@ constexpr int NOALLOC_MAX_ROWS = LOCKS_NOALLOC_MAX_ROWS;   // n_req*n_kv*split*G
 constexpr size_t NOALLOC_FLOATS = (size_t)NOALLOC_MAX_ROWS * (HD + 2);
 static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_FLOATS];
 // device address of the array, per device (the symbol itself is only a
-// host-side handle and must never be passed to a kernel)
+// host-side handle and must never be passed to a kernel).  An address stays
+// valid for the life of the device's primary context; the look-up is serialised
+// so that first calls from several host threads do not race.
 float* g_noalloc_ptr[64] = {nullptr};
+std::mutex g_noalloc_mu;
 }  // namespace
 }  // namespace locks
 
@@ -796,15 +800,20 @@ extern "C" int locks_decode_split_noalloc(
     LOCKS_REQUIRE(ce == cudaSuccess && dev >= 0 && dev < 64, LOCKS_ERR_LAUNCH,
                   "locks_decode_split_noalloc: cudaGetDevice: %s",
                   cudaGetErrorString(ce));
-    if (g_noalloc_ptr[dev] == nullptr) {
-        float* ptr = nullptr;
-        ce = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
-        LOCKS_REQUIRE(ce == cudaSuccess && ptr != nullptr, LOCKS_ERR_LAUNCH,
-                      "locks_decode_split_noalloc: cudaGetSymbolAddress: %s",
-                      cudaGetErrorString(ce));
-        g_noalloc_ptr[dev] = ptr;
+    float* base = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mu);
+        if (g_noalloc_ptr[dev] == nullptr) {
+            float* ptr = nullptr;
+            ce = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr),
+                                      g_noalloc_scratch);
+            LOCKS_REQUIRE(ce == cudaSuccess && ptr != nullptr, LOCKS_ERR_LAUNCH,
+                          "locks_decode_split_noalloc: cudaGetSymbolAddress: %s",
+                          cudaGetErrorString(ce));
+            g_noalloc_ptr[dev] = ptr;
+        }
+        base = g_noalloc_ptr[dev];
     }
-    float* base = g_noalloc_ptr[dev];
     float* m_part = base;
     float* l_part = base + NOALLOC_MAX_ROWS;
     float* acc_part = base + 2 * (size_t)NOALLOC_MAX_ROWS;

@@ -13,6 +13,10 @@
 //            barrier (the stores above are visible to the CTA) warps 0-3 run
 //            rki4_build_one over the page's heads, reading the 15 older tokens
 //            and the one just stored from the cache.
+// A launch that carries SEVERAL rows (a prefill chunk, speculative tokens) may
+// hold rows 14 and 15 of one page in different CTAs, and CTAs are not ordered:
+// such a launch runs phase 1 for all rows first and phase 2 as a second launch
+// of the same kernel behind it, so the builder always reads a complete page.
 // The page summary is then valid in the same step its page is completed, inside
 // whatever CUDA graph holds the KV write, with no host-side refresh decision.
 // The build is a Jacobi eigen-solve of about 45 us per head, so a write that
@@ -34,6 +38,7 @@ struct KvWriteParams {
     uint8_t* records;                              // this layer's (NB, n_kv, 832) or null
     __nv_bfloat16* tags;
     int n_kv;
+    int phases;                                    // bit 0: store the rows, bit 1: build
 };
 
 __global__ void __launch_bounds__(KW_THREADS) kv_write_kernel(const KvWriteParams p) {
@@ -45,9 +50,10 @@ __global__ void __launch_bounds__(KW_THREADS) kv_write_kernel(const KvWriteParam
     const int t = (int)(s % p.a.page);
     if (blk >= p.a.num_blocks) return;
     const int tid = threadIdx.x;
-    for (int i = tid; i < p.n_kv * BUILD_HD; i += KW_THREADS)
-        kv_append_elem(p.a, r, i / BUILD_HD, i % BUILD_HD);
-    if (p.records == nullptr || t != p.a.page - 1) return;
+    if (p.phases & 1)
+        for (int i = tid; i < p.n_kv * BUILD_HD; i += KW_THREADS)
+            kv_append_elem(p.a, r, i / BUILD_HD, i % BUILD_HD);
+    if (!(p.phases & 2) || p.records == nullptr || t != p.a.page - 1) return;
     __syncthreads();                   // the page's last row is in the cache
     const int warp = tid >> 5, lane = tid & 31;
     if (warp >= KW_BUILD_WARPS) return;
@@ -111,7 +117,17 @@ extern "C" int locks_kv_write(
     p.records = static_cast<uint8_t*>(records_layer);
     p.tags = static_cast<__nv_bfloat16*>(tags_layer);
     p.n_kv = n_kv;
-    kv_write_kernel<<<n_tok, KW_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (n_tok == 1 || records_layer == nullptr) {
+        p.phases = 3;
+        kv_write_kernel<<<n_tok, KW_THREADS, 0, s>>>(p);
+    } else {
+        // several rows: every row is in the cache before any page is summarised
+        p.phases = 1;
+        kv_write_kernel<<<n_tok, KW_THREADS, 0, s>>>(p);
+        p.phases = 2;
+        kv_write_kernel<<<n_tok, KW_THREADS, 0, s>>>(p);
+    }
     if (records_layer) pdl_break();    // the scorer prefetches summaries before its wait
     return check_launch("locks_kv_write");
 }

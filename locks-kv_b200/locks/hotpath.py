@@ -191,15 +191,24 @@ class HotPath:
         the token index is the current length; its slot comes from the block
         table; lengths grow by one and the page parameters follow; each layer
         rotates and stores the token, scores, selects and decodes.  Summaries
-        of the pages the PREVIOUS step completed are built on a forked branch
-        meanwhile -- such a page stays inside the recent window for
-        ``window_pages`` more pages, so no step scores it before the join at
-        the end of this one."""
+        of the pages the PREVIOUS step completed are built first.  With a
+        recent window of two pages or more such a page is still inside the
+        window during this step (no layer scores it), so the build runs on a
+        forked branch and is joined at the end of the step.  With a window of
+        one page (the default of ``LocksConfig``) the page completed by the
+        previous step is scored by THIS step, so the build stays on the main
+        stream in front of the first scorer -- the order the reference keeps
+        (tail build before the forward of the step, ``backend/builder.py:
+        1230-1245``)."""
         cur = torch.cuda.current_stream()
         append_advance(self.st, self.seq_lens, self.block_table, self.n_req,
                        self.slot, self.slot_prev, self.pos)
-        self._side.wait_stream(cur)
-        with torch.cuda.stream(self._side):
+        forked = self.st.window_pages >= 2
+        if forked:
+            self._side.wait_stream(cur)
+            with torch.cuda.stream(self._side):
+                rki4_build_slots(self.st, self.K_layers, self.slot_prev)
+        else:
             rki4_build_slots(self.st, self.K_layers, self.slot_prev)
         st, R = self.st, self.n_req
         for l, kvc in enumerate(self.kv_caches):
@@ -215,7 +224,8 @@ class HotPath:
             _runtime.decode_dispatch(q, kvc, self.block_table, self.seq_lens, st,
                                      self.out[l], self.vsources[l], self.scale,
                                      self.cfg)
-        cur.wait_stream(self._side)
+        if forked:
+            cur.wait_stream(self._side)
 
     def append_step(self) -> torch.Tensor:
         """Replay the captured append-and-attend step (captured on first use;

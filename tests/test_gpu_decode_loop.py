@@ -24,10 +24,10 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-def _case(extra):
+def _case(extra, window_pages=2):
     from locks import synth
     shape = synth.GqaShape(n_layers=2, n_kv=2, G=4, budget_pages=6,
-                           sink_pages=1, window_pages=2, n_needles=2)
+                           sink_pages=1, window_pages=window_pages, n_needles=2)
     lens = [100, 333]
     page = shape.page
     npg = [-(-s // page) for s in lens]
@@ -45,12 +45,13 @@ def _case(extra):
     return cpu, shape, bt, lens
 
 
-@pytest.mark.parametrize("fuse_write", [True, False])
-def test_append_loop_leaves_the_state_of_a_fresh_build(fuse_write):
+@pytest.mark.parametrize("fuse_write,window_pages",
+                         [(True, 2), (False, 2), (True, 1)])
+def test_append_loop_leaves_the_state_of_a_fresh_build(fuse_write, window_pages):
     from locks.config import LocksConfig
     from locks.hotpath import HotPath
     steps, extra = 40, 3
-    cpu, sh, bt_cpu, lens = _case(extra)
+    cpu, sh, bt_cpu, lens = _case(extra, window_pages)
     page, L, R = sh.page, sh.n_layers, len(lens)
     caches = [k.to(DEV) for k in cpu.kv_caches]
     bt = bt_cpu.to(DEV)
@@ -69,12 +70,33 @@ def test_append_loop_leaves_the_state_of_a_fresh_build(fuse_write):
     hp.enable_append(cs.to(DEV), neox=True, fuse_write=fuse_write)
     new_k = torch.randn(steps, L, R, sh.n_kv, sh.d, generator=g).to(torch.bfloat16)
     new_v = torch.randn(steps, L, R, sh.n_kv, sh.d, generator=g).to(torch.bfloat16)
+    n_checked = 0
     for s in range(steps):
         hp.new_k.copy_(new_k[s])
         hp.new_v.copy_(new_v[s])
         hp.append_step()
+        # a one-page window scores the page the PREVIOUS step completed in this
+        # very step: its summary must be in place before the first scorer.
+        # Compare such steps with a fresh driver built from the caches as they are.
+        if window_pages == 1 and s >= 1 and any(
+                (n + s - 1) % page == page - 1 for n in lens):
+            torch.cuda.synchronize()
+            chk = HotPath(caches, bt, hp.seq_lens.clone(), n_kv=sh.n_kv, G=sh.G,
+                          scale=cpu.scale, cfg=cfg)
+            chk.build_all()
+            chk.derive()
+            for l in range(L):
+                chk.q[l, :R].copy_(hp.q[l, :R])
+            chk.step_eager()
+            torch.cuda.synchronize()
+            assert torch.equal(hp.st.page_cnt, chk.st.page_cnt), s
+            assert torch.equal(hp.st.page_table, chk.st.page_table), s
+            np.testing.assert_allclose(t2n(hp.out[:, :R]), t2n(chk.out[:, :R]),
+                                       atol=2e-2, rtol=1e-2)
+            n_checked += 1
     torch.cuda.synchronize()
     hp.st.check_status()
+    assert window_pages != 1 or n_checked >= 2
     assert t2n(hp.seq_lens).tolist() == [n + steps for n in lens]
     out_loop = hp.out[:, :R].clone()
     tab_loop, cnt_loop = hp.st.page_table.clone(), hp.st.page_cnt.clone()

@@ -99,6 +99,42 @@ def test_page_completion_builds_the_summary():
     assert int(st.pp_rec[0, 2].abs().sum()) == 0
 
 
+def test_rows_of_one_page_in_one_launch():
+    """A launch that stores SEVERAL rows of the same page (a prefill chunk): the
+    CTA of the row that completes the page must not summarise it before its
+    siblings' rows are in the cache.  All 16 rows of a block arrive in one
+    launch (the completing row first, so that its CTA is scheduled first); the
+    summary equals a stand-alone build of the final cache."""
+    from locks.attention import rope_and_cache
+    from locks.selection import Rki4State, rki4_build_bulk
+    n_kv, G, d, page, NB = 8, 4, 128, 16, 5
+    g = torch.Generator().manual_seed(314)
+    cache = torch.zeros(NB, 2, page, n_kv, d, dtype=torch.bfloat16, device=DEV)
+
+    def state():
+        return Rki4State(DEV, num_layers=1, num_blocks=NB, n_kv=n_kv, G=G,
+                         head_dim=d, page=page, max_reqs=1, max_pages=NB)
+    for trial in range(8):
+        st = state()
+        cache.zero_()
+        key = torch.randn(page, n_kv, d, generator=g).to(torch.bfloat16).to(DEV)
+        val = torch.randn(page, n_kv, d, generator=g).to(torch.bfloat16).to(DEV)
+        order = [15] + list(range(15))
+        slots = torch.tensor([3 * page + t for t in order], dtype=torch.int64,
+                             device=DEV)
+        rope_and_cache(key, val, cache, slots, None, None, st=st, lidx=0)
+        ref = state()
+        bt = torch.tensor([[3]], dtype=torch.int32, device=DEV)
+        settled = torch.tensor([page], dtype=torch.int32, device=DEV)
+        rki4_build_bulk(ref, [cache[:, 0]], bt, settled, 1, 1)
+        torch.cuda.synchronize()
+        for r, t in enumerate(order):
+            assert torch.equal(cache[3, 0, t], key[r])
+        assert torch.equal(st.pp_rec[0, 3], ref.pp_rec[0, 3]), trial
+        assert torch.equal(st.pp_tag[0, 3].view(torch.int16),
+                           ref.pp_tag[0, 3].view(torch.int16))
+
+
 def test_slot_driven_build_matches_block_list_build():
     """locks_rki4_build_slots builds exactly the blocks whose last slot was
     written this step, in every layer, and leaves the others alone."""
