@@ -110,6 +110,18 @@ int locks_derive_page_params(const int32_t* seq_lens, int n_req, int page,
                              double budget, int32_t* n_pages, int32_t* n_sel_hi,
                              int32_t* b_fix, locks_stream_t stream);
 
+/* The same with one page budget PER REQUEST: budget_pages_req[r] > 0 is request
+ * r's budget in pages, <= 0 falls back to the fraction `budget`.  The reference
+ * keeps b_fix per request (the selector reads b_fix[r], selection/select.py:
+ * 92-105) but derives it from one engine-wide constant (BUDGET_ABS,
+ * selection/select.py:29-58); a continuous batch whose requests carry their own
+ * budgets passes them here. */
+int locks_derive_page_params_req(const int32_t* seq_lens, int n_req, int page,
+                                 int window_pages, int sink_pages,
+                                 const int32_t* budget_pages_req, double budget,
+                                 int32_t* n_pages, int32_t* n_sel_hi,
+                                 int32_t* b_fix, locks_stream_t stream);
+
 /* ---- Stage A.2: page score ------------------------------------------------
  * score_h[r,kh,g,p] = logsumexp_t scale*(cs[t]*sum_r C8[t,r]*qt[g,r] + mu.q)
  * for p < n_sel_hi[r], with q round-tripped through per-head int8 and the page
@@ -258,6 +270,17 @@ int locks_append_advance(int32_t* seq_lens, const int32_t* block_table,
                          double budget, int64_t* slot_mapping, int64_t* slot_prev,
                          int64_t* positions, int32_t* n_pages, int32_t* n_sel_hi,
                          int32_t* b_fix, locks_stream_t stream);
+
+/* locks_append_advance with per-request page budgets (see
+ * locks_derive_page_params_req). */
+int locks_append_advance_req(int32_t* seq_lens, const int32_t* block_table,
+                             int64_t bt_stride, int bt_width, int n_req, int page,
+                             int window_pages, int sink_pages,
+                             const int32_t* budget_pages_req, double budget,
+                             int64_t* slot_mapping, int64_t* slot_prev,
+                             int64_t* positions, int32_t* n_pages,
+                             int32_t* n_sel_hi, int32_t* b_fix,
+                             locks_stream_t stream);
 
 /* ---- Selection that also carries the layer's KV write -------------------------
  * The store of locks_kv_write (same arguments, same arithmetic, no summary

@@ -36,8 +36,19 @@ constexpr int SEL_THREADS = 512;
 constexpr int SEL_WARPS = 32;                // capacity of the per-warp arrays
 constexpr int MAX_G = 16;
 
+// static budget of one request: a page count (its own entry of budget_req when
+// the caller passes per-request budgets, else the engine-wide budget_pages)
+// clamped to [1, s], or the fraction `budget` of the s selectable pages rounded
+// up in fp64 (reference selection/select.py:36-45)
+__device__ __forceinline__ int budget_of(int s, int budget_pages, double budget) {
+    if (budget_pages > 0) return max(min(budget_pages, max(s, 1)), 1);
+    const double bf = ceil((double)s * budget);
+    return min(max((int)bf, 1), max(s, 1));
+}
+
 __global__ void derive_kernel(const int32_t* __restrict__ seq_lens, int n_req,
                               int page, int window, int sink, int budget_pages,
+                              const int32_t* __restrict__ budget_req,
                               double budget, int32_t* __restrict__ n_pages,
                               int32_t* __restrict__ n_sel_hi,
                               int32_t* __restrict__ b_fix) {
@@ -47,16 +58,9 @@ __global__ void derive_kernel(const int32_t* __restrict__ seq_lens, int n_req,
     const int npg = (sl + page - 1) / page;
     const int nsh = npg - window;
     const int s = nsh - sink;
-    int b;
-    if (budget_pages > 0) {
-        b = max(min(budget_pages, max(s, 1)), 1);
-    } else {
-        const double bf = ceil((double)s * budget);
-        b = min(max((int)bf, 1), max(s, 1));
-    }
     n_pages[i] = npg;
     n_sel_hi[i] = nsh;
-    b_fix[i] = b;
+    b_fix[i] = budget_of(s, budget_req ? budget_req[i] : budget_pages, budget);
 }
 
 // One decode step's bookkeeping for every request row, then its page parameters:
@@ -66,7 +70,8 @@ __global__ void derive_kernel(const int32_t* __restrict__ seq_lens, int n_req,
 __global__ void advance_kernel(int32_t* __restrict__ seq_lens,
                                const int32_t* __restrict__ block_table,
                                int64_t bt_stride, int bt_width, int n_req, int page,
-                               int window, int sink, int budget_pages, double budget,
+                               int window, int sink, int budget_pages,
+                               const int32_t* __restrict__ budget_req, double budget,
                                int64_t* __restrict__ slot,
                                int64_t* __restrict__ slot_prev,
                                int64_t* __restrict__ pos,
@@ -90,16 +95,9 @@ __global__ void advance_kernel(int32_t* __restrict__ seq_lens,
     const int npg = (sl + page - 1) / page;
     const int nsh = npg - window;
     const int s = nsh - sink;
-    int b;
-    if (budget_pages > 0) {
-        b = max(min(budget_pages, max(s, 1)), 1);
-    } else {
-        const double bf = ceil((double)s * budget);
-        b = min(max((int)bf, 1), max(s, 1));
-    }
     n_pages[i] = npg;
     n_sel_hi[i] = nsh;
-    b_fix[i] = b;
+    b_fix[i] = budget_of(s, budget_req ? budget_req[i] : budget_pages, budget);
 }
 
 struct SelParams {
@@ -666,10 +664,10 @@ topb_kernel(const SelParams p) {
 }  // namespace locks
 
 
-extern "C" int locks_derive_page_params(
+static int derive_impl(
     const int32_t* seq_lens, int n_req, int page, int window_pages,
-    int sink_pages, int budget_pages, double budget, int32_t* n_pages,
-    int32_t* n_sel_hi, int32_t* b_fix, locks_stream_t stream) {
+    int sink_pages, int budget_pages, const int32_t* budget_req, double budget,
+    int32_t* n_pages, int32_t* n_sel_hi, int32_t* b_fix, locks_stream_t stream) {
     using namespace locks;
     LOCKS_REQUIRE(seq_lens && n_pages && n_sel_hi && b_fix, LOCKS_ERR_ARG,
                   "locks_derive_page_params: null pointer argument");
@@ -678,17 +676,37 @@ extern "C" int locks_derive_page_params(
     if (n_req == 0) return LOCKS_OK;
     derive_kernel<<<(n_req + 127) / 128, 128, 0,
                     static_cast<cudaStream_t>(stream)>>>(
-        seq_lens, n_req, page, window_pages, sink_pages, budget_pages, budget,
-        n_pages, n_sel_hi, b_fix);
+        seq_lens, n_req, page, window_pages, sink_pages, budget_pages, budget_req,
+        budget, n_pages, n_sel_hi, b_fix);
     pdl_break();
     return check_launch("locks_derive_page_params");
 }
 
-extern "C" int locks_append_advance(
+extern "C" int locks_derive_page_params(
+    const int32_t* seq_lens, int n_req, int page, int window_pages,
+    int sink_pages, int budget_pages, double budget, int32_t* n_pages,
+    int32_t* n_sel_hi, int32_t* b_fix, locks_stream_t stream) {
+    return derive_impl(seq_lens, n_req, page, window_pages, sink_pages,
+                       budget_pages, nullptr, budget, n_pages, n_sel_hi, b_fix,
+                       stream);
+}
+
+extern "C" int locks_derive_page_params_req(
+    const int32_t* seq_lens, int n_req, int page, int window_pages,
+    int sink_pages, const int32_t* budget_pages_req, double budget,
+    int32_t* n_pages, int32_t* n_sel_hi, int32_t* b_fix, locks_stream_t stream) {
+    LOCKS_REQUIRE(budget_pages_req != nullptr, LOCKS_ERR_ARG,
+                  "locks_derive_page_params_req: null per-request budget array");
+    return derive_impl(seq_lens, n_req, page, window_pages, sink_pages, 0,
+                       budget_pages_req, budget, n_pages, n_sel_hi, b_fix, stream);
+}
+
+static int advance_impl(
     int32_t* seq_lens, const int32_t* block_table, int64_t bt_stride, int bt_width,
     int n_req, int page, int window_pages, int sink_pages, int budget_pages,
-    double budget, int64_t* slot_mapping, int64_t* slot_prev, int64_t* positions,
-    int32_t* n_pages, int32_t* n_sel_hi, int32_t* b_fix, locks_stream_t stream) {
+    const int32_t* budget_req, double budget, int64_t* slot_mapping,
+    int64_t* slot_prev, int64_t* positions, int32_t* n_pages, int32_t* n_sel_hi,
+    int32_t* b_fix, locks_stream_t stream) {
     using namespace locks;
     LOCKS_REQUIRE(seq_lens && block_table && slot_mapping && slot_prev && positions &&
                       n_pages && n_sel_hi && b_fix,
@@ -699,10 +717,35 @@ extern "C" int locks_append_advance(
     if (n_req == 0) return LOCKS_OK;
     advance_kernel<<<(n_req + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
         seq_lens, block_table, bt_stride, bt_width, n_req, page, window_pages,
-        sink_pages, budget_pages, budget, slot_mapping, slot_prev, positions, n_pages,
-        n_sel_hi, b_fix);
+        sink_pages, budget_pages, budget_req, budget, slot_mapping, slot_prev,
+        positions, n_pages, n_sel_hi, b_fix);
     pdl_break();
     return check_launch("locks_append_advance");
+}
+
+extern "C" int locks_append_advance(
+    int32_t* seq_lens, const int32_t* block_table, int64_t bt_stride, int bt_width,
+    int n_req, int page, int window_pages, int sink_pages, int budget_pages,
+    double budget, int64_t* slot_mapping, int64_t* slot_prev, int64_t* positions,
+    int32_t* n_pages, int32_t* n_sel_hi, int32_t* b_fix, locks_stream_t stream) {
+    return advance_impl(seq_lens, block_table, bt_stride, bt_width, n_req, page,
+                        window_pages, sink_pages, budget_pages, nullptr, budget,
+                        slot_mapping, slot_prev, positions, n_pages, n_sel_hi, b_fix,
+                        stream);
+}
+
+extern "C" int locks_append_advance_req(
+    int32_t* seq_lens, const int32_t* block_table, int64_t bt_stride, int bt_width,
+    int n_req, int page, int window_pages, int sink_pages,
+    const int32_t* budget_pages_req, double budget, int64_t* slot_mapping,
+    int64_t* slot_prev, int64_t* positions, int32_t* n_pages, int32_t* n_sel_hi,
+    int32_t* b_fix, locks_stream_t stream) {
+    LOCKS_REQUIRE(budget_pages_req != nullptr, LOCKS_ERR_ARG,
+                  "locks_append_advance_req: null per-request budget array");
+    return advance_impl(seq_lens, block_table, bt_stride, bt_width, n_req, page,
+                        window_pages, sink_pages, 0, budget_pages_req, budget,
+                        slot_mapping, slot_prev, positions, n_pages, n_sel_hi, b_fix,
+                        stream);
 }
 
 static int topb_select_impl(

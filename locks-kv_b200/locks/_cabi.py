@@ -28,6 +28,10 @@ _SIGNATURES = {
     "locks_rki4_tag_scan": ([_P, _L, _L, _L, _P, _P, _P, _P, _I, _I, _I, _I,
                              _I, _P], 1),
     "locks_derive_page_params": ([_P, _I, _I, _I, _I, _I, _D, _P, _P, _P, _P], 1),
+    "locks_derive_page_params_req": ([_P, _I, _I, _I, _I, _P, _D, _P, _P, _P,
+                                      _P], 1),
+    "locks_append_advance_req": ([_P, _P, _L, _I, _I, _I, _I, _I, _P, _D, _P, _P,
+                                  _P, _P, _P, _P, _P], 1),
     "locks_rki4_score_bt": ([_P, _L, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I,
                              _I, _I, _I, _I, _F, _I, _P, _P], 1),
     "locks_topb_select": ([_I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I,

@@ -26,7 +26,7 @@ class HotPath:
     def __init__(self, kv_caches: List[torch.Tensor], block_table: torch.Tensor,
                  seq_lens: torch.Tensor, *, n_kv: int, G: int, scale: float,
                  cfg: LocksConfig, max_reqs: Optional[int] = None,
-                 split_cap: int = 128):
+                 split_cap: int = 128, budget_pages_req=None):
         dev = kv_caches[0].device
         self.device = dev
         self.cfg = cfg
@@ -49,6 +49,9 @@ class HotPath:
                        combine=cfg.quad_combine, zsplit=cfg.rki4_zsplit)
         st.scale = self.scale
         st._layer_of = {int(c.data_ptr()): i for i, c in enumerate(kv_caches)}
+        if budget_pages_req is not None:       # one page budget per request row
+            st.set_request_budgets(budget_pages_req)
+            st.budget_abs = max(int(max(budget_pages_req)), st.budget_abs)
         ensure_stage_b_buffers(st, dev, split_cap)
         self.st = st
         self.K_layers = [c[:, 0] for c in kv_caches]

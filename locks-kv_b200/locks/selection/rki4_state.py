@@ -92,6 +92,8 @@ class Rki4State:
         self.n_sel_hi = torch.zeros(R, device=device, dtype=i32)
         self.b_fix = torch.ones(R, device=device, dtype=i32)
         self.budget64 = torch.tensor([self.budget], device=device, dtype=f64)
+        # optional per-request page budgets (see set_request_budgets)
+        self.budget_req = None
         # device word a kernel raises when one of its bounded waits runs out
         self.status = torch.zeros(1, device=device, dtype=i32)
 
@@ -132,6 +134,24 @@ class Rki4State:
         return (self.pp_v4[layer], self.pp_vs[layer], self.pp_c8[layer],
                 self.pp_cs[layer], self.pp_mu8[layer], self.pp_mus[layer],
                 self.pp_tag[layer])
+
+    def set_request_budgets(self, budget_pages) -> None:
+        """One page budget per request row (a continuous batch whose requests
+        carry their own budgets): ``derive_page_params`` then takes ``b_fix[r]``
+        from ``budget_pages[r]`` (> 0: pages, <= 0: the fraction ``budget``)
+        instead of the engine-wide ``budget_pages``.  ``None`` switches back.
+        The reference holds ``b_fix`` per request but fills it from one
+        constant (``selection/select.py:29-58``)."""
+        if budget_pages is None:
+            self.budget_req = None
+            return
+        b = torch.as_tensor(budget_pages, dtype=torch.int32).reshape(-1)
+        assert b.numel() <= self.max_reqs
+        if self.budget_req is None:
+            self.budget_req = torch.zeros(self.max_reqs, device=self.device,
+                                          dtype=torch.int32)
+        self.budget_req.zero_()
+        self.budget_req[:b.numel()].copy_(b)
 
     def check_status(self) -> None:
         """Host-side read of the kernel status word (synchronises)."""

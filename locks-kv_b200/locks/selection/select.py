@@ -16,6 +16,13 @@ COMBINE_NONE, COMBINE_NRM, COMBINE_MAX = 0, 1, 2
 def derive_page_params(st, seq_lens, n_req: int) -> None:
     """Refresh ``st.n_pages / n_sel_hi / b_fix`` for this decode step."""
     assert n_req <= st.max_reqs
+    if getattr(st, "budget_req", None) is not None:
+        _cabi.call("locks_derive_page_params_req", _cabi.ptr(seq_lens), int(n_req),
+                   int(st.page), int(st.window_pages), int(st.sink_pages),
+                   _cabi.ptr(st.budget_req), float(st.budget),
+                   _cabi.ptr(st.n_pages), _cabi.ptr(st.n_sel_hi),
+                   _cabi.ptr(st.b_fix), _cabi.stream())
+        return
     _cabi.call("locks_derive_page_params", _cabi.ptr(seq_lens), int(n_req),
                int(st.page), int(st.window_pages), int(st.sink_pages),
                int(getattr(st, "budget_abs", 0)), float(st.budget),
@@ -32,6 +39,16 @@ def append_advance(st, seq_lens, block_table, n_req: int, slot, slot_prev,
     assert seq_lens.dtype == torch.int32 and block_table.dtype == torch.int32
     assert slot.dtype == slot_prev.dtype == positions.dtype == torch.int64
     assert block_table.stride(1) == 1
+    if getattr(st, "budget_req", None) is not None:
+        _cabi.call("locks_append_advance_req", _cabi.ptr(seq_lens),
+                   _cabi.ptr(block_table), block_table.stride(0),
+                   int(block_table.shape[1]), int(n_req), int(st.page),
+                   int(st.window_pages), int(st.sink_pages),
+                   _cabi.ptr(st.budget_req), float(st.budget), _cabi.ptr(slot),
+                   _cabi.ptr(slot_prev), _cabi.ptr(positions),
+                   _cabi.ptr(st.n_pages), _cabi.ptr(st.n_sel_hi),
+                   _cabi.ptr(st.b_fix), _cabi.stream())
+        return
     _cabi.call("locks_append_advance", _cabi.ptr(seq_lens), _cabi.ptr(block_table),
                block_table.stride(0), int(block_table.shape[1]), int(n_req),
                int(st.page), int(st.window_pages), int(st.sink_pages),

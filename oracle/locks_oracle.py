@@ -181,11 +181,14 @@ def derive_page_params(seq_lens, page, window, sink, budget_pages=0,
     npg = (sl + (page - 1)) // page
     nsh = npg - window
     s = nsh - sink
-    if budget_pages and budget_pages > 0:
-        b = np.maximum(np.minimum(budget_pages, np.maximum(s, 1)), 1)
-    else:
-        bf = np.ceil(s.astype(np.float64) * np.float64(budget))
-        b = np.minimum(np.maximum(bf.astype(np.int64), 1), np.maximum(s, 1))
+    bp = np.broadcast_to(np.asarray(budget_pages if budget_pages is not None
+                                    else 0, dtype=np.int64), s.shape)
+    b_abs = np.maximum(np.minimum(bp, np.maximum(s, 1)), 1)
+    bf = np.ceil(s.astype(np.float64) * np.float64(budget))
+    b_frac = np.minimum(np.maximum(bf.astype(np.int64), 1), np.maximum(s, 1))
+    # budget_pages may be one number (the reference's engine-wide BUDGET_ABS)
+    # or one entry per request (> 0: pages, <= 0: the fraction)
+    b = np.where(bp > 0, b_abs, b_frac)
     return npg.astype(np.int32), nsh.astype(np.int32), b.astype(np.int32)
 
 

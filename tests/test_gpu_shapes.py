@@ -238,3 +238,60 @@ def test_ragged_batch_scores_equal_single_request_scores():
         assert torch.equal(one.score_h[0, :, :, :n], batch[r, :, :, :n]), r
         # the published per-head maxima agree as well
         assert torch.equal(one.hmax[0], st.hmax[r]), r
+
+
+def test_ragged_batch_with_per_request_budgets_matches_oracle():
+    """A continuous batch whose requests carry their own page budgets (the
+    ragged-batch benchmark draws them from {32, 64, 128, 256}): page
+    parameters, selected sets and outputs of every request against the oracle
+    run with the same per-request budgets.  One request is shorter than its
+    budget (keeps every page), one uses the fractional fallback (entry 0)."""
+    from locks import LocksConfig, synth
+    from locks.hotpath import HotPath
+    shape = synth.GqaShape(n_layers=1, n_kv=4, G=4, budget_pages=64,
+                           sink_pages=1, window_pages=2, n_needles=3)
+    lens = [3000, 700, 5200, 260, 1900]
+    budgets = [32, 64, 128, 256, 0]
+    cpu = synth.make_gqa_case(23, shape, lens, device="cpu")
+    cfg = LocksConfig(budget_pages=shape.budget_pages, sink_pages=1, window_pages=2)
+    hp = HotPath([c.to(DEV) for c in cpu.kv_caches], cpu.block_table.to(DEV),
+                 cpu.seq_lens.to(DEV), n_kv=shape.n_kv, G=shape.G, scale=cpu.scale,
+                 cfg=cfg, budget_pages_req=budgets)
+    hp.build_all()
+    hp.derive()
+    hp.q[:, :cpu.n_req].copy_(cpu.q.to(DEV))
+    out = t2n(hp.step()[0])
+    torch.cuda.synchronize()
+    hp.st.check_status()
+    f = lambda t: t.float().numpy()
+    slabs = {k: t2n(v) for k, v in zip(("v4", "vs", "c8", "cs", "mu8", "mus", "tag"),
+                                       hp.st.layer_state(0))}
+    ref = orc.gqa_decode_step(
+        slabs, f(cpu.q[0]), f(cpu.kv_caches[0][:, 0]), f(cpu.kv_caches[0][:, 1]),
+        cpu.block_table.numpy(), cpu.seq_lens.numpy(), cpu.scale, n_kv=shape.n_kv,
+        G=shape.G, page=16, window=2, sink=1, budget_pages=np.array(budgets),
+        budget=hp.st.budget, split=8)
+    R = len(lens)
+    np.testing.assert_array_equal(t2n(hp.st.n_pages)[:R], ref["n_pages"])
+    np.testing.assert_array_equal(t2n(hp.st.n_sel_hi)[:R], ref["n_sel_hi"])
+    np.testing.assert_array_equal(t2n(hp.st.b_fix)[:R], ref["b"])
+    # 700 tokens hold 41 selectable pages (< 64), 260 tokens 14 (< 256); the
+    # last request falls back to ceil(0.1 * 116)
+    assert ref["b"].tolist() == [32, 41, 128, 14, 12]
+    np.testing.assert_array_equal(t2n(hp.st.page_cnt)[:R], ref["page_cnt"])
+    nsh = ref["n_sel_hi"]
+    tab, tab_ref = t2n(hp.st.page_table), ref["page_table"]
+    for r in range(R):
+        for kh in range(shape.n_kv):
+            n = ref["page_cnt"][r, kh]
+            a, b = set(tab[r, kh, :n].tolist()), set(tab_ref[r, kh, :n].tolist())
+            if a != b:             # only pages tied with the threshold (1e-3)
+                sel = [p for p in b if 1 <= p < nsh[r]]
+                tau = min(ref["score"][r, kh, p] for p in sel)
+                assert all(abs(ref["score"][r, kh, p] - tau) <= 1e-3 * abs(tau)
+                           for p in a ^ b)
+    ref64, _ = orc.attention_over_pages(
+        f(cpu.q[0]), f(cpu.kv_caches[0][:, 0]), f(cpu.kv_caches[0][:, 1]),
+        cpu.block_table.numpy(), tab, t2n(hp.st.page_cnt), cpu.seq_lens.numpy(),
+        cpu.scale, shape.n_kv, shape.G)
+    np.testing.assert_allclose(out[:R], ref64, atol=2e-2, rtol=1e-2)
