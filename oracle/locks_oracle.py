@@ -171,6 +171,38 @@ def delta_blocks(tag_slab, K_layers, block_table, settled_lens, page, max_fin):
     return blk[stale & valid.reshape(-1)]
 
 
+def mask_blocks(blocks, nb_state, nb_cache):
+    """Drop block ids outside the summary slab or the K tensor (the engine's
+    memory-profile pass hands out placeholder tables).
+    selection/rki4_build.py:133-144 (``_mask_blocks``)."""
+    blocks = np.asarray(blocks, dtype=np.int64)
+    nb = min(int(nb_state), int(nb_cache))
+    return blocks[(blocks >= 0) & (blocks < nb)]
+
+
+def refresh_blocks(tag_layer, K, block_table, settled_lens, page, force=False):
+    """Single-layer refresh: the unique finalized blocks of the batch whose
+    stored tag differs from the live K of THIS layer (all of them when
+    ``force``).  selection/rki4_build.py:320-364 (``rki4_build_refresh``)."""
+    sl = np.asarray(settled_lens).astype(np.int64)
+    n_fin = sl // page
+    max_fin = int(n_fin.max()) if n_fin.size else 0
+    if max_fin == 0:
+        return np.zeros(0, np.int64)
+    bt = np.asarray(block_table)[:, :max_fin].astype(np.int64)
+    fin = np.arange(max_fin)[None, :] < n_fin[:, None]
+    blk = mask_blocks(bt[fin], tag_layer.shape[0], K.shape[0])
+    if blk.size == 0:
+        return blk
+    if force:
+        stale = np.ones(blk.shape[0], dtype=bool)
+    else:
+        cur = K[blk, page - 1, :, :TAGW]
+        with np.errstate(invalid="ignore"):
+            stale = (cur != tag_layer[blk]).any(-1).any(-1)
+    return np.unique(blk[stale])
+
+
 # --------------------------------------------------------------------------- #
 # Stage A.1 -- per-step page parameters                                        #
 # --------------------------------------------------------------------------- #

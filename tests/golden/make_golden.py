@@ -198,6 +198,63 @@ def run_topb_kat():
     print("topb_kat cnt", cnt.tolist())
 
 
+def _load_lifecycle():
+    spec = importlib.util.spec_from_file_location(
+        "lifecycle_script", os.path.join(HERE, "lifecycle_script.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def run_lifecycle():
+    """The scripted summary life cycle (tests/golden/lifecycle_script.py) played
+    through the reference's rki4_build_{bulk,delta,tail,refresh} and
+    _delta_select: per event the return value and the stale block list, at the
+    end every tag and the records of the blocks the events touched."""
+    from locks.selection.build import _delta_select
+    ls = _load_lifecycle()
+    K, blocks, g = ls.make_world()
+    st = Rki4State("cpu", num_layers=ls.L, num_blocks=ls.NB, n_kv=ls.N_KV,
+                   G=ls.G, head_dim=ls.D, page=ls.PAGE, max_reqs=4,
+                   max_pages=ls.WIDTH, budget_pages=4, sink_pages=1,
+                   window_pages=1)
+
+    class Api:
+        def bulk(self, bt, sl, n, mf):
+            return rb.rki4_build_bulk(st, K, bt, sl, n, mf)
+
+        def delta(self, bt, sl, n, mf):
+            return rb.rki4_build_delta(st, K, bt, sl, n, mf)
+
+        def stale(self, bt, sl, n, mf):
+            return _delta_select(st.pp_tag, K, bt, sl, n, st.page, mf,
+                                 st.tagw).tolist()
+
+        def tail(self, bt, sl, n, rows):
+            return rb.rki4_build_tail(st, K, bt, sl, n, rows)
+
+        def refresh(self, layer, bt, sl, n, force):
+            return rb.rki4_build_refresh(st, layer, K[layer], bt, sl, n,
+                                         force=force)
+
+    ev, rows, lens = ls.run(Api(), K, blocks, g)
+    keep = [blocks["b"][3]] + blocks["c"][:3] + [blocks["a"][6], blocks["a"][2],
+                                                 blocks["a"][0], blocks["b"][19]]
+    kb = torch.tensor(keep)
+    out = {"ret": np.array([e[1] for e in ev], np.int64),
+           "kind": np.array([e[0] for e in ev]),
+           "tags": f32(st.pp_tag), "keep": np.array(keep, np.int64),
+           "slab_v4": st.pp_v4[:, kb].numpy(), "slab_vs": f32(st.pp_vs[:, kb]),
+           "slab_c8": st.pp_c8[:, kb].numpy(), "slab_cs": f32(st.pp_cs[:, kb]),
+           "slab_mu8": st.pp_mu8[:, kb].numpy(),
+           "slab_mus": f32(st.pp_mus[:, kb])}
+    for i, e in enumerate(ev):
+        if e[2] is not None:
+            out[f"stale{i}"] = np.array(e[2], np.int64)
+    np.savez_compressed(os.path.join(HERE, "gqa_lifecycle.npz"), **out)
+    print("gqa_lifecycle", [(e[0], e[1], e[2]) for e in ev])
+
+
 def run_mla(name, seed, shape, seq_lens, rank=8):
     """MLA: the reference's factor build, torch scorer, keep rule and the
     attention block of its backend (``LocksMLAImpl.forward_mqa`` itself needs a
@@ -254,6 +311,7 @@ if __name__ == "__main__":
                            sink_pages=2, window_pages=1, n_needles=2),
             [911, 64], keep_blocks=8, combine="max", budget=0.15)
     run_topb_kat()
+    run_lifecycle()
     run_mla("mla_small", 21,
             synth.MlaShape(n_layers=1, budget_pages=24, sink_pages=1,
                            window_pages=4), [777, 2048 + 5, 300])
