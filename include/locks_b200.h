@@ -48,6 +48,8 @@ extern "C" {
 /* values a kernel may leave in a caller-provided device `status` word */
 #define LOCKS_ST_OK            0
 #define LOCKS_ST_WAIT_TIMEOUT  1  /* a bounded on-chip wait ran out            */
+#define LOCKS_ST_CP_OVERFLOW   2  /* context parallel: more kept pages than     */
+                                  /* candidate slots (cap sized too small)      */
 
 #define LOCKS_COMBINE_NONE 0      /* `score` already holds the combined score  */
 #define LOCKS_COMBINE_NRM  1      /* sum_g exp(S[g,p] - max_p S[g,p])          */
@@ -359,6 +361,71 @@ int locks_cp_ipc_close(void* peer_region);
 int locks_cp_exchange(void* const* peers, int world, int rank, const void* payload,
                       int nbytes, int slot_bytes, void* out, int mode, int* status,
                       locks_stream_t stream);
+
+/* ---- Context parallel with the exchanges INSIDE the kernels ----------------------
+ * The three per-layer exchanges (per-head score maxima, best-b candidates,
+ * attention partials) are done by the selector and the decode kernel
+ * themselves: they store their words into every peer's link region and poll
+ * their own region for the peers' words, so a layer is three launches (score,
+ * select, decode) at any number of GPUs, chained by programmatic dependent
+ * launch exactly as on one GPU.  No counterpart in the reference.
+ *
+ * A link region (one per rank; locks_cp_link_bytes gives its size for a
+ * geometry; allocate with locks_cp_alloc, share with locks_cp_ipc_export /
+ * _open) starts with the rank's decode-step counter.  Every rank calls
+ * locks_cp_begin_step once per decode step, before the first layer: exchange
+ * epochs are step * n_layers + layer + 1, equal on all ranks with no
+ * communication.  locks_cp_link_reset zeroes a region and sets its step
+ * counter: after a wait ran out (LOCKS_ST_WAIT_TIMEOUT) all ranks reset to a
+ * common step value, behind a host-side barrier, before the next step.
+ *
+ * locks_cp_link_t: regions[r] = rank r's region as seen from this process
+ * (regions[rank] the local one; with world == 1 the kernels talk to themselves
+ * through the local region).  Pages: local page j is global page p0 + j;
+ * sink_loc / nsh_loc = the sequence's sink count and n_sel_hi in local page
+ * numbers, clamped to the range; b_global = the sequence's page budget; cap =
+ * candidate slots per (rank, kv head) >= the entries a rank's local selection
+ * can keep (b_global + its forced pages).
+ *
+ * locks_topb_select_cp: locks_topb_select(LOCKS_COMBINE_NRM) for ONE sequence
+ *   (n_req = 1) with hmax = the keys the local scorer published; the maxima are
+ *   max-reduced over the ranks before the combine, and after the local selection
+ *   (with b_fix = b_global) the candidates of all ranks meet: the page table
+ *   keeps this rank's forced pages and those of its candidates that are among
+ *   the b_global best of ALL ranks by (score descending, page ascending) -- the
+ *   exact-b tie rule of selection/select.py:183-222 -- ascending, -1 padded.
+ * locks_decode_fused_cp: locks_decode_fused for ONE sequence; the (m, l, O) of
+ *   the pages this rank attended are exchanged and merged with the formula of
+ *   attention/merge.py:106-152, every rank writes the full output row.
+ * Waits are bounded (about two seconds, then *status = LOCKS_ST_WAIT_TIMEOUT
+ * and the kernel returns with an undefined result). */
+#define LOCKS_CP_MAX_RANKS 8
+typedef struct locks_cp_link_t {
+    void* regions[LOCKS_CP_MAX_RANKS];
+    int32_t world, rank;
+    int32_t layer, n_layers;
+    int32_t p0, cap, b_global, sink_loc, nsh_loc;
+} locks_cp_link_t;
+
+int locks_cp_link_bytes(int n_kv, int G, int cap, int64_t* out);
+int locks_cp_begin_step(void* region, locks_stream_t stream);
+int locks_cp_link_reset(void* region, int64_t bytes, uint32_t step,
+                        locks_stream_t stream);
+int locks_topb_select_cp(const float* score_h, float* score, uint32_t* hmax,
+                         const int32_t* n_pages, const int32_t* n_sel_hi,
+                         const int32_t* b_fix, int32_t* page_table,
+                         int32_t* page_cnt, int n_kv, int G, int max_pages,
+                         int sink_pages, const locks_cp_link_t* link, int* status,
+                         locks_stream_t stream);
+int locks_decode_fused_cp(const void* q, int64_t q_stride_req, const void* k_cache,
+                          const void* v_cache, int64_t kv_stride_block,
+                          int64_t kv_stride_tok, int64_t kv_stride_head,
+                          const int32_t* block_table, int64_t bt_stride,
+                          const int32_t* page_table, const int32_t* page_cnt,
+                          const int32_t* seq_lens, void* out, int64_t out_stride_req,
+                          int n_kv, int G, int head_dim, int page, int max_pages,
+                          float scale, const locks_cp_link_t* link, int* status,
+                          locks_stream_t stream);
 
 /* Split decode + merge WITHOUT caller-provided partial buffers.  No counterpart
  * in the reference (its kernels always take caller-allocated partials).

@@ -17,6 +17,7 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "cp_link.cuh"
 
 namespace locks {
 namespace {
@@ -396,4 +397,43 @@ extern "C" int locks_cp_exchange(void* const* peers, int world, int rank,
         x, world, rank, static_cast<const uint4*>(payload), nbytes, slot_bytes,
         static_cast<uint8_t*>(out), mode, status);
     return check_launch("locks_cp_exchange");
+}
+
+// ---------------------------------------------------------------------------
+// Link regions of the in-kernel exchanges (cp_link.cuh)
+// ---------------------------------------------------------------------------
+namespace locks {
+namespace {
+__global__ void cp_begin_step_kernel(uint32_t* step) { *step += 1u; }
+__global__ void cp_set_step_kernel(uint32_t* step, uint32_t v) { *step = v; }
+}  // namespace
+}  // namespace locks
+
+extern "C" int locks_cp_link_bytes(int n_kv, int G, int cap, int64_t* out) {
+    LOCKS_REQUIRE(out && n_kv >= 1 && G >= 1 && G <= 16 && cap >= 1, LOCKS_ERR_ARG,
+                  "locks_cp_link_bytes: bad argument");
+    *out = cp_region_bytes(n_kv, G, cap);
+    return LOCKS_OK;
+}
+
+extern "C" int locks_cp_begin_step(void* region, locks_stream_t stream) {
+    LOCKS_REQUIRE(region != nullptr, LOCKS_ERR_ARG,
+                  "locks_cp_begin_step: null region");
+    cp_begin_step_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<uint32_t*>(region));
+    pdl_break();
+    return check_launch("locks_cp_begin_step");
+}
+
+extern "C" int locks_cp_link_reset(void* region, int64_t bytes, uint32_t step,
+                                   locks_stream_t stream) {
+    LOCKS_REQUIRE(region != nullptr && bytes >= CP_HEADER_BYTES, LOCKS_ERR_ARG,
+                  "locks_cp_link_reset: bad argument");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const cudaError_t e = cudaMemsetAsync(region, 0, (size_t)bytes, s);
+    if (e != cudaSuccess)
+        return fail(LOCKS_ERR_LAUNCH, "locks_cp_link_reset: %s", cudaGetErrorString(e));
+    cp_set_step_kernel<<<1, 1, 0, s>>>(static_cast<uint32_t*>(region), step);
+    pdl_break();
+    return check_launch("locks_cp_link_reset");
 }

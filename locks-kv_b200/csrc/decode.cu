@@ -25,6 +25,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "cp_link.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -95,7 +96,68 @@ struct DecParams {
     int n_kv, G, max_pages, split, pps_min, fused;
     float scale;
     int* status;
+    CpLink cp;          // context parallel: partials meet the peers' (world > 0)
 };
+
+// Context parallel: this rank's unnormalised partial of one output element --
+// (m, l) of head g and O[g][dd], all relative to m -- meets the other ranks'.
+// The words go to every rank's link region (the thread of channel 0 also sends
+// the head's m and l), the peers' words are polled in the local region, and the
+// merge of attention/merge.py:106-152 gives the sequence-wide (l, O).
+__device__ __forceinline__ void cp_merge_element(const CpLink& cp, int kh, int G,
+                                                 int g, int dd, float& M,
+                                                 float& Lsum, float& o,
+                                                 int* status) {
+    const uint32_t epoch = cp_epoch(cp);
+    const int idx = (kh * G + g) * CP_PART_WORDS_PER_HEAD;
+    if (dd == 0) {
+        cp_push(cp, cp.off_part, cp.part_words, epoch, idx, __float_as_uint(M));
+        cp_push(cp, cp.off_part, cp.part_words, epoch, idx + 1, __float_as_uint(Lsum));
+    }
+    cp_push(cp, cp.off_part, cp.part_words, epoch, idx + 2 + dd, __float_as_uint(o));
+    const uint8_t* mine = cp.base[cp.rank];
+    uint2 vm[CP_MAX_RANKS], vl[CP_MAX_RANKS], vo[CP_MAX_RANKS];
+    const unsigned long long t0 = cp_time_ns();
+    bool late = false;
+    for (;;) {
+#pragma unroll
+        for (int r = 0; r < CP_MAX_RANKS; ++r) {
+            if (r < cp.world) {
+                const uint8_t* a = mine + cp_slot(cp.off_part, cp.part_words, epoch, r, idx);
+                vm[r] = cp_load(a);
+                vl[r] = cp_load(a + 8);
+                vo[r] = cp_load(a + 8 * (2 + dd));
+            }
+        }
+        bool all = true;
+#pragma unroll
+        for (int r = 0; r < CP_MAX_RANKS; ++r)
+            if (r < cp.world)
+                all = all && vm[r].y == epoch && vl[r].y == epoch && vo[r].y == epoch;
+        if (all) break;
+        if (cp_time_ns() - t0 > CP_WAIT_NS) { late = true; break; }
+    }
+    if (late) {
+        if (status) atomicExch(status, LOCKS_ST_WAIT_TIMEOUT);
+        return;                                  // keep the local partial
+    }
+    float Mg = -INFINITY;
+#pragma unroll
+    for (int r = 0; r < CP_MAX_RANKS; ++r)
+        if (r < cp.world && __uint_as_float(vl[r].x) > 0.f)
+            Mg = fmaxf(Mg, __uint_as_float(vm[r].x));
+    float Lg = 0.f, og = 0.f;
+#pragma unroll
+    for (int r = 0; r < CP_MAX_RANKS; ++r) {
+        if (r < cp.world) {
+            const float lr = __uint_as_float(vl[r].x);
+            const float wt = (lr > 0.f) ? __expf(__uint_as_float(vm[r].x) - Mg) : 0.f;
+            Lg += wt * lr;
+            og += wt * __uint_as_float(vo[r].x);
+        }
+    }
+    M = Mg; Lsum = Lg; o = og;
+}
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src,
                                            int src_bytes) {
@@ -419,6 +481,7 @@ decode_kernel(const DecParams p) {
                 o += wt * sm.xacc[c * per_e + (e - sp * per_e)];
             }
         }
+        if (p.cp.world > 0) cp_merge_element(p.cp, kh, G, g, dd, M, Lsum, o, p.status);
         const float val = (Lsum > 0.f) ? o / Lsum : 0.f;
         p.out[(int64_t)r * p.out_stride_req + (int64_t)(kh * G + g) * HD + dd] =
             __float2bfloat16_rn(val);
@@ -699,6 +762,41 @@ extern "C" int locks_decode_fused(
     p.pps_min = 1; p.fused = 1; p.scale = scale; p.status = status;
     return launch_decode("locks_decode_fused", p, n_req,
                          fused_cluster_size(n_req, n_kv),
+                         static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int locks_decode_fused_cp(
+    const void* q, int64_t q_stride_req, const void* k_cache,
+    const void* v_cache, int64_t kv_stride_block, int64_t kv_stride_tok,
+    int64_t kv_stride_head, const int32_t* block_table, int64_t bt_stride,
+    const int32_t* page_table, const int32_t* page_cnt, const int32_t* seq_lens,
+    void* out, int64_t out_stride_req, int n_kv, int G, int head_dim, int page,
+    int max_pages, float scale, const locks_cp_link_t* link, int* status,
+    locks_stream_t stream) {
+    LOCKS_REQUIRE(q && k_cache && v_cache && block_table && page_table &&
+                      page_cnt && seq_lens && out && link,
+                  LOCKS_ERR_ARG, "locks_decode_fused_cp: null pointer argument");
+    int rc = check_geometry("locks_decode_fused_cp", G, head_dim, page);
+    if (rc) return rc;
+    rc = check_kv("locks_decode_fused_cp", q, k_cache, v_cache, q_stride_req,
+                  kv_stride_block, kv_stride_tok, kv_stride_head);
+    if (rc) return rc;
+    LOCKS_REQUIRE(n_kv >= 1 && n_kv <= 65535 && max_pages >= 1, LOCKS_ERR_ARG,
+                  "locks_decode_fused_cp: bad size argument");
+    DecParams p{};
+    rc = cp_link_fill(p.cp, link, n_kv, G, "locks_decode_fused_cp");
+    if (rc) return rc;
+    p.q = static_cast<const __nv_bfloat16*>(q); p.q_stride_req = q_stride_req;
+    p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
+    p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
+    p.stride_block = kv_stride_block; p.stride_tok = kv_stride_tok;
+    p.stride_head = kv_stride_head;
+    p.block_table = block_table; p.bt_stride = bt_stride;
+    p.page_table = page_table; p.page_cnt = page_cnt; p.seq_lens = seq_lens;
+    p.out = static_cast<__nv_bfloat16*>(out); p.out_stride_req = out_stride_req;
+    p.n_kv = n_kv; p.G = G; p.max_pages = max_pages; p.split = 1;
+    p.pps_min = 1; p.fused = 1; p.scale = scale; p.status = status;
+    return launch_decode("locks_decode_fused_cp", p, 1, fused_cluster_size(1, n_kv),
                          static_cast<cudaStream_t>(stream));
 }
 

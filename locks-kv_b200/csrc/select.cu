@@ -25,6 +25,7 @@
 #include <cooperative_groups.h>
 
 #include "common.cuh"
+#include "cp_link.cuh"
 #include "kv_append.cuh"
 
 namespace cg = cooperative_groups;
@@ -114,6 +115,8 @@ struct SelParams {
     int owner_mode;     // keys of a whole row fit one CTA: helpers only combine
     int key_cap;        // key slots per CTA (the histogram copies follow them)
     KvAppend app;       // optional: the new token's K/V store of this layer (key != null)
+    CpLink cp;          // context parallel: exchanges with the peer ranks (world > 0)
+    int* status;        // bounded-wait status word (context parallel only)
 };
 
 
@@ -326,6 +329,122 @@ __device__ __forceinline__ void sweep_max_groups(
         else { constexpr int GT = 16; CALL; }                \
     } while (0)
 
+// Context parallel, after the local selection with the sequence's budget: this
+// rank's selected pages meet those of the other ranks.  One CTA per kv-head:
+//   1. entry j < cap of the local table becomes a candidate packet pair
+//      {score key, global page}; forced pages and empty slots travel as key 0;
+//   2. the candidates of all ranks are polled into shared memory;
+//   3. a candidate stays when fewer than b candidates of ALL ranks beat it by
+//      (key descending, page ascending) -- counted directly, world * cap entries
+//      are a few thousand at most;
+//   4. the table is rewritten in place: forced pages + surviving candidates,
+//      ascending, -1 behind them, the count.
+// scratch: cap + 2 * world * cap words of shared memory.
+template <int NT>
+__device__ __forceinline__ void cp_global_cut(const CpLink& cp, int kh,
+                                              int32_t* tab, int32_t* cnt_out,
+                                              const float* score, int cnt,
+                                              uint32_t* scratch, int* wsum,
+                                              int* status) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int NW = NT / 32;
+    const int cap = cp.cap, W = cp.world;
+    const uint32_t epoch = cp_epoch(cp);
+    int* keep_sh = reinterpret_cast<int*>(scratch);
+    uint32_t* ckey = scratch + cap;
+    int32_t* cpage = reinterpret_cast<int32_t*>(ckey + W * cap);
+    for (int j = tid; j < cap; j += NT) {
+        const int e = (j < cnt) ? tab[j] : -1;
+        const bool sel = e >= cp.sink_loc && e < cp.nsh_loc;
+        const uint32_t key = sel ? min(max(f2key(score[e]), 1u), 0xFFFFFFFEu) : 0u;
+        const int idx = (kh * cap + j) * 2;
+        cp_push(cp, cp.off_cand, cp.cand_words, epoch, idx, key);
+        cp_push(cp, cp.off_cand, cp.cand_words, epoch, idx + 1,
+                (uint32_t)(sel ? e + cp.p0 : 0x7FFFFFFF));
+    }
+    bool late = false;
+    const uint8_t* mine = cp.base[cp.rank];
+    for (int i0 = 0; i0 < W * cap; i0 += 2 * NT) {         // 2 candidates per thread
+        const uint8_t* addr[4];
+        uint32_t val[4];
+        int n = 0, slot[2] = {-1, -1};
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int i = i0 + u * NT + tid;
+            if (i < W * cap) {
+                const int r = i / cap, c = i - r * cap;
+                const int idx = (kh * cap + c) * 2;
+                addr[n] = mine + cp_slot(cp.off_cand, cp.cand_words, epoch, r, idx);
+                addr[n + 1] = addr[n] + 8;
+                slot[u] = i;
+                n += 2;
+            }
+        }
+        if (n > 0) {
+            if (!cp_wait_words<4>(addr, n, epoch, val)) {
+                late = true;
+                val[0] = val[2] = 0u;                       // no candidate
+            }
+            int k = 0;
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+                if (slot[u] >= 0) {
+                    ckey[slot[u]] = val[k];
+                    cpage[slot[u]] = (int32_t)val[k + 1];
+                    k += 2;
+                }
+        }
+    }
+    if (late && status) atomicExch(status, LOCKS_ST_WAIT_TIMEOUT);
+    __syncthreads();
+    for (int j = warp; j < cap; j += NW) {
+        const int e = (j < cnt) ? tab[j] : -1;
+        const bool live = e >= 0;
+        const bool sel = live && e >= cp.sink_loc && e < cp.nsh_loc;
+        int keep = live ? 1 : 0;
+        if (sel) {                                          // warp-uniform
+            const uint32_t key = ckey[cp.rank * cap + j];
+            const int pg = cpage[cp.rank * cap + j];
+            int beat = 0;
+            for (int c = lane; c < W * cap; c += 32) {
+                const uint32_t k2 = ckey[c];
+                beat += (k2 > key || (k2 == key && k2 != 0u && cpage[c] < pg)) ? 1 : 0;
+            }
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1)
+                beat += __shfl_xor_sync(0xffffffffu, beat, o);
+            keep = (beat < cp.b_global && key != 0u) ? 1 : 0;
+        }
+        if (lane == 0) keep_sh[j] = keep;
+    }
+    __syncthreads();
+    int base = 0;
+    for (int j0 = 0; j0 < cap; j0 += NT) {
+        const int j = j0 + tid;
+        const int k = (j < cap) ? keep_sh[j] : 0;
+        const int e = (j < cnt) ? tab[j] : -1;
+        int inc = k;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += t;
+        }
+        if (lane == 31) wsum[warp] = inc;
+        __syncthreads();                                    // all reads of tab[j0..] done
+        int wbase = 0, total = 0;
+        for (int w = 0; w < NW; ++w) {
+            const int v = wsum[w];
+            if (w < warp) wbase += v;
+            total += v;
+        }
+        if (k) tab[base + wbase + inc - 1] = e;             // slot <= j: never ahead of a reader
+        base += total;
+        __syncthreads();
+    }
+    for (int j = base + tid; j < cnt; j += NT) tab[j] = -1;
+    if (tid == 0) *cnt_out = base;
+}
+
 // NT threads per CTA.  OWNER: CTA 0 selects the whole row, the other CTAs of the
 // cluster only combine (or there is no cluster); otherwise every CTA of the
 // cluster keeps and selects the keys of its page slice.
@@ -402,10 +521,37 @@ topb_kernel(const SelParams p) {
         for (int i = n_loc + tid; i < p.key_cap; i += NT) keys[i] = 0u;
 
     // ---------------- 1. GQA combine -> score[slice], keys[slice] --------------
+    // Context parallel: the per-head maxima are those of the WHOLE sequence.  CTA 0
+    // of the row sends the keys the local scorer published (0 = nothing scored
+    // here) to every rank; every CTA polls the local region for all ranks' keys.
+    // A rank with nothing to combine still takes part.
+    const bool cp_on = p.cp.world > 0;
+    if (cp_on && tid < G) {
+        const uint32_t epoch = cp_epoch(p.cp);
+        const int idx = kh * G + tid;
+        if (c_phys == 0)
+            cp_push(p.cp, p.cp.off_hmax, p.cp.hmax_words, epoch, idx,
+                    p.hmax[row * G + tid]);
+        const uint8_t* addr[CP_MAX_RANKS];
+        uint32_t val[CP_MAX_RANKS];
+#pragma unroll
+        for (int rr = 0; rr < CP_MAX_RANKS; ++rr)
+            addr[rr] = p.cp.base[p.cp.rank] +
+                       cp_slot(p.cp.off_hmax, p.cp.hmax_words, epoch, rr, idx);
+        if (!cp_wait_words<CP_MAX_RANKS>(addr, p.cp.world, epoch, val) && p.status)
+            atomicExch(p.status, LOCKS_ST_WAIT_TIMEOUT);
+        uint32_t m = 0u;
+#pragma unroll
+        for (int rr = 0; rr < CP_MAX_RANKS; ++rr)
+            if (rr < p.cp.world) m = max(m, val[rr]);
+        sm.hm_sh[tid] = key2f(m);
+    }
     if (p.combine == LOCKS_COMBINE_NRM && n_comb > 0) {
         const float* sh = p.score_h + row * (int64_t)G * MP;
         const bool published = p.hmax != nullptr;
-        if (published) {
+        if (cp_on) {
+            // hm_sh holds the sequence-wide maxima (published by sync_hm below)
+        } else if (published) {
             if (tid < G) sm.hm_sh[tid] = key2f(p.hmax[row * G + tid]);
         } else {
             sweep_max_groups<GT>(sh, sm.wmax[warp], G, MP, cs0, cn_loc, n_comb, cg_beg,
@@ -658,6 +804,17 @@ topb_kernel(const SelParams p) {
         if (!owner && c_phys == CL_phys - 1 && tid < p.app.head_dim)
             kv_append_elem(p.app, r, kh, tid);
     }
+    // context parallel: the ranks' selections meet (CTA 0 of the row; the other
+    // slices' table entries and scores are visible behind the cluster barrier)
+    if (cp_on) {
+        if (CL > 1) cluster.sync(); else __syncthreads();
+        if (c == 0 && cnt > p.cp.cap && tid == 0 && p.status)
+            atomicExch(p.status, LOCKS_ST_CP_OVERFLOW);     // caller sized cap too small
+        if (c == 0)
+            cp_global_cut<NT>(p.cp, kh, tab, &p.page_cnt[row], score,
+                              min(cnt, p.cp.cap),
+                              reinterpret_cast<uint32_t*>(h4), sm.wtot, p.status);
+    }
 }
 
 }  // namespace
@@ -753,7 +910,8 @@ static int topb_select_impl(
     const int32_t* n_pages, const int32_t* n_sel_hi, const int32_t* b_fix,
     int32_t* page_table, int32_t* page_cnt, int n_req, int n_kv, int G,
     int max_pages, int sink_pages, const locks_kv_append_t* app,
-    locks_stream_t stream) {
+    locks_stream_t stream, const locks_cp_link_t* link = nullptr,
+    int* status = nullptr) {
     using namespace locks;
     LOCKS_REQUIRE(combine >= 0 && combine <= 2, LOCKS_ERR_ARG,
                   "locks_topb_select: combine must be 0, 1 or 2, got %d", combine);
@@ -773,6 +931,21 @@ static int topb_select_impl(
     p.page_table = page_table; p.page_cnt = page_cnt;
     p.n_kv = n_kv; p.G = G; p.max_pages = max_pages; p.sink = sink_pages;
     p.app = KvAppend{};
+    p.cp = CpLink{};
+    p.status = status;
+    if (link != nullptr) {
+        LOCKS_REQUIRE(n_req == 1 && combine == LOCKS_COMBINE_NRM && hmax != nullptr,
+                      LOCKS_ERR_ARG,
+                      "locks_topb_select_cp: one sequence, nrm combine and the "
+                      "scorer's published maxima are required");
+        const int rc = cp_link_fill(p.cp, link, n_kv, G, "locks_topb_select_cp");
+        if (rc) return rc;
+        LOCKS_REQUIRE(p.cp.cap <= max_pages &&
+                          p.cp.cap + 2 * p.cp.world * p.cp.cap <= HSLOTS * HCOPIES,
+                      LOCKS_ERR_SIZE,
+                      "locks_topb_select_cp: %d candidate slots x %d ranks beyond "
+                      "the shared-memory staging area", p.cp.cap, p.cp.world);
+    }
     if (app != nullptr) {
         LOCKS_REQUIRE(app->key && app->val && app->k_cache && app->v_cache &&
                           app->slot_mapping,
@@ -893,6 +1066,19 @@ extern "C" int locks_topb_select(
     return topb_select_impl(combine, score_h, score, hmax, n_pages, n_sel_hi, b_fix,
                             page_table, page_cnt, n_req, n_kv, G, max_pages,
                             sink_pages, nullptr, stream);
+}
+
+extern "C" int locks_topb_select_cp(
+    const float* score_h, float* score, uint32_t* hmax, const int32_t* n_pages,
+    const int32_t* n_sel_hi, const int32_t* b_fix, int32_t* page_table,
+    int32_t* page_cnt, int n_kv, int G, int max_pages, int sink_pages,
+    const locks_cp_link_t* link, int* status, locks_stream_t stream) {
+    using namespace locks;
+    LOCKS_REQUIRE(link != nullptr, LOCKS_ERR_ARG,
+                  "locks_topb_select_cp: null link description");
+    return topb_select_impl(LOCKS_COMBINE_NRM, score_h, score, hmax, n_pages,
+                            n_sel_hi, b_fix, page_table, page_cnt, 1, n_kv, G,
+                            max_pages, sink_pages, nullptr, stream, link, status);
 }
 
 extern "C" int locks_topb_select_append(

@@ -58,6 +58,13 @@ _SIGNATURES = {
     "locks_cp_ipc_open": ([_P, _P], 0),
     "locks_cp_ipc_close": ([_P], 0),
     "locks_cp_exchange": ([_P, _I, _I, _P, _I, _I, _P, _I, _P, _P], 1),
+    "locks_cp_link_bytes": ([_I, _I, _I, _P], 0),
+    "locks_cp_begin_step": ([_P, _P], 1),
+    "locks_cp_link_reset": ([_P, _L, ctypes.c_uint32, _P], 1),
+    "locks_topb_select_cp": ([_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P,
+                              _P, _P], 1),
+    "locks_decode_fused_cp": ([_P, _L, _P, _P, _L, _L, _L, _P, _L, _P, _P, _P, _P,
+                               _L, _I, _I, _I, _I, _I, _F, _P, _P, _P], 1),
     "locks_merge_gathered": ([_P, _L, _I, _P, _L, _I, _I, _I, _I, _I, _P], 1),
     "locks_decode_fused": ([_P, _L, _P, _P, _L, _L, _L, _P, _L, _P, _P, _P, _P,
                             _L, _I, _I, _I, _I, _I, _I, _F, _P, _P], 1),
@@ -142,6 +149,15 @@ class KvAppendDesc(ctypes.Structure):
                 ("cos_sin_row_stride", _L), ("rot_dim", ctypes.c_int32),
                 ("neox", ctypes.c_int32), ("head_dim", ctypes.c_int32),
                 ("page", ctypes.c_int32), ("num_blocks", ctypes.c_int32)]
+
+
+class CpLinkDesc(ctypes.Structure):
+    """``locks_cp_link_t`` of the header, field for field."""
+    _fields_ = [("regions", _P * 8), ("world", ctypes.c_int32),
+                ("rank", ctypes.c_int32), ("layer", ctypes.c_int32),
+                ("n_layers", ctypes.c_int32), ("p0", ctypes.c_int32),
+                ("cap", ctypes.c_int32), ("b_global", ctypes.c_int32),
+                ("sink_loc", ctypes.c_int32), ("nsh_loc", ctypes.c_int32)]
 
 
 def stream() -> c_void_p:
