@@ -451,7 +451,8 @@ __device__ __forceinline__ void cp_global_cut(const CpLink& cp, int kh,
 // GT: the GQA group size rounded up to a power of two (a kernel per value keeps
 // the once-through instruction stream short).
 // APPEND: the launch also stores the new token's K/V of its rows (p.app).
-template <int NT, bool OWNER, int GT, bool APPEND>
+// CP: context parallel (the exchanges with the peer ranks are compiled in).
+template <int NT, bool OWNER, int GT, bool APPEND, bool CP>
 __global__ void __launch_bounds__(NT)
 topb_kernel(const SelParams p) {
     constexpr int NW = NT / 32;
@@ -525,7 +526,7 @@ topb_kernel(const SelParams p) {
     // of the row sends the keys the local scorer published (0 = nothing scored
     // here) to every rank; every CTA polls the local region for all ranks' keys.
     // A rank with nothing to combine still takes part.
-    const bool cp_on = p.cp.world > 0;
+    constexpr bool cp_on = CP;
     if (cp_on && tid < G) {
         const uint32_t epoch = cp_epoch(p.cp);
         const int idx = kh * G + tid;
@@ -806,7 +807,7 @@ topb_kernel(const SelParams p) {
     }
     // context parallel: the ranks' selections meet (CTA 0 of the row; the other
     // slices' table entries and scores are visible behind the cluster barrier)
-    if (cp_on) {
+    if constexpr (CP) {
         if (CL > 1) cluster.sync(); else __syncthreads();
         if (c == 0 && cnt > p.cp.cap && tid == 0 && p.status)
             atomicExch(p.status, LOCKS_ST_CP_OVERFLOW);     // caller sized cap too small
@@ -940,8 +941,7 @@ static int topb_select_impl(
                       "scorer's published maxima are required");
         const int rc = cp_link_fill(p.cp, link, n_kv, G, "locks_topb_select_cp");
         if (rc) return rc;
-        LOCKS_REQUIRE(p.cp.cap <= max_pages &&
-                          p.cp.cap + 2 * p.cp.world * p.cp.cap <= HSLOTS * HCOPIES,
+        LOCKS_REQUIRE(p.cp.cap + 2 * p.cp.world * p.cp.cap <= HSLOTS * HCOPIES,
                       LOCKS_ERR_SIZE,
                       "locks_topb_select_cp: %d candidate slots x %d ranks beyond "
                       "the shared-memory staging area", p.cp.cap, p.cp.world);
@@ -1014,14 +1014,16 @@ static int topb_select_impl(
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-#define LOCKS_SEL_ATTR_A(GTV, AP)                                                  \
-        cudaFuncSetAttribute(topb_kernel<SEL_THREADS, true, GTV, AP>,              \
+#define LOCKS_SEL_ATTR_A(GTV, AP, CPV)                                             \
+        cudaFuncSetAttribute(topb_kernel<SEL_THREADS, true, GTV, AP, CPV>,         \
                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);\
-        cudaFuncSetAttribute(topb_kernel<SEL_THREADS, false, GTV, AP>,             \
+        cudaFuncSetAttribute(topb_kernel<SEL_THREADS, false, GTV, AP, CPV>,        \
                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);\
-        cudaFuncSetAttribute(topb_kernel<SEL_THREADS, false, GTV, AP>,             \
+        cudaFuncSetAttribute(topb_kernel<SEL_THREADS, false, GTV, AP, CPV>,        \
                              cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-#define LOCKS_SEL_ATTR(GTV) LOCKS_SEL_ATTR_A(GTV, false) LOCKS_SEL_ATTR_A(GTV, true)
+#define LOCKS_SEL_ATTR(GTV)                                                        \
+    LOCKS_SEL_ATTR_A(GTV, false, false) LOCKS_SEL_ATTR_A(GTV, true, false)         \
+    LOCKS_SEL_ATTR_A(GTV, false, true)
         LOCKS_SEL_ATTR(1) LOCKS_SEL_ATTR(2) LOCKS_SEL_ATTR(4) LOCKS_SEL_ATTR(8)
         LOCKS_SEL_ATTR(16)
 #undef LOCKS_SEL_ATTR
@@ -1043,14 +1045,21 @@ static int topb_select_impl(
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
     cudaError_t e = cudaSuccess;
-    if (app == nullptr) {
+    if (link != nullptr) {
+        LOCKS_REQUIRE(app == nullptr, LOCKS_ERR_ARG,
+                      "locks_topb_select_cp: the carried KV write is not available "
+                      "with context parallelism");
         LOCKS_DISPATCH_GT(G, (e = owner_mode
-            ? cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, true, GT, false>, p)
-            : cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, false, GT, false>, p)));
+            ? cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, true, GT, false, true>, p)
+            : cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, false, GT, false, true>, p)));
+    } else if (app == nullptr) {
+        LOCKS_DISPATCH_GT(G, (e = owner_mode
+            ? cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, true, GT, false, false>, p)
+            : cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, false, GT, false, false>, p)));
     } else {
         LOCKS_DISPATCH_GT(G, (e = owner_mode
-            ? cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, true, GT, true>, p)
-            : cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, false, GT, true>, p)));
+            ? cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, true, GT, true, false>, p)
+            : cudaLaunchKernelEx(&cfg, topb_kernel<SEL_THREADS, false, GT, true, false>, p)));
     }
     if (e != cudaSuccess)
         return fail(LOCKS_ERR_LAUNCH, "locks_topb_select: %s",

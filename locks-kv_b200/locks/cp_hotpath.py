@@ -16,7 +16,15 @@ Per layer three small exchanges make the result equal to the single-GPU one:
 
 The reference has no distributed code; the page rules are the reference's
 (``selection/select.py:28-58``, ``:183-222``), applied to global page numbers.
-The collectives go through ``torch.distributed`` (NCCL); remote data lands in
+
+Transports.  ``"fused"`` (default): the exchanges happen INSIDE the selector and
+the decode kernel -- they store their words into every peer's link region over
+NVLink and poll their own region (``locks_topb_select_cp``,
+``locks_decode_fused_cp``), so a layer is three launches (score, select, decode)
+at any number of GPUs, chained by programmatic dependent launch as on one GPU.
+``"peer"``: one exchange kernel per exchange between the single-GPU kernels
+(ten launches per layer); ``"nccl"``: library collectives -- both kept as the
+baselines the fused path is measured against.  Remote data always lands in
 local memory before a kernel of this library reads it.  The whole step has
 fixed shapes and no host synchronisation, so it can be captured in a CUDA graph.
 """
@@ -63,7 +71,7 @@ class ContextParallelHotPath:
     def __init__(self, kv_caches: List[torch.Tensor], block_table: torch.Tensor,
                  *, seq_len: int, p0: int, p1: int, n_kv: int, G: int,
                  scale: float, cfg: LocksConfig, group=None,
-                 split: Optional[int] = None, transport: str = "peer"):
+                 split: Optional[int] = None, transport: str = "fused"):
         dev = kv_caches[0].device
         self.device, self.cfg, self.group = dev, cfg, group
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -133,9 +141,22 @@ class ContextParallelHotPath:
         # transport of the three exchanges: "peer" = one fused kernel per rank
         # over NVLink peer memory (locks_cp_exchange), "nccl" = library
         # collectives (kept as the baseline the fused kernel is measured against)
-        assert transport in ("peer", "nccl")
-        self.transport = transport if self.world > 1 else "none"
+        assert transport in ("fused", "peer", "nccl")
+        self.transport = transport if (self.world > 1 or transport == "fused") \
+            else "none"
         self.hm_pad = None
+        self.link = None
+        if self.transport == "fused":
+            from .peer import CpLinkRegion
+            # candidate slots per rank: the same on every rank (the regions
+            # share one layout), enough for the budget plus the forced pages
+            cap_link = b + cfg.sink_pages + cfg.window_pages + 1
+            self.link = CpLinkRegion(n_kv=n_kv, G=G, cap=cap_link, n_layers=L,
+                                     group=group)
+            self._links = [self.link.link(l, p0=self.p0, b_global=b,
+                                          sink_loc=self.sink_loc,
+                                          nsh_loc=self.nsh_loc)
+                           for l in range(L)]
         if self.transport == "peer":
             from .peer import PeerExchange
             # keys and candidates (a few KB): flag-in-packet transport; partial
@@ -220,8 +241,47 @@ class ContextParallelHotPath:
                    out.stride(0), 1, int(self.n_kv), int(self.G), int(self.d),
                    int(self.split), _cabi.stream())
 
+    # ---- the fused path: exchanges inside the selector and the decode -------
+    def _layers_fused(self) -> None:
+        import ctypes
+        st = self.st
+        self.link.begin_step()
+        for l in range(len(self.kv_caches)):
+            q = self.q[l]
+            link = ctypes.cast(ctypes.pointer(self._links[l]), ctypes.c_void_p)
+            rki4_score_only(st, l, q, self.block_table, self.seq_lens, 1,
+                            self.scale)
+            _cabi.call("locks_topb_select_cp", _cabi.ptr(st.score_h),
+                       _cabi.ptr(st.score), _cabi.ptr(st.hmax),
+                       _cabi.ptr(st.n_pages), _cabi.ptr(st.n_sel_hi),
+                       _cabi.ptr(st.b_fix), _cabi.ptr(st.page_table),
+                       _cabi.ptr(st.page_cnt), int(self.n_kv), int(self.G),
+                       int(st.max_pages), int(st.sink_pages), link,
+                       _cabi.ptr(st.status), _cabi.stream())
+            k, v = _kv_args(self.kv_caches[l], self.vsources[l])
+            out = self.out[l]
+            _cabi.call("locks_decode_fused_cp", _cabi.ptr(q), q.stride(0),
+                       _cabi.ptr(k), _cabi.ptr(v), k.stride(0), k.stride(1),
+                       k.stride(2), _cabi.ptr(self.block_table),
+                       self.block_table.stride(0), _cabi.ptr(st.page_table),
+                       _cabi.ptr(st.page_cnt), _cabi.ptr(self.seq_lens),
+                       _cabi.ptr(out), out.stride(0), int(self.n_kv), int(self.G),
+                       int(self.d), int(self.page), int(st.max_pages),
+                       float(self.scale), link, _cabi.ptr(st.status),
+                       _cabi.stream())
+
+    def resync(self) -> None:
+        """After ``st.status`` reported a wait that ran out: bring the ranks'
+        link regions and step counters back in line (collective, host-side)."""
+        if self.link is not None:
+            self.link.resync()
+        self.st.status.zero_()
+
     # ---- one decode step ---------------------------------------------------
     def _layers(self) -> None:
+        if self.transport == "fused":
+            self._layers_fused()
+            return
         st = self.st
         for l in range(len(self.kv_caches)):
             rki4_score_only(st, l, self.q[l], self.block_table, self.seq_lens, 1,

@@ -40,7 +40,7 @@ def main() -> int:
     caches, q, bt = synth.make_gqa_shard(11, shape, seq_len, p0, p1, device=dev)
     cp = ContextParallelHotPath(caches, bt, seq_len=seq_len, p0=p0, p1=p1,
                                 n_kv=shape.n_kv, G=shape.G, scale=scale, cfg=cfg,
-                                transport=os.environ.get("CP_TRANSPORT", "peer"))
+                                transport=os.environ.get("CP_TRANSPORT", "fused"))
     cp.build_all()
     cp.q.copy_(q)
     out_eager = cp.step_eager().clone()

@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("transport", ["peer", "nccl"])
+@pytest.mark.parametrize("transport", ["fused", "peer", "nccl"])
 @pytest.mark.parametrize("seq_len", [40005, 4099])
 def test_context_parallel_matches_single_gpu(seq_len, transport):
     if torch.cuda.device_count() < 2:

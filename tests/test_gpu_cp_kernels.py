@@ -154,3 +154,86 @@ def test_exchange_wait_runs_out_and_reports(mode):
     finally:
         _cabi.call("locks_cp_free", r0)
         _cabi.call("locks_cp_free", r1)
+
+
+def _single_rank_pair(seq_len, seed=11, n_layers=3):
+    """The same seeded sequence through the single-GPU driver and through the
+    context-parallel driver with ONE rank (the in-kernel exchanges then run
+    against the rank's own link region: same code path, no peer)."""
+    import math
+    from locks import LocksConfig, synth
+    from locks.cp_hotpath import ContextParallelHotPath
+    from locks.hotpath import HotPath
+    shape = synth.GqaShape(n_layers=n_layers, n_kv=2, G=16, d=128, page=16,
+                           budget_pages=64, sink_pages=1, window_pages=8,
+                           n_needles=6, n_outlier=4)
+    cfg = LocksConfig(budget_pages=shape.budget_pages, sink_pages=shape.sink_pages,
+                      window_pages=shape.window_pages)
+    scale = 1.0 / math.sqrt(shape.d)
+    npg = -(-seq_len // shape.page)
+    caches, q, bt = synth.make_gqa_shard(seed, shape, seq_len, 0, npg, device=DEV)
+    sl = torch.tensor([seq_len], dtype=torch.int32, device=DEV)
+    hp = HotPath(caches, bt, sl, n_kv=shape.n_kv, G=shape.G, scale=scale, cfg=cfg)
+    hp.build_all(); hp.derive(); hp.q.copy_(q)
+    cp = ContextParallelHotPath(caches, bt, seq_len=seq_len, p0=0, p1=npg,
+                                n_kv=shape.n_kv, G=shape.G, scale=scale, cfg=cfg,
+                                transport="fused")
+    cp.st.pp_rec.copy_(hp.st.pp_rec)
+    cp.q.copy_(q)
+    return hp, cp, shape
+
+
+@pytest.mark.parametrize("seq_len", [4099, 40005, 300])
+def test_fused_context_parallel_single_rank_equals_hot_path(seq_len):
+    """Selector with the maxima exchange and the global cut inside, decode with
+    the partial exchange and merge inside, against the plain kernels: the same
+    page tables bit for bit and the same outputs; replayed as a graph several
+    times (every replay is a new step with new exchange epochs)."""
+    hp, cp, shape = _single_rank_pair(seq_len)
+    ref = hp.step_eager().clone()
+    torch.cuda.synchronize()
+    tab_ref, cnt_ref = hp.st.page_table.clone(), hp.st.page_cnt.clone()
+    got = cp.step_eager().clone()
+    torch.cuda.synchronize()
+    cp.st.check_status()
+    assert torch.equal(cp.st.page_cnt, cnt_ref)
+    assert torch.equal(cp.st.page_table, tab_ref)
+    np.testing.assert_allclose(t2n(got), t2n(ref), atol=2e-2, rtol=1e-2)
+    for _ in range(3):
+        out = cp.step().clone()
+    torch.cuda.synchronize()
+    cp.st.check_status()
+    assert torch.equal(out, got)
+    assert torch.equal(cp.st.page_table, tab_ref)
+
+
+def test_fused_context_parallel_wait_runs_out_and_reports():
+    """A peer that never shows up, for the in-kernel exchanges: the link claims
+    two ranks, rank 1's region is a second allocation on this GPU that nothing
+    writes.  Selector and decode give up after their time limit, raise the
+    status word and return; after ``resync`` a normal step works again."""
+    import ctypes
+    from locks import _cabi
+    hp, cp, shape = _single_rank_pair(4099, n_layers=1)
+    want = cp.step_eager().clone()
+    torch.cuda.synchronize()
+    cp.st.check_status()
+    ghost = ctypes.c_void_p()
+    _cabi.call("locks_cp_alloc", cp.link.nbytes, ctypes.byref(ghost))
+    try:
+        for d in cp._links:
+            d.world = 2
+            d.regions[1] = ghost.value
+        cp.step_eager()
+        torch.cuda.synchronize()                     # returns after a few seconds
+        assert int(cp.st.status.item()) == 1         # LOCKS_ST_WAIT_TIMEOUT
+        for d in cp._links:
+            d.world = 1
+            d.regions[1] = None
+        cp.resync()
+        got = cp.step_eager().clone()
+        torch.cuda.synchronize()
+        cp.st.check_status()
+        assert torch.equal(got, want)
+    finally:
+        _cabi.call("locks_cp_free", ghost)
