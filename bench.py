@@ -13,6 +13,12 @@ One JSON line is printed by rank 0.
 
 With N > 1 every rank decodes its own sequence of the same shape (sequence
 sharding, no data-path collective): weak scaling, value = N sequences' tokens/s.
+The same line then carries the two partitioned workloads, run by all N ranks
+together: `c2_sharded` (the seeded 64-sequence ragged batch with per-sequence
+page budgets, sequences dealt to the ranks by step bytes, no collective) and
+`cp` (ONE 1M-token sequence, context parallel over the ranks, exchanges inside
+the selector and decode kernels; strong scaling) with `cp_parity`, a small
+context-parallel case checked against the single-GPU path inside the run.
 
 `--impl reference` times the CPU restatement of the reference's own path
 (oracle/locks_oracle.py, numpy, all host threads) on a bounded sample of the
@@ -39,7 +45,21 @@ import torch  # noqa: E402
 
 REC_ALGO_BYTES = 818           # summary bytes per (page, kv-head) the scorer needs
 PAGE_KV_BYTES = 16 * 128 * 2 * 2   # K + V bytes of one attended (page, kv-head)
-SCORE_TRAFFIC_PER_UNIT = (54559232 + 71936) / 65480.0   # measured DRAM bytes per unit
+
+
+def score_traffic_per_unit():
+    """DRAM bytes (read + write) the scorer moved per (page, kv-head) in the ncu
+    capture of the committed profile summary: the line
+    ``scorer_dram_bytes_per_unit: <number>`` of the summary file under
+    ``profiles/``; None when no such line exists."""
+    import glob
+    import re
+    for f in sorted(glob.glob(os.path.join(ROOT, "profiles", "*.md"))):
+        m = re.search(r"^scorer_dram_bytes_per_unit:\s*([0-9.]+)", open(f).read(),
+                      re.M)
+        if m:
+            return float(m.group(1))
+    return None
 
 
 def workload(name: str, ctx: int | None):
@@ -51,25 +71,34 @@ def workload(name: str, ctx: int | None):
     elif name in ("c4", "c4cp"):
         sh, c = synth.CONFIG4, 1048576
     elif name == "c2":
-        # ragged continuous batch: 8 sequences, log-uniform in [4096, 262144]
-        sh = synth.CONFIG1
-        rng = np.random.default_rng(20260202)
-        c = [int(x) for x in np.exp(rng.uniform(np.log(4096), np.log(262144), 8))]
-        return sh, c
+        # ragged continuous batch: 64 sequences, log-uniform in [4096, 262144]
+        return synth.CONFIG1, c2_draw()[0]
     else:
         raise SystemExit(f"unknown workload {name}")
     return sh, (ctx or c)
 
 
-def algo_bytes(sh, seq_len):
+def c2_draw(n_seq: int = 64):
+    """The ragged batch of the continuous-batching workload: context lengths
+    log-uniform in [4096, 262144] and a page budget per sequence from
+    {32, 64, 128, 256}, both from one seed."""
+    rng = np.random.default_rng(20260202)
+    ctx = [int(x) for x in np.exp(rng.uniform(np.log(4096), np.log(262144), n_seq))]
+    budgets = [int(b) for b in rng.choice([32, 64, 128, 256], n_seq)]
+    return ctx, budgets
+
+
+def algo_bytes(sh, seq_len, budgets=None):
     """Algorithmic bytes of one step: summaries scanned + selected K/V pages
-    (summed over the sequences of a ragged batch)."""
+    (summed over the sequences of a ragged batch; ``budgets``: one page budget
+    per sequence instead of the shape's)."""
     lens = seq_len if isinstance(seq_len, (list, tuple)) else [seq_len]
     score = dec = dense = nsh_t = A_t = 0
-    for sl in lens:
+    for i, sl in enumerate(lens):
         npg = -(-sl // sh.page)
         nsh = npg - sh.window_pages
-        A = min(sh.budget_pages, max(nsh - sh.sink_pages, 0)) + sh.sink_pages \
+        bp = budgets[i] if budgets is not None else sh.budget_pages
+        A = min(bp, max(nsh - sh.sink_pages, 0)) + sh.sink_pages \
             + sh.window_pages
         score += sh.n_layers * sh.n_kv * nsh * REC_ALGO_BYTES
         dec += sh.n_layers * sh.n_kv * A * PAGE_KV_BYTES
@@ -210,11 +239,13 @@ def run_reference(args, sh, seq_len):
 # --------------------------------------------------------------------------- #
 # GPU arm                                                                      #
 # --------------------------------------------------------------------------- #
-def make_device_case(sh, seq_len, dev, seed, return_needles=False, extra_pages=4):
+def make_device_case(sh, seq_len, dev, seed, return_needles=False, extra_pages=4,
+                     n_slabs=None):
     """Paged caches for one sequence (or a ragged batch: a list of lengths),
     generated on the device layer by layer (the full-size cache does not fit a
     CPU round trip).  All sequences share one block pool; block ids are a seeded
-    permutation."""
+    permutation.  ``n_slabs``: generate only that many distinct layer caches
+    (the caller cycles its layer launches over them); q is still per layer."""
     from locks import synth
     page = sh.page
     lens = list(seq_len) if isinstance(seq_len, (list, tuple)) else [seq_len]
@@ -231,7 +262,7 @@ def make_device_case(sh, seq_len, dev, seed, return_needles=False, extra_pages=4
         o += n + extra_pages
     bt = bt_cpu.contiguous().to(dev)
     caches, qs, needles = [], [], []
-    for l in range(sh.n_layers):
+    for l in range(n_slabs or sh.n_layers):
         kvc = torch.zeros(NB, 2, page, sh.n_kv, sh.d, device=dev,
                           dtype=torch.bfloat16)
         ql, ndl = [], []
@@ -250,6 +281,8 @@ def make_device_case(sh, seq_len, dev, seed, return_needles=False, extra_pages=4
         needles.append(ndl[0] if len(lens) == 1 else ndl)
         caches.append(kvc)
         qs.append(torch.stack(ql))
+    if n_slabs:
+        qs = [qs[l % n_slabs] for l in range(sh.n_layers)]
     sl_t = torch.tensor(lens, dtype=torch.int32, device=dev)
     if return_needles:
         return caches, torch.stack(qs), bt, sl_t, needles
@@ -282,8 +315,6 @@ def run_gpu(args, sh, seq_len):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
 
     # ---- set-up (untimed): caches, summaries, page parameters -----------------
     caches, q, bt, sl = make_device_case(sh, seq_len, dev, seed=1234 + rank)
@@ -474,8 +505,6 @@ def run_gpu(args, sh, seq_len):
     clocks = sampler.stop() if rank == 0 else None
 
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
         return None
 
     # ---- roofline of the dominant kernel (the scorer) --------------------------
@@ -532,10 +561,10 @@ def run_gpu(args, sh, seq_len):
         "roofline": {"kernel": "rki4_score_kernel", "bound": "hbm",
                      "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak,
-                     # dram__bytes_read+write of one launch, ncu --set full on the
-                     # same shape (profiles/c1_score_select_decode_ncu_full.md):
-                     # 833.2 B per (page, kv-head), scaled by the units of a launch
-                     "traffic": SCORE_TRAFFIC_PER_UNIT * sh.n_kv * nsh,
+                     # dram__bytes_read + write per (page, kv-head) of the ncu
+                     # capture on this shape, scaled by the units of a launch
+                     "traffic": (score_traffic_per_unit() or 0) * sh.n_kv * nsh
+                     or None,
                      "peak_source": peak_src,
                      "bytes_per_launch": score_launch_bytes,
                      "us_per_launch": ms_score * 1e3},
@@ -562,126 +591,237 @@ def run_gpu(args, sh, seq_len):
         "decode_loop": loop,
         "cpu_baseline": cpu,
     }
-    if world > 1:
-        dist.destroy_process_group()
     return line
 
 
-def run_gpu_cp(args, sh, seq_len):
-    """Workload c4cp: ONE sequence (config 4: 1M tokens) whose pages are split
-    over the ranks -- context parallel, three small exchanges per layer.  Strong
-    scaling: the job is the same at every N."""
-    import torch.distributed as dist
-    from locks import LocksConfig, synth
-    from locks.cp_hotpath import ContextParallelHotPath
-    from locks.parallel import partition_pages
+def _peak():
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        return float(json.load(open(peaks_path))["hbm_gbs"]), \
+            "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback"
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
+
+def _timed_steps(step, steps, warmup, dev, world):
+    """K replays bracketed by a barrier and a device synchronise on both sides;
+    ms per step, max over ranks."""
+    import torch.distributed as dist
+    for _ in range(max(warmup, 3)):
+        step()
+    torch.cuda.synchronize()
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        dist.barrier()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+    return ms
+
+
+def cp_record(args, dev, rank, world, layers=8):
+    """ONE sequence of the 1M-token shape (40 layers as written; `layers` of them
+    are run) whose pages are split over the ranks by contiguous ranges: strong
+    scaling.  Three launches per layer on every rank (score, select, decode);
+    the three per-layer exchanges happen inside the selector and the decode
+    kernel over NVLink peer memory.  Reported: us per layer (max over ranks),
+    the same with the exchanges switched off (every rank on its own range with
+    no peer: the streaming work alone), their difference (= what the three
+    exchanges cost), and the earlier arrangement with one exchange kernel per
+    exchange between the single-GPU kernels."""
+    import dataclasses
+    from locks import LocksConfig, synth
+    from locks.cp_hotpath import ContextParallelHotPath, check_against_single_gpu
+    from locks.parallel import partition_pages
+    sh = dataclasses.replace(synth.CONFIG4, n_layers=layers)
+    seq_len = 1048576 + 1
     npg = -(-seq_len // sh.page)
     p0, p1 = partition_pages(npg, world)[rank]
     caches, q, bt = synth.make_gqa_shard(1234, sh, seq_len, p0, p1, device=dev)
     cfg = LocksConfig(budget_pages=sh.budget_pages, sink_pages=sh.sink_pages,
                       window_pages=sh.window_pages)
-    cp = ContextParallelHotPath(caches, bt, seq_len=seq_len, p0=p0, p1=p1,
-                                n_kv=sh.n_kv, G=sh.G,
-                                scale=1.0 / math.sqrt(sh.d), cfg=cfg,
-                                transport=os.environ.get("LOCKS_CP_TRANSPORT",
-                                                         "peer"))
+    scale = 1.0 / math.sqrt(sh.d)
+    rec = {"workload": f"c4 context parallel: {layers} of 40 layers, "
+                       f"{sh.n_kv * sh.G}q/{sh.n_kv}kv, ONE sequence of ctx "
+                       f"{seq_len - 1} split over {world} GPU(s) by contiguous "
+                       f"page ranges, budget {sh.budget_pages}+{sh.sink_pages} "
+                       f"sink+{sh.window_pages} recent",
+           "scaling": "strong", "n_gpus": world, "layers": layers}
+
+    def run(transport, solo=False):
+        cp = ContextParallelHotPath(caches, bt, seq_len=seq_len, p0=p0, p1=p1,
+                                    n_kv=sh.n_kv, G=sh.G, scale=scale, cfg=cfg,
+                                    transport=transport,
+                                    group=None)
+        if solo:          # every rank alone on its range: no peer in the links
+            for d in cp._links:
+                d.world, d.rank = 1, 0
+                d.regions[0] = cp.link._peers[cp.link.rank]
+        return cp
+    cp = run("fused")
     t_build = timed(lambda: cp.build_all(), 1)
     cp.q.copy_(q)
     cp.capture()
-    for _ in range(max(args.warmup, 3)):
-        cp.step()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    e0 = torch.cuda.Event(enable_timing=True)
-    e1 = torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    e0.record()
-    for _ in range(args.steps):
-        cp.step()
-    e1.record()
-    torch.cuda.synchronize()
-    ms_step = e0.elapsed_time(e1) / args.steps
-    q_host = q.cpu().pin_memory()
-    out_host = torch.empty(cp.out.shape, dtype=torch.bfloat16).pin_memory()
-
-    def e2e_step():
-        cp.q.copy_(q_host, non_blocking=True)
-        cp.step()
-        out_host.copy_(cp.out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-
-    for _ in range(3):
-        e2e_step()
-    torch.cuda.synchronize()
-    e0.record()
-    for _ in range(args.steps):
-        e2e_step()
-    e1.record()
-    torch.cuda.synchronize()
-    ms_e2e = e0.elapsed_time(e1) / args.steps
-    if world > 1:
-        t = torch.tensor([ms_step, ms_e2e], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_step, ms_e2e = float(t[0].item()), float(t[1].item())
-        dist.barrier()
+    ms = _timed_steps(cp.step, args.steps, args.warmup, dev, world)
     status = int(cp.st.status.item())
-    clocks = sampler.stop() if rank == 0 else None
-    line = None
-    if rank == 0:
-        b_score, b_dec, b_dense, nsh, A = algo_bytes(sh, seq_len)
-        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-        peak = (float(json.load(open(peaks_path))["hbm_gbs"])
-                if os.path.exists(peaks_path) else 6650.0)
-        L = sh.n_layers
-        line = {
-            "metric": "sparse_decode_tokens_per_s", "value": 1.0 / (ms_step * 1e-3),
-            "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
-            "tpot_ms": ms_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"c4cp: {L} layers, {sh.n_kv * sh.G}q/"
-                                   f"{sh.n_kv}kv, d{sh.d}, page {sh.page}, ONE "
-                                   f"sequence of ctx {seq_len - 1} split over "
-                                   f"{world} GPU(s), budget {sh.budget_pages}+"
-                                   f"{sh.sink_pages} sink+{sh.window_pages} "
-                                   f"recent = {A} pages attended",
-                       "l2_policy": "inputs larger than L2 "
-                                    f"({(b_score + b_dec) / 1e9:.2f} GB per step)",
-                       "sharding": "contiguous page ranges; per layer: all-reduce"
-                                   "(max) of head maxima, all-gather of <= b "
-                                   "candidates, all-gather of split-K partials; "
-                                   f"transport {cp.transport}"},
-            "clocks": clocks,
-            "e2e": {"value": 1.0 / (ms_e2e * 1e-3), "unit": "tokens/s",
-                    "ms_per_step": ms_e2e,
-                    "h2d_bytes_per_step": q_host.numel() * 2,
-                    "d2h_bytes_per_step": out_host.numel() * 2},
-            "gpu_launches": 6 * L * args.steps,
-            "step_roofline": {
-                "algorithmic_bytes": b_score + b_dec,
-                "achieved_gbs": (b_score + b_dec) / (ms_step * 1e-3) / 1e9,
-                "frac_of_measured_peak_x_gpus":
-                    (b_score + b_dec) / (ms_step * 1e-3) / 1e9 / (peak * world)},
-            "us_per_layer": ms_step * 1e3 / L,
-            "build": {"bulk_ms": t_build},
-            "status_word": status,
-        }
-        print(json.dumps(line), flush=True)
-    sys.stdout.flush()
-    # leave without tearing NCCL down (graphs that captured collectives are alive)
-    os._exit(0)
+    rec.update({"us_per_layer": ms * 1e3 / layers, "ms_per_step": ms,
+                "launches_per_layer": 3, "status_word": status,
+                "build_bulk_ms": t_build})
+    recs = cp.st.pp_rec
+    # the streaming work alone (no exchange): same kernels, links to itself
+    solo = run("fused", solo=True)
+    solo.st.pp_rec.copy_(recs)
+    solo.q.copy_(q)
+    solo.capture()
+    ms_solo = _timed_steps(solo.step, args.steps, args.warmup, dev, world)
+    rec["us_per_layer_no_exchange"] = ms_solo * 1e3 / layers
+    rec["exchange_cost_us_per_layer"] = (ms - ms_solo) * 1e3 / layers
+    del solo
+    if world > 1:
+        old = run("peer")
+        old.st.pp_rec.copy_(recs)
+        old.q.copy_(q)
+        old.capture()
+        ms_old = _timed_steps(old.step, args.steps, args.warmup, dev, world)
+        rec["us_per_layer_separate_exchange_kernels"] = ms_old * 1e3 / layers
+        rec["status_word"] |= int(old.st.status.item())
+        del old
+    b_score, b_dec, _, _, A = algo_bytes(sh, seq_len)
+    peak, _ = _peak()
+    rec["step_roofline"] = {
+        "algorithmic_bytes": b_score + b_dec,
+        "achieved_gbs": (b_score + b_dec) / (ms * 1e-3) / 1e9,
+        "frac_of_measured_peak_x_gpus":
+            (b_score + b_dec) / (ms * 1e-3) / 1e9 / (peak * world)}
+    rec["gpu_launches_per_step"] = 3 * layers + 1
+    del cp, caches
+    torch.cuda.empty_cache()
+    # parity of a small context-parallel case against the single-GPU path,
+    # inside this run, on these ranks
+    if world > 1:
+        ok, err, msgs = check_against_single_gpu(seq_len=40005, n_layers=3)
+        rec["cp_parity"] = "ok" if ok else "FAILED: " + "; ".join(msgs)
+        rec["cp_parity_max_abs_err"] = err
+    else:
+        rec["cp_parity"] = "n/a (one rank: checked by the single-GPU tests)"
+    return rec
+
+
+def c2_record(args, dev, rank, world, full_line=False):
+    """The continuous-batching workload as the benchmark states it: 64 sequences
+    with seeded log-uniform context lengths in [4096, 262144], one page budget
+    per sequence from {32, 64, 128, 256}, block tables a random permutation of
+    the pool, 32 layers.  Sequences are dealt to the ranks by their step bytes
+    (no data-path collective).  The 32 layer launches walk over a few distinct
+    layer slabs (each far larger than L2) so that the pool stays within the
+    150 GB the workload names."""
+    import dataclasses
+    import torch.distributed as dist
+    from locks import LocksConfig, synth
+    from locks.hotpath import HotPath
+    from locks.parallel import shard_sequences
+    from locks.selection import rki4_score_only
+    sh = synth.CONFIG1
+    ctx, budgets = c2_draw()
+    lens = [c + 1 for c in ctx]
+    mine = shard_sequences(lens, budgets, world, sh.sink_pages,
+                           sh.window_pages)[rank]
+    my_lens = [lens[i] for i in mine]
+    my_budgets = [budgets[i] for i in mine]
+    tok = sum(my_lens)
+    slab_bytes = tok * sh.n_kv * sh.d * 2 * 2 * 1.12
+    free, _ = torch.cuda.mem_get_info()
+    n_slabs = int(max(1, min(8, (0.80 * free) // slab_bytes)))
+    if world > 1:
+        t = torch.tensor([n_slabs], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        n_slabs = int(t.item())
+    L = sh.n_layers
+    caches, q, bt, sl = make_device_case(sh, my_lens, dev, seed=4321 + rank,
+                                         n_slabs=n_slabs)
+    cfg = LocksConfig(budget_pages=max(budgets), sink_pages=sh.sink_pages,
+                      window_pages=sh.window_pages)
+    hp = HotPath(caches, bt, sl, n_kv=sh.n_kv, G=sh.G, scale=1.0 / math.sqrt(sh.d),
+                 cfg=cfg, budget_pages_req=my_budgets, launch_layers=L)
+    t_build = timed(lambda: hp.build_all(), 1)
+    hp.derive()
+    hp.q.copy_(q)
+    hp.capture()
+    torch.cuda.synchronize()
+    hp.st.check_status()
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    if rank == 0 and full_line:
+        sampler.start()
+    ms = _timed_steps(hp.step, args.steps, args.warmup, dev, world)
+    hp.st.check_status()
+    clocks = sampler.stop() if (rank == 0 and full_line) else None
+    # scorer alone (dominant kernel), graph of the L launches
+    st, R = hp.st, hp.n_req
+    for l in range(L):
+        rki4_score_only(st, l % n_slabs, hp.q[l, :R], bt, sl, R, hp.scale)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for l in range(L):
+            rki4_score_only(st, l % n_slabs, hp.q[l, :R], bt, sl, R, hp.scale)
+    ms_score = timed(g.replay, max(args.steps // 4, 8)) / L
+    st.hmax.zero_()
+    b_score, b_dec, b_dense, nsh, _ = algo_bytes(sh, my_lens, my_budgets)
+    tot = torch.tensor([float(b_score), float(b_dec), float(tok), float(len(mine)),
+                        ms_score], device=dev, dtype=torch.float64)
+    mx = tot.clone()
+    if world > 1:
+        dist.all_reduce(tot)
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+    peak, peak_src = _peak()
+    all_score, all_dec = float(tot[0]), float(tot[1])
+    rec = {
+        "workload": f"c2: {len(lens)} sequences, ctx {min(ctx)}..{max(ctx)} "
+                    f"(log-uniform, seeded), per-sequence budget_pages from "
+                    f"{{32,64,128,256}} + {sh.sink_pages} sink + "
+                    f"{sh.window_pages} recent, {L} layers cycling over "
+                    f"{n_slabs} distinct layer slabs, permuted block tables, "
+                    f"pool {n_slabs * slab_bytes * world / 1.12 / 1e9:.0f} GB",
+        "scaling": "strong (the same 64 sequences at every N)",
+        "n_gpus": world, "sequences_on_rank0": len(mine),
+        "tokens_per_s": len(lens) / (ms * 1e-3), "ms_per_step": ms,
+        "sharding": "whole sequences per GPU by step bytes "
+                    "(locks.parallel.shard_sequences), no collective",
+        "step_roofline": {
+            "algorithmic_bytes": all_score + all_dec,
+            "achieved_gbs": (all_score + all_dec) / (ms * 1e-3) / 1e9,
+            "frac_of_measured_peak_x_gpus":
+                (all_score + all_dec) / (ms * 1e-3) / 1e9 / (peak * world)},
+        "roofline": {"kernel": "rki4_score_kernel", "bound": "hbm",
+                     "achieved": b_score / L / (ms_score * 1e-3) / 1e9,
+                     "peak": peak, "unit": "GB/s",
+                     "frac": b_score / L / (ms_score * 1e-3) / 1e9 / peak,
+                     "traffic": (score_traffic_per_unit() or 0) * sh.n_kv * nsh
+                     or None,
+                     "peak_source": peak_src, "us_per_launch": ms_score * 1e3,
+                     "note": "rank 0's launch"},
+        "load_balance": {"max_rank_bytes": float(mx[0] + mx[1]),
+                         "mean_rank_bytes": (all_score + all_dec) / world},
+        "gpu_launches_per_step": hp.launches_per_step,
+        "build_bulk_ms": t_build,
+    }
+    if full_line:
+        rec["_clocks"] = clocks
+        rec["_hp"] = hp
+        rec["_case"] = (my_lens, my_budgets, sh)
+    else:
+        del hp, caches
+        torch.cuda.empty_cache()
+    return rec
 
 
 def run_gpu_mla(args, seq_len):
@@ -812,6 +952,69 @@ def run_gpu_mla(args, seq_len):
     }
 
 
+def c2_line(args, dev, rank, world):
+    """`--workload c2`: the ragged batch as a bench line of its own."""
+    rec = c2_record(args, dev, rank, world, full_line=True)
+    hp, clocks = rec.pop("_hp"), rec.pop("_clocks")
+    my_lens, my_budgets, sh = rec.pop("_case")
+    # end to end with host buffers: q, lengths and block table in, outputs back
+    hp.enable_host_io()
+    hp.host_q.copy_(hp.q[:, :hp.n_req].cpu())
+    hp.host_seq_lens.copy_(hp.seq_lens.cpu())
+    hp.host_block_table.copy_(hp.block_table.cpu())
+    for _ in range(3):
+        hp.step_host()
+    ms_e2e = _timed_steps(hp.step_host, args.steps, 0, dev, world)
+    h2d = hp.host_q.numel() * 2 + hp.host_seq_lens.numel() * 4 + \
+        hp.host_block_table.numel() * 4
+    d2h = hp.host_out.numel() * 2
+    cpu = None
+    if rank == 0 and not args.no_cpu_baseline:
+        # the oracle on ONE sampled sequence (the median length) with its own
+        # budget, one layer, scaled by the batch's share of step bytes
+        try:
+            import dataclasses
+            order = sorted(range(len(my_lens)), key=lambda i: my_lens[i])
+            i = order[len(order) // 2]
+            shs = dataclasses.replace(sh, budget_pages=my_budgets[i])
+            arm = CpuArm(shs, my_lens[i])
+            arm.step()
+            t_one = float(np.mean([arm.step() for _ in range(3)]))
+            bs, bd, _, _, _ = algo_bytes(shs, my_lens[i])
+            share = (bs + bd) / rec["step_roofline"]["algorithmic_bytes"]
+            cpu = {"value": 64 / (t_one / share), "unit": "tokens/s",
+                   "cores": os.cpu_count(), "kind": "port",
+                   "sample": f"sequence of {my_lens[i] - 1} tokens, budget "
+                             f"{my_budgets[i]}: " + arm.sample +
+                             f"; scaled by its {share:.4f} share of the batch's "
+                             "step bytes"}
+        except Exception as e:
+            cpu = {"value": None, "unit": "tokens/s", "cores": os.cpu_count(),
+                   "kind": "port", "sample": f"failed: {type(e).__name__}: {e}"}
+    if rank != 0:
+        return None
+    ms = rec["ms_per_step"]
+    return {
+        "metric": "sparse_decode_tokens_per_s", "value": rec["tokens_per_s"],
+        "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "tpot_ms": ms,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": rec["workload"],
+                   "l2_policy": "inputs larger than L2",
+                   "sharding": rec["sharding"]},
+        "clocks": clocks,
+        "e2e": {"value": 64 / (ms_e2e * 1e-3), "unit": "tokens/s",
+                "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": rec["gpu_launches_per_step"] * args.steps,
+        "roofline": rec["roofline"], "step_roofline": rec["step_roofline"],
+        "load_balance": rec["load_balance"],
+        "build": {"bulk_ms": rec["build_bulk_ms"]},
+        "cpu_baseline": cpu,
+    }
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -821,11 +1024,16 @@ def main():
     ap.add_argument("--workload", dest="workload_name", default="c1")
     ap.add_argument("--ctx", type=int, default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-partitioned", action="store_true",
+                    help="skip the c2_sharded and cp records of the default run")
     ap.add_argument("--layers", type=int, default=None,
                     help="override the layer count (quick experiments only)")
     args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.workload_name == "c3":
-        if int(os.environ.get("RANK", "0")) == 0:
+        if rank == 0:
             print(json.dumps(run_gpu_mla(args, (args.ctx or 131072) + 1)), flush=True)
         return
     sh, ctx = workload(args.workload_name, args.ctx)
@@ -833,18 +1041,54 @@ def main():
         import dataclasses
         sh = dataclasses.replace(sh, n_layers=args.layers)
     seq_len = [c + 1 for c in ctx] if isinstance(ctx, list) else ctx + 1
-    rank = int(os.environ.get("RANK", "0"))
     if args.impl == "reference":
         if rank != 0:
             return
         print(json.dumps(run_reference(args, sh, seq_len)), flush=True)
         return
-    if args.workload_name == "c4cp":
-        run_gpu_cp(args, sh, seq_len)
-        return
-    line = run_gpu(args, sh, seq_len)
+    import torch.distributed as dist
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if args.workload_name == "c2":
+        line = c2_line(args, dev, rank, world)
+    elif args.workload_name == "c4cp":
+        rec = cp_record(args, dev, rank, world, layers=args.layers or 8)
+        line = None
+        if rank == 0:
+            ms = rec["ms_per_step"]
+            line = {"metric": "sparse_decode_tokens_per_s", "value": 1e3 / ms,
+                    "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+                    "warmup": max(args.warmup, 3), "ms_per_step": ms,
+                    "higher_is_better": True, "scaling": "strong",
+                    "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                    "config": {"workload": rec["workload"]},
+                    "gpu_launches": rec["gpu_launches_per_step"] * args.steps,
+                    "cp": rec}
+    else:
+        line = run_gpu(args, sh, seq_len)
+        if args.workload_name == "c1" and not args.no_partitioned \
+                and not args.ctx and not args.layers:
+            import gc
+            gc.collect()
+            torch.cuda.empty_cache()
+            extra = {}
+            for name, fn in (("cp", cp_record), ("c2_sharded", c2_record)):
+                try:
+                    extra[name] = fn(args, dev, rank, world)
+                except Exception as e:   # a side record must not sink the line
+                    extra[name] = {"failed": f"{type(e).__name__}: {e}"}
+                gc.collect()
+                torch.cuda.empty_cache()
+            if line is not None:
+                line.update(extra)
     if line is not None:
         print(json.dumps(line), flush=True)
+    sys.stdout.flush()
+    sys.stderr.flush()
+    # leave without tearing the process group and the IPC mappings down
+    os._exit(0)
 
 
 if __name__ == "__main__":

@@ -314,3 +314,92 @@ class ContextParallelHotPath:
             self.capture()
         self.graph.replay()
         return self.out
+
+
+def check_against_single_gpu(*, seq_len: int = 40005, n_layers: int = 3,
+                             transport: str = "fused", group=None, seed: int = 11):
+    """Self-check of a context-parallel set-up, run by ALL ranks of ``group``:
+    one seeded sequence (2 KV heads x 16 query heads, budget 64 + 1 sink + 8
+    recent pages) is decoded context-parallel -- eagerly and as a replayed graph
+    -- and rank 0 compares it with the single-GPU hot path on the whole
+    sequence: the union of the ranks' attended pages must EQUAL the single-GPU
+    page table of the last layer, the outputs must agree within the decode
+    tolerance (2e-2; bf16 outputs, different merge order), eager and graph
+    outputs must be identical and no wait may have run out.
+    Returns ``(ok, max_abs_err, messages)`` (the same on every rank)."""
+    import math
+    from . import synth
+    from .hotpath import HotPath
+    from .parallel import partition_pages
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    dev = torch.device("cuda", torch.cuda.current_device())
+    shape = synth.GqaShape(n_layers=n_layers, n_kv=2, G=16, d=128, page=16,
+                           budget_pages=64, sink_pages=1, window_pages=8,
+                           n_needles=6, n_outlier=4)
+    cfg = LocksConfig(budget_pages=shape.budget_pages, sink_pages=shape.sink_pages,
+                      window_pages=shape.window_pages)
+    scale = 1.0 / math.sqrt(shape.d)
+    npg = -(-seq_len // shape.page)
+    p0, p1 = partition_pages(npg, world)[rank]
+    caches, q, bt = synth.make_gqa_shard(seed, shape, seq_len, p0, p1, device=dev)
+    cp = ContextParallelHotPath(caches, bt, seq_len=seq_len, p0=p0, p1=p1,
+                                n_kv=shape.n_kv, G=shape.G, scale=scale, cfg=cfg,
+                                group=group, transport=transport)
+    cp.build_all()
+    cp.q.copy_(q)
+    out_eager = cp.step_eager().clone()
+    torch.cuda.synchronize()
+    cnt = cp.st.page_cnt[0].tolist()
+    mine = [(cp.st.page_table[0, kh, :cnt[kh]] + p0).tolist()
+            for kh in range(shape.n_kv)]
+    gathered = [mine]
+    if world > 1:
+        gathered = [None] * world
+        dist.all_gather_object(gathered, mine, group=group)
+    out_graph = cp.step().clone()
+    cp.step()
+    torch.cuda.synchronize()
+    msgs, ok, err = [], True, 0.0
+    if not torch.equal(out_graph, cp.out):
+        msgs.append(f"[rank {rank}] graph replay is not repeatable"); ok = False
+    if (out_graph.float() - out_eager.float()).abs().max().item() > 0:
+        msgs.append(f"[rank {rank}] graph and eager outputs differ"); ok = False
+    status = int(cp.st.status.item())
+    if status:
+        msgs.append(f"[rank {rank}] kernel status word {status}"); ok = False
+    if rank == 0:
+        fc, fq, fbt = synth.make_gqa_shard(seed, shape, seq_len, 0, npg, device=dev)
+        sl = torch.tensor([seq_len], dtype=torch.int32, device=dev)
+        hp = HotPath(fc, fbt, sl, n_kv=shape.n_kv, G=shape.G, scale=scale, cfg=cfg)
+        hp.build_all(); hp.derive(); hp.q.copy_(fq)
+        ref = hp.step_eager().clone()
+        torch.cuda.synchronize()
+        rc = hp.st.page_cnt[0].tolist()
+        for kh in range(shape.n_kv):
+            want = hp.st.page_table[0, kh, :rc[kh]].tolist()
+            got = sorted(p for r in range(world) for p in gathered[r][kh])
+            if got != want:
+                extra = sorted(set(got) - set(want))[:5]
+                miss = sorted(set(want) - set(got))[:5]
+                msgs.append(f"kv head {kh}: page sets differ ({len(got)} vs "
+                            f"{len(want)}; extra {extra}, missing {miss})")
+                ok = False
+        err = (out_eager.float() - ref.float()).abs().max().item()
+        if not err <= 2e-2:
+            msgs.append(f"max |out - single GPU| = {err:.3e}"); ok = False
+        del hp, fc
+    res = [ok, err, msgs]
+    if world > 1:
+        flag = torch.tensor([0 if ok else 1], device=dev)
+        dist.all_reduce(flag, group=group)
+        res[0] = int(flag.item()) == 0
+        box = [res if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0, group=group)
+        res = [res[0], box[0][1], box[0][2] + ([] if rank == 0 else msgs)]
+    if cp.link is not None:
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier(group=group)       # nobody closes while a peer still stores
+        cp.link.close()
+    return tuple(res)

@@ -26,7 +26,13 @@ class HotPath:
     def __init__(self, kv_caches: List[torch.Tensor], block_table: torch.Tensor,
                  seq_lens: torch.Tensor, *, n_kv: int, G: int, scale: float,
                  cfg: LocksConfig, max_reqs: Optional[int] = None,
-                 split_cap: int = 128, budget_pages_req=None):
+                 split_cap: int = 128, budget_pages_req=None,
+                 launch_layers: Optional[int] = None):
+        """``launch_layers``: run that many layer launches per step, cycling
+        over the ``kv_caches`` given (layer launch l uses cache l % len): a
+        benchmark whose full set of layer slabs would not fit in memory keeps
+        a few distinct slabs -- each far larger than L2 -- and walks them in
+        turn.  q / out are per launch."""
         dev = kv_caches[0].device
         self.device = dev
         self.cfg = cfg
@@ -38,6 +44,7 @@ class HotPath:
         NB, _, page, _, d = kv_caches[0].shape
         self.page, self.d = int(page), int(d)
         L = len(kv_caches)
+        self.launch_layers = int(launch_layers or L)
         st = Rki4State(dev, num_layers=L, num_blocks=int(NB), n_kv=n_kv, G=G,
                        head_dim=int(d), page=int(page),
                        max_reqs=max_reqs or self.n_req,
@@ -57,8 +64,9 @@ class HotPath:
         self.K_layers = [c[:, 0] for c in kv_caches]
         self.vsources = [ResidentVSource(c) for c in kv_caches]
         H = n_kv * G
-        self.q = torch.zeros(L, st.max_reqs, H, d, device=dev, dtype=torch.bfloat16)
-        self.out = torch.zeros(L, st.max_reqs, H, d, device=dev, dtype=torch.bfloat16)
+        LL = self.launch_layers
+        self.q = torch.zeros(LL, st.max_reqs, H, d, device=dev, dtype=torch.bfloat16)
+        self.out = torch.zeros(LL, st.max_reqs, H, d, device=dev, dtype=torch.bfloat16)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.launches_per_step = 0
 
@@ -79,13 +87,15 @@ class HotPath:
     # ---- one decode step ---------------------------------------------------
     def _layers(self) -> None:
         st, R = self.st, self.n_req
-        for l, kvc in enumerate(self.kv_caches):
+        n = len(self.kv_caches)
+        for l in range(self.launch_layers):
+            kvc = self.kv_caches[l % n]
             q = self.q[l, :R]
             _runtime._rki4_select_adapter(q, kvc, self.block_table,
                                           self.seq_lens, st, R, self.scale,
                                           self.cfg)
             _runtime.decode_dispatch(q, kvc, self.block_table, self.seq_lens, st,
-                                     self.out[l], self.vsources[l], self.scale,
+                                     self.out[l], self.vsources[l % n], self.scale,
                                      self.cfg)
 
     def step_eager(self) -> torch.Tensor:
