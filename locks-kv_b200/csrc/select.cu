@@ -330,22 +330,27 @@ __device__ __forceinline__ void sweep_max_groups(
     } while (0)
 
 // Context parallel, after the local selection with the sequence's budget: this
-// rank's selected pages meet those of the other ranks.  One CTA per kv-head:
-//   1. entry j < cap of the local table becomes a candidate packet pair
-//      {score key, global page}; forced pages and empty slots travel as key 0;
+// rank's selected pages meet those of the other ranks.  One CTA per kv-head.  The
+// local selection left its kept pages -- ascending, with their class-folded keys
+// (0xFFFFFFFF = forced page) -- in CTA 0's shared memory instead of the table:
+//   1. entry j becomes a candidate packet pair {score key, global page}; forced
+//      pages and empty slots travel as key 0;
 //   2. the candidates of all ranks are polled into shared memory;
 //   3. a candidate stays when fewer than b candidates of ALL ranks beat it by
 //      (key descending, page ascending) -- counted directly, world * cap entries
 //      are a few thousand at most;
-//   4. the table is rewritten in place: forced pages + surviving candidates,
-//      ascending, -1 behind them, the count.
-// scratch: cap + 2 * world * cap words of shared memory.
+//   4. the table is written once: forced pages + surviving candidates,
+//      ascending, -1 behind them up to the local count, and the final count.
+// scratch (words): keep[cap] | ckey[world*cap] | cpage[world*cap] | lkey[cap] |
+// lpage[cap]; the last two are the local list.
+__device__ __forceinline__ uint32_t* cp_list_keys(uint32_t* scratch, int cap, int W) {
+    return scratch + cap + 2 * W * cap;
+}
 template <int NT>
 __device__ __forceinline__ void cp_global_cut(const CpLink& cp, int kh,
                                               int32_t* tab, int32_t* cnt_out,
-                                              const float* score, int cnt,
-                                              uint32_t* scratch, int* wsum,
-                                              int* status) {
+                                              int cnt, uint32_t* scratch,
+                                              int* wsum, int* status) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int NW = NT / 32;
     const int cap = cp.cap, W = cp.world;
@@ -353,14 +358,15 @@ __device__ __forceinline__ void cp_global_cut(const CpLink& cp, int kh,
     int* keep_sh = reinterpret_cast<int*>(scratch);
     uint32_t* ckey = scratch + cap;
     int32_t* cpage = reinterpret_cast<int32_t*>(ckey + W * cap);
+    const uint32_t* lkey = cp_list_keys(scratch, cap, W);
+    const int32_t* lpage = reinterpret_cast<const int32_t*>(lkey + cap);
     for (int j = tid; j < cap; j += NT) {
-        const int e = (j < cnt) ? tab[j] : -1;
-        const bool sel = e >= cp.sink_loc && e < cp.nsh_loc;
-        const uint32_t key = sel ? min(max(f2key(score[e]), 1u), 0xFFFFFFFEu) : 0u;
+        const uint32_t k0 = (j < cnt) ? lkey[j] : 0u;
+        const bool sel = k0 != 0u && k0 != 0xFFFFFFFFu;
         const int idx = (kh * cap + j) * 2;
-        cp_push(cp, cp.off_cand, cp.cand_words, epoch, idx, key);
+        cp_push(cp, cp.off_cand, cp.cand_words, epoch, idx, sel ? k0 : 0u);
         cp_push(cp, cp.off_cand, cp.cand_words, epoch, idx + 1,
-                (uint32_t)(sel ? e + cp.p0 : 0x7FFFFFFF));
+                (uint32_t)(sel ? lpage[j] + cp.p0 : 0x7FFFFFFF));
     }
     bool late = false;
     const uint8_t* mine = cp.base[cp.rank];
@@ -398,22 +404,20 @@ __device__ __forceinline__ void cp_global_cut(const CpLink& cp, int kh,
     if (late && status) atomicExch(status, LOCKS_ST_WAIT_TIMEOUT);
     __syncthreads();
     for (int j = warp; j < cap; j += NW) {
-        const int e = (j < cnt) ? tab[j] : -1;
-        const bool live = e >= 0;
-        const bool sel = live && e >= cp.sink_loc && e < cp.nsh_loc;
-        int keep = live ? 1 : 0;
+        const uint32_t k0 = (j < cnt) ? lkey[j] : 0u;
+        const bool sel = k0 != 0u && k0 != 0xFFFFFFFFu;
+        int keep = (k0 != 0u) ? 1 : 0;                      // forced pages stay
         if (sel) {                                          // warp-uniform
-            const uint32_t key = ckey[cp.rank * cap + j];
-            const int pg = cpage[cp.rank * cap + j];
+            const int pg = lpage[j] + cp.p0;
             int beat = 0;
             for (int c = lane; c < W * cap; c += 32) {
                 const uint32_t k2 = ckey[c];
-                beat += (k2 > key || (k2 == key && k2 != 0u && cpage[c] < pg)) ? 1 : 0;
+                beat += (k2 > k0 || (k2 == k0 && cpage[c] < pg)) ? 1 : 0;
             }
 #pragma unroll
             for (int o = 16; o >= 1; o >>= 1)
                 beat += __shfl_xor_sync(0xffffffffu, beat, o);
-            keep = (beat < cp.b_global && key != 0u) ? 1 : 0;
+            keep = (beat < cp.b_global) ? 1 : 0;
         }
         if (lane == 0) keep_sh[j] = keep;
     }
@@ -422,7 +426,6 @@ __device__ __forceinline__ void cp_global_cut(const CpLink& cp, int kh,
     for (int j0 = 0; j0 < cap; j0 += NT) {
         const int j = j0 + tid;
         const int k = (j < cap) ? keep_sh[j] : 0;
-        const int e = (j < cnt) ? tab[j] : -1;
         int inc = k;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -430,14 +433,14 @@ __device__ __forceinline__ void cp_global_cut(const CpLink& cp, int kh,
             if (lane >= o) inc += t;
         }
         if (lane == 31) wsum[warp] = inc;
-        __syncthreads();                                    // all reads of tab[j0..] done
+        __syncthreads();
         int wbase = 0, total = 0;
         for (int w = 0; w < NW; ++w) {
             const int v = wsum[w];
             if (w < warp) wbase += v;
             total += v;
         }
-        if (k) tab[base + wbase + inc - 1] = e;             // slot <= j: never ahead of a reader
+        if (k) tab[base + wbase + inc - 1] = lpage[j];
         base += total;
         __syncthreads();
     }
@@ -692,6 +695,13 @@ topb_kernel(const SelParams p) {
         else { tau_key = prefix; quota = k; }
     }
 
+    // context parallel: where the kept (key, page) list lives (CTA 0 of the row)
+    uint32_t* cpl_key = nullptr;
+    if constexpr (CP) {
+        uint32_t* l0 = cp_list_keys(reinterpret_cast<uint32_t*>(h4), p.cp.cap,
+                                    p.cp.world);
+        cpl_key = (CL > 1) ? cluster.map_shared_rank(l0, 0) : l0;
+    }
     // ---- 3. keep flags + ascending compaction.  Warp w owns a contiguous run of
     // keys and walks it 128 keys at a time.
     const uint32_t lt_mask = (1u << lane) - 1u;
@@ -787,7 +797,20 @@ topb_kernel(const SelParams p) {
         }
 #pragma unroll
         for (int s = 0; s < 4; ++s) {
-            if (keep[s]) tab[slot++] = s0 + base + s;
+            if (keep[s]) {
+                if constexpr (CP) {
+                    // context parallel: the kept pages and their keys go to the
+                    // list in CTA 0's shared memory; the table is written once,
+                    // after the ranks' selections have met
+                    if (slot < p.cp.cap) {
+                        cpl_key[slot] = kk[s];
+                        cpl_key[slot + p.cp.cap] = (uint32_t)(s0 + base + s);
+                    }
+                    ++slot;
+                } else {
+                    tab[slot++] = s0 + base + s;
+                }
+            }
         }
         pos += total;
     }
@@ -812,8 +835,7 @@ topb_kernel(const SelParams p) {
         if (c == 0 && cnt > p.cp.cap && tid == 0 && p.status)
             atomicExch(p.status, LOCKS_ST_CP_OVERFLOW);     // caller sized cap too small
         if (c == 0)
-            cp_global_cut<NT>(p.cp, kh, tab, &p.page_cnt[row], score,
-                              min(cnt, p.cp.cap),
+            cp_global_cut<NT>(p.cp, kh, tab, &p.page_cnt[row], min(cnt, p.cp.cap),
                               reinterpret_cast<uint32_t*>(h4), sm.wtot, p.status);
     }
 }
@@ -941,7 +963,7 @@ static int topb_select_impl(
                       "scorer's published maxima are required");
         const int rc = cp_link_fill(p.cp, link, n_kv, G, "locks_topb_select_cp");
         if (rc) return rc;
-        LOCKS_REQUIRE(p.cp.cap + 2 * p.cp.world * p.cp.cap <= HSLOTS * HCOPIES,
+        LOCKS_REQUIRE(3 * p.cp.cap + 2 * p.cp.world * p.cp.cap <= HSLOTS * HCOPIES,
                       LOCKS_ERR_SIZE,
                       "locks_topb_select_cp: %d candidate slots x %d ranks beyond "
                       "the shared-memory staging area", p.cp.cap, p.cp.world);
