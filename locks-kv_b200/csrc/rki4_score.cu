@@ -159,22 +159,47 @@ rki4_score_kernel(const ScoreParams p) {
     int z = blockIdx.x, Z = gridDim.x, r = blockIdx.z;
     if (p.ragged) {
         // Ragged batch: the gridDim.x CTAs of a kv-head are dealt to the requests
-        // in proportion to their chunk counts (every request gets one, the rest
-        // go by share), so a 4K-token row and a 70K-token row finish together.
-        const int R = p.n_req, Zt = (int)gridDim.x, cap0 = min(p.max_pages, p.bt_width);
+        // in proportion to their chunk counts (every request gets one, the other
+        // `extra` go by share), so a 4K-token row and a 70K-token row finish
+        // together.  Every lane walks requests lane, lane + 32, ...; the CTA's
+        // request is the one whose run of CTAs contains blockIdx.x.
+        const int R = p.n_req, cap0 = min(p.max_pages, p.bt_width);
+        const int extra = (int)gridDim.x - R, b = (int)blockIdx.x;
         int total = 0;
-        for (int i = 0; i < R; ++i)
+        for (int i = lane; i < R; i += 32)
             total += (min(max(p.n_sel_hi[i], 0), cap0) + CHUNK - 1) / CHUNK;
-        const int extra = Zt - R, b = (int)blockIdx.x;
-        int acc = 0;
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1)
+            total += __shfl_xor_sync(0xffffffffu, total, o);
+        // request i owns CTAs [i + floor(extra * c_before / total),
+        //                      i + 1 + floor(extra * c_through / total)):
+        // the runs tile the grid exactly, whatever the rounding
+        int acc = 0;                                        // chunks of requests < i0
         r = -1;
-        for (int i = 0; i < R; ++i) {
-            const int ci = (min(max(p.n_sel_hi[i], 0), cap0) + CHUNK - 1) / CHUNK;
-            const int Zi = 1 + (int)(((int64_t)extra * ci) / max(total, 1));
-            if (b < acc + Zi) { r = i; z = b - acc; Z = Zi; break; }
-            acc += Zi;
+        for (int i0 = 0; i0 < R && r < 0; i0 += 32) {
+            const int i = i0 + lane;
+            const int ci = (i < R)
+                ? (min(max(p.n_sel_hi[i], 0), cap0) + CHUNK - 1) / CHUNK : 0;
+            int inc = ci;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += t;
+            }
+            const int64_t c_before = acc + inc - ci, c_through = acc + inc;
+            const int beg = i + (int)((extra * c_before) / max(total, 1));
+            const int end = i + 1 + (int)((extra * c_through) / max(total, 1));
+            const bool hit = i < R && b >= beg && b < end;
+            const uint32_t m = __ballot_sync(0xffffffffu, hit);
+            if (m) {
+                const int src = __ffs(m) - 1;
+                r = i0 + src;
+                z = b - __shfl_sync(0xffffffffu, beg, src);
+                Z = __shfl_sync(0xffffffffu, end - beg, src);
+            }
+            acc += __shfl_sync(0xffffffffu, inc, 31);
         }
-        if (r < 0) return;                       // CTAs left over by the rounding
+        if (r < 0) return;                       // (no request: an empty batch)
     }
     const int gid = lane >> 2, tig = lane & 3;
     const int G = p.G;
@@ -523,8 +548,12 @@ extern "C" int locks_rki4_score_bt(
     Z = max(1, min(Z, min(max_z, 65535)));
     // several requests (of possibly very different lengths) and room for at least
     // two CTAs each: share the CTAs of a kv-head by length
-    const int Zt = (CTAS_PER_SM * sm_count()) / max(1, n_kv);
-    const bool ragged = zsplit <= 0 && n_req > 1 && n_req <= 64 && 2 * n_req <= Zt;
+    // (a few requests: one wave in all; many requests: one CTA each plus a whole
+    // wave dealt by length -- the short rows' CTAs retire at once and the long
+    // rows still get their share of the resident slots)
+    const int slots = (CTAS_PER_SM * sm_count()) / max(1, n_kv);
+    const int Zt = (4 * n_req <= slots) ? slots : n_req + slots;
+    const bool ragged = zsplit <= 0 && n_req > 1 && n_req <= 1024;
 
     ScoreParams p;
     p.q = static_cast<const __nv_bfloat16*>(q);
