@@ -213,24 +213,151 @@ class CpuArm:
         return sh.n_layers * ((t1 - t0) * self.page_ratio + (t2 - t1))
 
 
+class RefArm:
+    """The reference's OWN CPU code, staged under ``oracle/_ref`` by
+    ``oracle/make_ref.py``: its ``Rki4State("cpu")``, ``rki4_build_bulk``
+    (LAPACK eigh; untimed set-up), and per step ``derive_page_params`` (its
+    Triton kernel, interpreted), ``rki4_score_torch``, the nrm combine (three
+    torch lines restating ``select_cuda.py:607-658``, as the golden generator
+    does) and ``_topb_select_torch``, at the workload's FULL context.  The
+    sparse decode + merge has no CPU implementation in the reference (Triton /
+    CUDA only): that part is the numpy restatement.  A step = `layers` layers
+    (each with its own seeded K/V), scaled to the workload's layer count."""
+
+    def __init__(self, sh, seq_len, layers=1, seed=1234):
+        os.environ.setdefault("TRITON_INTERPRET", "1")
+        ref_root = os.path.join(ROOT, "oracle", "_ref")
+        if ref_root not in sys.path:
+            sys.path.insert(0, ref_root)
+        from locks_ref.selection import rki4_build as rb
+        from locks_ref.selection.rki4_score_torch import rki4_score_torch
+        from locks_ref.selection.rki4_state import Rki4State
+        from locks_ref.selection.select import (_topb_select_torch,
+                                                derive_page_params)
+        import locks_oracle as orc
+        from locks import synth
+        self.orc, self.sh, self.layers = orc, sh, layers
+        self._score, self._select, self._derive = (rki4_score_torch,
+                                                   _topb_select_torch,
+                                                   derive_page_params)
+        case = synth.make_gqa_case(seed, sh, [seq_len], device="cpu",
+                                   n_layers=layers)
+        self.case = case
+        G = sh.G
+        if G > 8:          # the reference asserts G <= 8; its CPU code is G-generic
+            Rki4State.validate_geometry = staticmethod(lambda **kw: None)
+        st = Rki4State("cpu", num_layers=layers, num_blocks=case.num_blocks,
+                       n_kv=sh.n_kv, G=G, head_dim=sh.d, page=sh.page, max_reqs=1,
+                       max_pages=case.max_pages, budget_pages=sh.budget_pages,
+                       sink_pages=sh.sink_pages, window_pages=sh.window_pages,
+                       combine="nrm")
+        K_layers = [c[:, 0] for c in case.kv_caches]
+        settled = case.seq_lens - 1
+        rb.rki4_build_bulk(st, K_layers, case.block_table, settled, 1,
+                           int((settled // sh.page).max()))
+        self.st = st
+        f = lambda t: t.float().numpy()
+        self.bt, self.sl = case.block_table.numpy(), case.seq_lens.numpy()
+        self.Kc = [f(c[:, 0]) for c in case.kv_caches]
+        self.Vc = [f(c[:, 1]) for c in case.kv_caches]
+        self.qf = [f(case.q[l]) for l in range(layers)]
+        self.sample = (f"{layers} of {sh.n_layers} layers at the full context "
+                       f"({seq_len - 1} tokens), time x{sh.n_layers / layers:g}; "
+                       "reference torch code for page parameters, scoring and "
+                       "selection (oracle/_ref), numpy restatement for the "
+                       "decode + merge it has no CPU code for; summaries prebuilt")
+
+    def step(self):
+        """Seconds the sampled layers took."""
+        st, sh, case, orc = self.st, self.sh, self.case, self.orc
+        t0 = time.perf_counter()
+        self._derive(st, case.seq_lens, 1)
+        for l in range(self.layers):
+            self._score(st, l, case.q[l], case.block_table, case.seq_lens, 1,
+                        case.scale)
+            hi = int(st.n_sel_hi[0])
+            hm = st.score_h[0, :, :, :hi].amax(-1, keepdim=True)
+            acc = torch.zeros(sh.n_kv, hi)
+            for g in range(sh.G):
+                acc = acc + torch.exp(st.score_h[0, :, g, :hi] - hm[:, g])
+            st.score[0, :, :hi] = acc
+            self._select(st, 1)
+            tab, cnt = st.page_table.numpy(), st.page_cnt.numpy()
+            m, lse, a = orc.sparse_decode_split(
+                self.qf[l], self.Kc[l], self.Vc[l], self.bt, tab, cnt, self.sl,
+                case.scale, sh.n_kv, sh.G, 64, 2)
+            orc.merge_splits(m, lse, a, cnt, 64, 2)
+        return time.perf_counter() - t0
+
+
+def reference_available() -> bool:
+    return os.path.exists(os.path.join(ROOT, "oracle", "_ref", "locks_ref",
+                                       "selection", "rki4_score_torch.py"))
+
+
+def workload_config(args, sh, seq_len):
+    """The `config` object both arms print for a single-sequence workload."""
+    A = min(sh.budget_pages, max(-(-seq_len // sh.page) - sh.window_pages
+                                 - sh.sink_pages, 0)) + sh.sink_pages \
+        + sh.window_pages
+    b_score, b_dec, _, _, _ = algo_bytes(sh, seq_len)
+    return {"workload": f"{args.workload_name}: {sh.n_layers} layers, "
+                        f"{sh.n_kv * sh.G}q/{sh.n_kv}kv, d{sh.d}, page {sh.page}, "
+                        f"bs1 per GPU, ctx {seq_len - 1}, budget "
+                        f"{sh.budget_pages}+{sh.sink_pages} sink+"
+                        f"{sh.window_pages} recent = {A} pages attended",
+            "l2_policy": "inputs larger than L2 "
+                         f"({(b_score + b_dec) / 1e9:.2f} GB touched per step)",
+            "sharding": "whole sequences per GPU, no collective"}
+
+
 def run_reference(args, sh, seq_len):
+    """`--impl reference`: the reference's CPU implementation of the path on the
+    host cores.  A step is a bounded sample (see RefArm / CpuArm); `ms_per_step`
+    is the measured time of that sample, `value` the tokens/s of the whole
+    workload it implies (sample time x layer ratio)."""
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    arm = CpuArm(sh, seq_len)
+    if isinstance(seq_len, (list, tuple)):
+        seq_len = sorted(seq_len)[len(seq_len) // 2]       # ragged: median length
+    if reference_available():
+        arm, kind = RefArm(sh, seq_len, layers=1), "reference"
+        scale = sh.n_layers / arm.layers
+        full = lambda t: t * scale
+    else:
+        arm, kind = CpuArm(sh, seq_len), "port"
+        full = lambda t: t                 # CpuArm.step already returns full-job s
+        arm_step = arm.step
+        # the sample's own wall time, for ms_per_step
+        def timed_step():
+            t0 = time.perf_counter()
+            v = arm_step()
+            return time.perf_counter() - t0, v
     for _ in range(args.warmup):
         arm.step()
-    per_step = [arm.step() for _ in range(args.steps)]
-    tpot = float(np.mean(per_step))
+    samples, fulls = [], []
+    for _ in range(args.steps):
+        if kind == "reference":
+            t = arm.step()
+            samples.append(t)
+            fulls.append(full(t))
+        else:
+            t, v = timed_step()
+            samples.append(t)
+            fulls.append(v)
+    tpot = float(np.mean(fulls))
+    ms_sample = float(np.mean(samples)) * 1e3
     return {
         "impl": "reference", "metric": "sparse_decode_tokens_per_s",
         "value": 1.0 / tpot, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": tpot * 1e3, "tpot_ms": tpot * 1e3,
+        "ms_per_step": ms_sample, "tpot_ms": tpot * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload_name, "ctx": seq_len - 1},
+        "config": workload_config(args, sh, seq_len),
         "cpu_baseline": {"value": 1.0 / tpot, "unit": "tokens/s",
-                         "cores": cores, "kind": "port", "sample": arm.sample},
+                         "cores": cores, "kind": kind, "sample": arm.sample,
+                         "tpot_ms": tpot * 1e3},
         "e2e": {"value": 1.0 / tpot, "unit": "tokens/s",
                 "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -522,14 +649,18 @@ def run_gpu(args, sh, seq_len):
     cpu = None
     ragged = isinstance(seq_len, (list, tuple))
     if not args.no_cpu_baseline and world == 1 and not ragged:
+        # the reference arm, run as a process of its own on the host cores (its
+        # Triton interpreter switch and thread settings stay out of this one)
         try:
-            cores = os.cpu_count() or 1
-            arm = CpuArm(sh, seq_len)
-            arm.step()
-            t_cpu = float(np.mean([arm.step() for _ in range(10)]))
-            cpu = {"value": 1.0 / t_cpu, "unit": "tokens/s", "cores": cores,
-                   "kind": "port", "sample": arm.sample + "; mean of 10",
-                   "tpot_ms": t_cpu * 1e3}
+            cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference",
+                   "--workload", args.workload_name, "--steps", "5", "--warmup",
+                   "1"] + (["--ctx", str(args.ctx)] if args.ctx else []) \
+                + (["--layers", str(args.layers)] if args.layers else [])
+            r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+            ref = json.loads([ln for ln in r.stdout.splitlines()
+                              if ln.startswith("{")][-1])
+            cpu = ref["cpu_baseline"]
+            cpu["sample"] += "; mean of 5"
         except Exception as e:   # the baseline must not sink the GPU number
             cpu = {"value": None, "unit": "tokens/s", "cores": os.cpu_count(),
                    "kind": "port", "sample": f"failed: {type(e).__name__}: {e}"}
@@ -541,18 +672,7 @@ def run_gpu(args, sh, seq_len):
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
         "tpot_ms": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{args.workload_name}: {L} layers, "
-                               f"{sh.n_kv * sh.G}q/{sh.n_kv}kv, d{sh.d}, page "
-                               f"{sh.page}, "
-                               + (f"ragged batch of {len(seq_len)} per GPU, ctx "
-                                  f"{min(seq_len) - 1}..{max(seq_len) - 1}, "
-                                  if isinstance(seq_len, (list, tuple)) else
-                                  f"bs1 per GPU, ctx {seq_len - 1}, ") +
-                               f"budget {sh.budget_pages}+{sh.sink_pages} sink+"
-                               f"{sh.window_pages} recent = {A} pages attended",
-                   "l2_policy": "inputs larger than L2 "
-                                f"({step_bytes / 1e9:.2f} GB touched per step)",
-                   "sharding": "whole sequences per GPU, no collective"},
+        "config": workload_config(args, sh, seq_len),
         "clocks": clocks,
         "e2e": {"value": world * R / (ms_e2e * 1e-3), "unit": "tokens/s",
                 "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
