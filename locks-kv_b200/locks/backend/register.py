@@ -46,6 +46,39 @@ def _swap_path(path):
     return path
 
 
+def _bracket_profiling_runs() -> None:
+    """Mark the engine's memory-profiling dummy runs (they use a throw-away
+    minimal KV cache) so that the builder does not latch its state on them:
+    ``GPUModelRunner.profile_cudagraph_memory`` and ``_dummy_run(is_profile=
+    True)`` are wrapped to raise the runtime's profiling flag for their
+    duration (reference ``backend/register.py:340-393``).  Absent methods are
+    skipped: the builder also re-checks the latched cache pointers itself."""
+    try:
+        from vllm.v1.worker.gpu_model_runner import GPUModelRunner as MR
+    except Exception as exc:                       # pragma: no cover
+        print(f"[locks] profiling-window bracket skipped ({exc})", flush=True)
+        return
+
+    def wrap(name, only_if=None):
+        orig = getattr(MR, name, None)
+        if orig is None or getattr(orig, "_locks_wrapped", False):
+            return
+
+        def wrapped(self, *args, **kwargs):
+            if only_if is not None and not only_if(args, kwargs):
+                return orig(self, *args, **kwargs)
+            _runtime.set_profiling(True)
+            try:
+                return orig(self, *args, **kwargs)
+            finally:
+                _runtime.set_profiling(False)
+        wrapped._locks_wrapped = True
+        setattr(MR, name, wrapped)
+
+    wrap("profile_cudagraph_memory")
+    wrap("_dummy_run", only_if=lambda a, kw: bool(kw.get("is_profile")))
+
+
 def register(overrides: dict | None = None) -> None:
     """Runs in every engine / worker process; no device work."""
     global _APPLIED
@@ -77,6 +110,7 @@ def register(overrides: dict | None = None) -> None:
         return new
 
     target.get_attn_backend_cls = classmethod(get_attn_backend_cls)
+    _bracket_profiling_runs()
     _APPLIED = True
     print("[locks] registered (patched CudaPlatform.get_attn_backend_cls)",
           flush=True)
