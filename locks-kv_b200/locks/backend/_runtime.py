@@ -133,11 +133,22 @@ def dump_layer(lidx, q, kv_cache, block_table, seq_lens, st, out, n_req) -> None
     torch.cuda.synchronize()
     c = lambda t: t.detach().float().cpu() if t.dtype == torch.bfloat16 \
         else t.detach().cpu()
+    # only the blocks the rows use travel, renumbered 0..n-1 (the engine's cache
+    # holds every block of the pool)
+    page = int(st.page)
+    sl = seq_lens[:n_req]
+    npg = int((int(sl.max().item()) + page - 1) // page)
+    bt = block_table[:n_req, :npg].long()
+    used, inv = torch.unique(bt.reshape(-1), return_inverse=True)
+    bt_small = inv.reshape(n_req, npg).to(torch.int32)
+    from ..attention.decode import _split_kv
+    k, v = _split_kv(kv_cache)
     _DUMP["layers"][int(lidx)] = {
-        "q": c(q[:n_req]), "out": c(out[:n_req]), "kv_cache": c(kv_cache),
-        "records": c(st.pp_rec[lidx]), "score_h": c(st.score_h[:n_req]),
+        "q": c(q[:n_req]), "out": c(out[:n_req]),
+        "k_cache": c(k[used]), "v_cache": c(v[used]),
+        "records": c(st.pp_rec[lidx][used]), "score_h": c(st.score_h[:n_req]),
         "page_table": c(st.page_table[:n_req]), "page_cnt": c(st.page_cnt[:n_req]),
-        "block_table": c(block_table[:n_req]), "seq_lens": c(seq_lens[:n_req]),
+        "block_table": c(bt_small), "seq_lens": c(sl),
         "b_fix": c(st.b_fix[:n_req]), "n_sel_hi": c(st.n_sel_hi[:n_req])}
     if len(_DUMP["layers"]) == st.L:
         torch.save(_DUMP["layers"], os.environ.get("LOCKS_DUMP_PATH",

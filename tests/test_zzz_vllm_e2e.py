@@ -119,8 +119,8 @@ def test_selective_step_inside_vllm_matches_the_oracle(stock):
     assert sorted(layers) == [0, 1]
     n_kv, G, page, sink, window = 2, 4, 16, 1, 2
     for l, d in layers.items():
-        kv = d["kv_cache"].float().numpy()               # (2, NB, page, n_kv, d)
-        Kc, Vc = kv[0], kv[1]
+        Kc = d["k_cache"].float().numpy()                # (blocks used, page, n_kv, d)
+        Vc = d["v_cache"].float().numpy()
         bt, sl = d["block_table"].numpy(), d["seq_lens"].numpy()
         R = sl.shape[0]
         assert R == 2 and sl.min() > 700
