@@ -531,6 +531,23 @@ int locks_mla_decode(const void* q, int64_t q_stride_row, const void* cache,
                      int max_pages, float scale, int* status,
                      locks_stream_t stream);
 
+/* locks_mla_decode on the tcgen05 tensor cores, tokens in the M dimension:
+ * S^T[128 tokens x 16 heads] = K[128 x 576] Q^T and O^T[512 x 16] = V^T[512 x 128]
+ * P^T, accumulators in tensor memory, pages gathered through the block table by
+ * TMA tensor copies (2-D map over the cache seen as (num_blocks * 16, 576), box
+ * 16 x 64, 128-byte swizzle) -- one copy of a page feeds both products.  Same
+ * arguments and results as locks_mla_decode plus num_blocks (the tensor map's
+ * extent).  Needs stride_block == 16 * stride_tok (LOCKS_ERR_GEOMETRY
+ * otherwise: use locks_mla_decode).  The reference computes this step with
+ * eager fp32 bmm (backend/mla_attn.py:178-201). */
+int locks_mla_decode_tc(const void* q, int64_t q_stride_row, const void* cache,
+                        int64_t stride_block, int64_t stride_tok,
+                        const int32_t* block_table, int64_t bt_stride,
+                        const int32_t* page_table, const int32_t* page_cnt,
+                        const int32_t* seq_lens, void* out, float* lse, int n_rows,
+                        int max_pages, int num_blocks, float scale, int* status,
+                        locks_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

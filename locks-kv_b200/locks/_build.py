@@ -17,7 +17,7 @@ CSRC = os.path.join(os.path.dirname(PKG), "csrc")
 LIB_DIR = os.path.join(PKG, "_lib")
 LIB_PATH = os.path.join(LIB_DIR, "liblocks_b200.so")
 SOURCES = ["api.cu", "rki4_build.cu", "rki4_score.cu", "select.cu", "decode.cu",
-           "mla.cu", "cp.cu", "kv_write.cu"]
+           "mla.cu", "mla_tc.cu", "cp.cu", "kv_write.cu"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a",
               "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 

@@ -138,9 +138,24 @@ def mla_select_pages(st: MlaState, n_rows: int) -> None:
 
 
 def mla_decode(st: MlaState, q, cache, block_table, seq_lens, out, lse,
-               n_rows: int, scale: float) -> None:
-    """o (rows,16,512) bf16 and lse (rows,16) f32 over the kept pages."""
+               n_rows: int, scale: float, tensor_core: bool = None) -> None:
+    """o (rows,16,512) bf16 and lse (rows,16) f32 over the kept pages.
+    ``tensor_core``: the tcgen05 kernel (tokens in the M dimension, TMA page
+    gather) -- the default when the cache layout allows a tensor map (token rows
+    evenly spaced across blocks); False = the warp-level kernel."""
     _check_cache(cache)
+    if tensor_core is None:
+        tensor_core = getattr(st, "tensor_core", True) and \
+            cache.stride(0) == PAGE * cache.stride(1)
+    if tensor_core:
+        _cabi.call("locks_mla_decode_tc", _cabi.ptr(q), q.stride(0),
+                   _cabi.ptr(cache), cache.stride(0), cache.stride(1),
+                   _cabi.ptr(block_table), block_table.stride(0),
+                   _cabi.ptr(st.page_table), _cabi.ptr(st.page_cnt),
+                   _cabi.ptr(seq_lens), _cabi.ptr(out), _cabi.ptr(lse), int(n_rows),
+                   int(st.max_pages), int(cache.shape[0]), float(scale),
+                   _cabi.ptr(st.status), _cabi.stream())
+        return
     _cabi.call("locks_mla_decode", _cabi.ptr(q), q.stride(0), _cabi.ptr(cache),
                cache.stride(0), cache.stride(1), _cabi.ptr(block_table),
                block_table.stride(0), _cabi.ptr(st.page_table),

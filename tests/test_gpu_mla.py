@@ -117,3 +117,114 @@ def test_mla_factors_score_select_decode(name):
     torch.cuda.synchronize()
     for bi in range(B):
         np.testing.assert_allclose(t2n(out2[bi]), ref["o"][bi], atol=2e-2, rtol=1e-2)
+
+
+def test_mla_full_size_properties():
+    """Config 3 at full size -- batch 8 x 131072 tokens, 16 heads on one latent
+    head of 576 -- for one of its 27 layers: counts, ascending tables, the exact
+    keep rule against a torch sort of the DEVICE scores (forced sink + recent
+    pages, best-scored middle pages up to the budget), scores of a page sample
+    against the fp32 product the factors approximate, and o / lse against a
+    plain torch attention over the kept pages."""
+    from locks import synth
+    from locks.selection import mla_select as ms
+    sh = synth.CONFIG3
+    dev = torch.device("cuda", 0)
+    B, seq_len = 8, 131072 + 1
+    case = synth.make_mla_case(77, sh, [seq_len] * B, device=dev, n_layers=1)
+    MP, NB = int(case.block_table.shape[1]), int(case.caches[0].shape[0])
+    st = ms.MlaState(dev, num_layers=1, num_blocks=NB, max_rows=B, max_pages=MP,
+                     budget_pages=sh.budget_pages, sink_pages=sh.sink_pages,
+                     window_pages=sh.window_pages)
+    ms.mla_derive(st, case.seq_lens, B)
+    ms.build_prompt_factors(st, case.caches, case.block_table, case.seq_lens)
+    out = torch.zeros(B, sh.n_heads, sh.kv_lora_rank, device=dev, dtype=torch.bfloat16)
+    lse = torch.zeros(B, sh.n_heads, device=dev)
+    ms.mla_forward(st, 0, case.q[0], case.caches[0], case.block_table,
+                   case.seq_lens, out, lse, case.scale)
+    torch.cuda.synchronize()
+    st.check_status()
+    npg = -(-seq_len // sh.page)
+    n_cache = seq_len // sh.page
+    assert (st.n_pages[:B] == npg).all() and (st.n_cache[:B] == n_cache).all()
+    A = sh.budget_pages                       # the MLA budget includes forced pages
+    assert (st.page_cnt[:B, 0] == A).all()
+    tab = st.page_table[:B, 0]
+    assert (tab[:, A:] == -1).all()
+    assert (tab[:, 1:A] > tab[:, :A - 1]).all()
+    score = st.score[:B, 0]
+    assert torch.isfinite(score[:, :n_cache]).all()
+    nsh = npg - sh.window_pages
+    forced = list(range(sh.sink_pages)) + list(range(nsh, npg))
+    n_mid = A - len(forced)
+    for r in range(B):
+        mid = score[r, sh.sink_pages:nsh]
+        order = torch.sort(mid, descending=True, stable=True).indices[:n_mid] \
+            + sh.sink_pages
+        assert tab[r, :A].tolist() == sorted(order.tolist() + forced), r
+    # scores of a sample of pages against the oracle's factored scorer on the
+    # same pages (fp16 factors: the 3e-3 band of the small-case test)
+    cache, q = case.caches[0], case.q[0].float()
+    g = torch.Generator().manual_seed(1)
+    for r in (0, B - 1):
+        pages = torch.randint(0, n_cache, (64,), generator=g)
+        blks = case.block_table[r, pages.to(dev)].long()
+        kv = t2n(cache[blks])                                      # (64, 16, 576)
+        Lf, Rf = orc.mla_build_page_factors(
+            kv[:, :, :sh.kv_lora_rank].reshape(-1, sh.kv_lora_rank), 64, sh.page, 8)
+        qr = t2n(case.q[0][r])
+        want = orc.mla_page_score(qr[:, :sh.kv_lora_rank], qr[:, sh.kv_lora_rank:],
+                                  Lf, Rf, kv[:, :, sh.kv_lora_rank:],
+                                  np.full(64, sh.page), case.scale)
+        np.testing.assert_allclose(t2n(score[r, pages.to(dev)]), want, rtol=3e-3,
+                                   atol=3e-3)
+    # attention over the kept pages, plain torch fp32
+    for r in (0, 3, B - 1):
+        pg = tab[r, :A].long()
+        blks = case.block_table[r, pg].long()
+        kv = cache[blks].reshape(-1, sh.width).float()
+        pos = (pg[:, None] * sh.page + torch.arange(sh.page, device=dev)[None]).reshape(-1)
+        s_ = (q[r] @ kv.T) * case.scale
+        s_ = s_.masked_fill(~(pos < seq_len)[None], float("-inf"))
+        o_ref = torch.softmax(s_, -1) @ kv[:, :sh.kv_lora_rank]
+        torch.testing.assert_close(out[r].float(), o_ref, atol=2e-2, rtol=1e-2)
+        torch.testing.assert_close(lse[r], torch.logsumexp(s_, -1), atol=2e-2,
+                                   rtol=1e-2)
+
+
+@pytest.mark.parametrize("lens", [[777, 2053, 300, 16, 5000], [130, 4096 + 7]])
+def test_mla_tensor_core_decode_equals_warp_level_decode(lens):
+    """The tcgen05 decode (tokens in M, TMA page gather, accumulators in tensor
+    memory) against the warp-level kernel on the same kept pages: rows shorter
+    than a tile, partial last pages, several tiles per CTA (a dense selection:
+    budget >= pages) and the sparse selection of the path."""
+    from locks import synth
+    from locks.selection import mla_select as ms
+    sh = synth.MlaShape(n_layers=1, budget_pages=24, sink_pages=1, window_pages=4)
+    case = synth.make_mla_case(5, sh, lens, device=DEV, n_layers=1)
+    B = len(lens)
+    MP, NB = int(case.block_table.shape[1]), int(case.caches[0].shape[0])
+    for budget in (24, MP):
+        st = ms.MlaState(DEV, num_layers=1, num_blocks=NB, max_rows=B, max_pages=MP,
+                         budget_pages=budget, sink_pages=1, window_pages=4)
+        ms.mla_derive(st, case.seq_lens, B)
+        ms.build_prompt_factors(st, case.caches, case.block_table, case.seq_lens)
+        ms.mla_page_score(st, 0, case.q[0], case.caches[0], case.block_table, B,
+                          case.scale)
+        ms.mla_select_pages(st, B)
+        outs = []
+        for tc in (False, True):
+            out = torch.full((B, 16, 512), float("nan"), device=DEV,
+                             dtype=torch.bfloat16)
+            lse = torch.full((B, 16), float("nan"), device=DEV)
+            ms.mla_decode(st, case.q[0], case.caches[0], case.block_table,
+                          case.seq_lens, out, lse, B, case.scale, tensor_core=tc)
+            torch.cuda.synchronize()
+            st.check_status()
+            outs.append((out.float(), lse))
+        (o0, l0), (o1, l1) = outs
+        assert torch.isfinite(o1).all() and torch.isfinite(l1).all()
+        # both within the decode tolerance of each other (bf16 P in the tensor-core
+        # kernel, hi+lo split P in the warp-level one)
+        torch.testing.assert_close(o1, o0, atol=2e-2, rtol=1e-2)
+        torch.testing.assert_close(l1, l0, atol=2e-3, rtol=2e-3)
