@@ -178,6 +178,27 @@ mla_tc_decode_kernel(const __grid_constant__ CUtensorMap tmap, const TcParams p)
     cluster.sync();                  // barriers, TMEM base and peers' CTAs are up
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
+    // ---- Q^T into the swizzled K-major B layout: [chunk][head][128 B].  q is an
+    // input of the whole layer (the scorer of this layer has read it already), not
+    // a product of the selector, so it is staged ahead of the dependency wait;
+    // all loads are in flight before the first store --------------------------------
+    {
+        const uint4* q4 = reinterpret_cast<const uint4*>(p.q + (int64_t)row * p.q_stride_row);
+        constexpr int C16 = WIDTH * 2 / 16;            // 72 pieces per head
+        constexpr int NQ = NH * C16 / TC_THREADS;      // 9 per thread
+        static_assert(NH * C16 % TC_THREADS == 0, "q pieces divide over the threads");
+        uint4 v[NQ];
+#pragma unroll
+        for (int i = 0; i < NQ; ++i) v[i] = q4[tid + i * TC_THREADS];
+#pragma unroll
+        for (int i = 0; i < NQ; ++i) {
+            const int e = tid + i * TC_THREADS;
+            const int h = e / C16, pc = e % C16;       // piece pc = channels 8pc..8pc+7
+            const int chunk = pc >> 3, byte = (pc & 7) << 4;
+            *reinterpret_cast<uint4*>(&sm.q[chunk * QP_CHUNK_BYTES + swz128(h, byte)]) = v[i];
+        }
+        fence_proxy_async();
+    }
     pdl_wait();                      // the page table comes from the selector
 
     const int seq_len = p.seq_lens[row];
@@ -187,19 +208,6 @@ mla_tc_decode_kernel(const __grid_constant__ CUtensorMap tmap, const TcParams p)
     const int np = j1 - j0;
     const int32_t* tab = p.page_table + (int64_t)row * p.max_pages;
     const int32_t* bt = p.block_table + (int64_t)row * p.bt_stride;
-
-    // ---- Q^T into the swizzled K-major B layout: [chunk][head][128 B] --------
-    {
-        const uint4* q4 = reinterpret_cast<const uint4*>(p.q + (int64_t)row * p.q_stride_row);
-        constexpr int C16 = WIDTH * 2 / 16;            // 72 pieces per head
-        for (int e = tid; e < NH * C16; e += TC_THREADS) {
-            const int h = e / C16, pc = e % C16;       // piece pc = channels 8pc..8pc+7
-            const int chunk = pc >> 3, byte = (pc & 7) << 4;
-            *reinterpret_cast<uint4*>(&sm.q[chunk * QP_CHUNK_BYTES + swz128(h, byte)]) =
-                q4[e];
-        }
-        fence_proxy_async();
-    }
 
     float acc[4][NH];
 #pragma unroll
@@ -226,11 +234,17 @@ mla_tc_decode_kernel(const __grid_constant__ CUtensorMap tmap, const TcParams p)
             if (lane == 0)
                 mbar_expect_tx(&sm.bar_full, (uint32_t)nt * NCHUNK * PAGE_CHUNK_BYTES);
             __syncwarp();
-            if (lane < nt) {
-#pragma unroll
-                for (int ch = 0; ch < NCHUNK; ++ch)
-                    tma_load_2d(&sm.kt[ch * CHUNK_BYTES + lane * PAGE_CHUNK_BYTES], &tmap,
-                                ch * 64, blk * PG, &sm.bar_full);
+            // the 9 x nt boxes are issued by all 32 lanes (a request costs its
+            // issuer tens of cycles)
+            // (every lane runs every round: the shuffle needs the whole warp)
+            for (int i0 = 0; i0 < nt * NCHUNK; i0 += 32) {
+                const int i = i0 + lane;
+                const bool on = i < nt * NCHUNK;
+                const int slot = on ? i / NCHUNK : 0, ch = i - slot * NCHUNK;
+                const int b = __shfl_sync(0xffffffffu, blk, slot);
+                if (on)
+                    tma_load_2d(&sm.kt[ch * CHUNK_BYTES + slot * PAGE_CHUNK_BYTES],
+                                &tmap, ch * 64, b * PG, &sm.bar_full);
             }
         }
         __syncthreads();                               // tile_pt is visible
@@ -255,13 +269,16 @@ mla_tc_decode_kernel(const __grid_constant__ CUtensorMap tmap, const TcParams p)
         // ---- S^T = K . Q^T : 9 chunks x 4 k-steps of 16 channels -------------------
         if (tid == 0) {
             tc_fence_after();
-#pragma unroll 1
+            // descriptors differ only in their start-address field (16-byte units)
+            const uint64_t a0 = umma_desc(kt_addr, 16, 1024);
+            const uint64_t b0 = umma_desc(q_addr, 16, 1024);
+#pragma unroll
             for (int ch = 0; ch < NCHUNK; ++ch) {
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
-                    const uint64_t a = umma_desc(kt_addr + ch * CHUNK_BYTES + ks * 32, 16, 1024);
-                    const uint64_t b = umma_desc(q_addr + ch * QP_CHUNK_BYTES + ks * 32, 16, 1024);
-                    umma_f16(tmem, a, b, IDESC_S, (ch | ks) ? 1u : 0u);
+                    umma_f16(tmem, a0 + (uint64_t)((ch * CHUNK_BYTES + ks * 32) >> 4),
+                             b0 + (uint64_t)((ch * QP_CHUNK_BYTES + ks * 32) >> 4),
+                             IDESC_S, (ch | ks) ? 1u : 0u);
                 }
             }
             umma_commit(&sm.bar_s);
@@ -314,14 +331,17 @@ mla_tc_decode_kernel(const __grid_constant__ CUtensorMap tmap, const TcParams p)
         // ---- O^T = V^T . P^T : 4 channel blocks x nt k-steps of one page ----------
         if (tid == 0) {
             tc_fence_after();
-#pragma unroll 1
+            const uint64_t a0 = umma_desc(kt_addr, CHUNK_BYTES, 1024);
+            const uint64_t b0 = umma_desc(p_addr, 16, 1024);
+#pragma unroll
             for (int mb = 0; mb < 4; ++mb) {
-                for (int ks = 0; ks < nt; ++ks) {
-                    const uint64_t a = umma_desc(kt_addr + (2 * mb) * CHUNK_BYTES + ks * 2048,
-                                                 CHUNK_BYTES, 1024);
-                    const uint64_t b = umma_desc(p_addr + (ks >> 2) * QP_CHUNK_BYTES +
-                                                 (ks & 3) * 32, 16, 1024);
-                    umma_f16(tmem + 16 + 16 * mb, a, b, IDESC_O, ks ? 1u : 0u);
+#pragma unroll
+                for (int ks = 0; ks < TILE_PAGES; ++ks) {
+                    if (ks < nt)
+                        umma_f16(tmem + 16 + 16 * mb,
+                                 a0 + (uint64_t)(((2 * mb) * CHUNK_BYTES + ks * 2048) >> 4),
+                                 b0 + (uint64_t)(((ks >> 2) * QP_CHUNK_BYTES + (ks & 3) * 32) >> 4),
+                                 IDESC_O, ks ? 1u : 0u);
                 }
             }
             umma_commit(&sm.bar_o);
@@ -362,40 +382,56 @@ mla_tc_decode_kernel(const __grid_constant__ CUtensorMap tmap, const TcParams p)
             cluster.map_shared_rank(&sm.xl[c][0], d)[tid] = sm.lrun[tid];
         }
     }
-    constexpr int OUT_PITCH = LKV + 4;
-    static_assert(sizeof(sm.kt) >= NH * OUT_PITCH * sizeof(float), "staging fits the tile");
-    float (*stage_o)[OUT_PITCH] = reinterpret_cast<float (*)[OUT_PITCH]>(sm.kt);
+    // this thread owns channel mb * 128 + tid of every head: each value goes
+    // straight to the CTA that normalises it (a warp's store covers 128
+    // contiguous bytes of one head in one CTA)
 #pragma unroll
-    for (int mb = 0; mb < 4; ++mb)
+    for (int mb = 0; mb < 4; ++mb) {
 #pragma unroll
-        for (int h = 0; h < NH; ++h) stage_o[h][mb * 128 + tid] = acc[mb][h];
-    __syncthreads();
-    for (int i = tid; i < NH * (LKV / 4); i += TC_THREADS) {
-        const int h = i / (LKV / 4), c4 = i % (LKV / 4);
-        const float4 val = *reinterpret_cast<const float4*>(&stage_o[h][4 * c4]);
-        const int e = h * LKV + 4 * c4;
-        const int d = e / per_e;
-        float* dst = cluster.map_shared_rank(&sm.xacc[0], d) + c * per_e + (e - d * per_e);
-        *reinterpret_cast<float4*>(dst) = val;
+        for (int h = 0; h < NH; ++h) {
+            const int e = h * LKV + mb * 128 + tid;
+            const int d = e / per_e;
+            cluster.map_shared_rank(&sm.xacc[0], d)[c * per_e + (e - d * per_e)] =
+                acc[mb][h];
+        }
     }
     cluster.sync();                              // every CTA's pushes have landed
     if (warp == 0) {                             // all tcgen05.ld of this CTA are done
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
                      ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
-    for (int h = tid; h < NH; h += TC_THREADS) {
+    {   // merge weights: 8 threads per head, each takes CTAs sub, sub + 8
+        const int h = tid >> 3, sub = tid & 7;
+        float mv[2], lv[2];
         float M = -INFINITY;
-        for (int cc = 0; cc < CL; ++cc) M = fmaxf(M, sm.xm[cc][h]);
-        float Ls = 0.f;
-        for (int cc = 0; cc < CL; ++cc) {
-            const float lw = sm.xl[cc][h];
-            const float wt = (lw > 0.f) ? __expf(sm.xm[cc][h] - M) : 0.f;
-            sm.xm[cc][h] = wt;
-            Ls += wt * lw;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int cc = sub + 8 * i;
+            mv[i] = (cc < CL) ? sm.xm[cc][h] : -INFINITY;
+            lv[i] = (cc < CL) ? sm.xl[cc][h] : 0.f;
+            M = fmaxf(M, mv[i]);
         }
+        M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 1));
+        M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 2));
+        M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 4));
+        float wt[2], Ls = 0.f;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            wt[i] = (lv[i] > 0.f) ? __expf(mv[i] - M) : 0.f;
+            Ls += wt[i] * lv[i];
+        }
+        Ls += __shfl_xor_sync(0xffffffffu, Ls, 1);
+        Ls += __shfl_xor_sync(0xffffffffu, Ls, 2);
+        Ls += __shfl_xor_sync(0xffffffffu, Ls, 4);
         const float inv = (Ls > 0.f) ? 1.f / Ls : 0.f;
-        for (int cc = 0; cc < CL; ++cc) sm.xm[cc][h] *= inv;
-        if (c == 0) p.lse[(int64_t)row * NH + h] = (Ls > 0.f) ? M + __logf(Ls) : 0.f;
+        __syncwarp();                            // every lane has read xm / xl
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int cc = sub + 8 * i;
+            if (cc < CL) sm.xm[cc][h] = wt[i] * inv;     // reuse: now the weight
+        }
+        if (c == 0 && sub == 0)
+            p.lse[(int64_t)row * NH + h] = (Ls > 0.f) ? M + __logf(Ls) : 0.f;
     }
     __syncthreads();
     for (int el = tid; el < per_e; el += TC_THREADS) {
