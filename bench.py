@@ -290,6 +290,108 @@ class RefArm:
         return time.perf_counter() - t0
 
 
+class RefArmMla:
+    """Config 3 on the host cores with the reference's own torch code (staged
+    under ``oracle/_ref``): ``build_page_factors`` (untimed set-up, as in the
+    engine: factors are built once per prompt), then per step
+    ``mla_page_score_ref``, ``topb_middle`` and the attention block of its
+    backend (``backend/mla_attn.py:178-201``: gather the kept pages, fp32
+    softmax(q kv^T) kv[:, :512]) -- ONE batch row of ONE layer at the full
+    context, scaled by rows x layers."""
+
+    def __init__(self, sh, seq_len, rows=8, seed=77):
+        ref_root = os.path.join(ROOT, "oracle", "_ref")
+        if ref_root not in sys.path:
+            sys.path.insert(0, ref_root)
+        from locks_ref.selection.mla_score_torch import (mla_page_score_ref,
+                                                         topb_middle)
+        from locks_ref.selection.mla_select import build_page_factors
+        from locks import synth
+        self.sh, self.rows = sh, rows
+        self._score, self._keep = mla_page_score_ref, topb_middle
+        case = synth.make_mla_case(seed, sh, [seq_len], device="cpu", n_layers=1)
+        page, Lkv = sh.page, sh.kv_lora_rank
+        self.L, self.page, self.Lkv = seq_len, page, Lkv
+        n_pages, n_cache = -(-seq_len // page), seq_len // page
+        self.n_pages, self.n_cache = n_pages, n_cache
+        self.cache, self.bt = case.caches[0], case.block_table[0].long()
+        kvb = self.cache.index_select(0, self.bt[:n_pages]).reshape(-1, sh.width)[:seq_len]
+        Lf, Rf = build_page_factors(kvb[:n_cache * page, :Lkv].float(), n_cache, page, 8)
+        self.C8 = Lf @ Rf
+        self.k_rope = kvb[:n_cache * page, Lkv:].float().view(n_cache, page, -1)
+        self.q = case.q[0][0].float()
+        self.scale = case.scale
+        self.sample = (f"1 of {rows} rows, 1 of {sh.n_layers} layers at the full "
+                       f"context ({seq_len - 1} tokens), time x{rows * sh.n_layers}; "
+                       "reference torch code (oracle/_ref): mla_page_score_ref, "
+                       "topb_middle, fp32 attention over the kept pages as in its "
+                       "backend; page factors prebuilt")
+
+    def step(self):
+        sh, page, Lkv, L = self.sh, self.page, self.Lkv, self.L
+        t0 = time.perf_counter()
+        valid = torch.full((self.n_cache,), page, dtype=torch.long)
+        ps = torch.full((self.n_pages,), float("-inf"))
+        ps[:self.n_cache] = self._score(self.q[:, :Lkv], self.q[:, Lkv:], self.C8,
+                                        self.k_rope, valid, self.scale)
+        keep = self._keep(ps, sh.budget_pages, sh.sink_pages, sh.window_pages)
+        idx = keep.nonzero().flatten()
+        sel = self.cache.index_select(0, self.bt[idx]).reshape(-1, sh.width).float()
+        pos = (idx[:, None] * page + torch.arange(page)[None]).reshape(-1)
+        sc = (self.q @ sel.T) * self.scale
+        sc = sc.masked_fill(~(pos < L)[None], float("-inf"))
+        o = torch.softmax(sc, -1) @ sel[:, :Lkv]
+        lse = torch.logsumexp(sc, -1)
+        del o, lse
+        return time.perf_counter() - t0
+
+
+def run_reference_mla(args, seq_len):
+    from locks import synth
+    sh = synth.CONFIG3
+    if args.layers:
+        import dataclasses
+        sh = dataclasses.replace(sh, n_layers=args.layers)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    B = 8
+    if not reference_available():
+        return {"impl": "reference", "unavailable":
+                "oracle/_ref is not staged (run oracle/make_ref.py where the "
+                "reference checkout is)"}
+    arm = RefArmMla(sh, seq_len, rows=B)
+    for _ in range(args.warmup):
+        arm.step()
+    ts = [arm.step() for _ in range(args.steps)]
+    tpot = float(np.mean(ts)) * B * sh.n_layers
+    return {
+        "impl": "reference", "metric": "sparse_decode_tokens_per_s",
+        "value": B / tpot, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": float(np.mean(ts)) * 1e3, "tpot_ms": tpot * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": mla_config(sh, B, seq_len),
+        "cpu_baseline": {"value": B / tpot, "unit": "tokens/s", "cores": cores,
+                         "kind": "reference", "sample": arm.sample,
+                         "tpot_ms": tpot * 1e3},
+        "e2e": {"value": B / tpot, "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+    }
+
+
+def mla_config(sh, B, seq_len):
+    rec_b = 8448 + sh.page * sh.rope_dim * 2
+    b_score = sh.n_layers * B * (seq_len // sh.page) * rec_b
+    b_dec = sh.n_layers * B * min(sh.budget_pages, -(-seq_len // sh.page)) \
+        * sh.page * sh.width * 2
+    return {"workload": f"c3: MLA, {sh.n_layers} layers, {sh.n_heads} heads, latent "
+                        f"{sh.width}, page {sh.page}, batch {B}, ctx {seq_len - 1}, "
+                        f"budget {sh.budget_pages} pages incl. {sh.sink_pages} sink + "
+                        f"{sh.window_pages} recent",
+            "l2_policy": "inputs larger than L2 "
+                         f"({(b_score + b_dec) / 1e9:.2f} GB per step)"}
+
+
 def reference_available() -> bool:
     return os.path.exists(os.path.join(ROOT, "oracle", "_ref", "locks_ref",
                                        "selection", "rki4_score_torch.py"))
@@ -1037,18 +1139,26 @@ def run_gpu_mla(args, seq_len):
     peak = (float(json.load(open(peaks_path))["hbm_gbs"])
             if os.path.exists(peaks_path) else 6650.0)
     ach = (b_score / L) / (ms_score * 1e-3) / 1e9
+    cpu = None
+    if not args.no_cpu_baseline:
+        try:
+            cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference",
+                   "--workload", "c3", "--steps", "3", "--warmup", "1"] \
+                + (["--ctx", str(args.ctx)] if args.ctx else []) \
+                + (["--layers", str(args.layers)] if args.layers else [])
+            r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+            cpu = json.loads([ln for ln in r.stdout.splitlines()
+                              if ln.startswith("{")][-1]).get("cpu_baseline")
+        except Exception as e:
+            cpu = {"value": None, "unit": "tokens/s", "cores": os.cpu_count(),
+                   "kind": "reference", "sample": f"failed: {type(e).__name__}: {e}"}
     return {
         "metric": "sparse_decode_tokens_per_s", "value": B / (ms_step * 1e-3),
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "tpot_ms": ms_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"c3: MLA, {L} layers, {sh.n_heads} heads, latent "
-                               f"{W}, page {sh.page}, batch {B}, ctx {seq_len - 1}, "
-                               f"budget {sh.budget_pages} pages incl. "
-                               f"{sh.sink_pages} sink + {sh.window_pages} recent",
-                   "l2_policy": "inputs larger than L2 "
-                                f"({(b_score + b_dec) / 1e9:.2f} GB per step)"},
+        "config": mla_config(sh, B, seq_len),
         "clocks": clocks,
         "e2e": {"value": B / (ms_e2e * 1e-3), "unit": "tokens/s",
                 "ms_per_step": ms_e2e, "h2d_bytes_per_step": q_host.numel() * 2,
@@ -1069,7 +1179,7 @@ def run_gpu_mla(args, seq_len):
                   "gbs": L * B * npg * page_b / (ms_dense * 1e-3) / 1e9,
                   "speedup_sparse_over_dense": ms_dense / ms_step},
         "build": {"factors_ms": t_build},
-        "cpu_baseline": None,
+        "cpu_baseline": cpu,
     }
 
 
@@ -1155,7 +1265,8 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.workload_name == "c3":
         if rank == 0:
-            print(json.dumps(run_gpu_mla(args, (args.ctx or 131072) + 1)), flush=True)
+            fn = run_reference_mla if args.impl == "reference" else run_gpu_mla
+            print(json.dumps(fn(args, (args.ctx or 131072) + 1)), flush=True)
         return
     sh, ctx = workload(args.workload_name, args.ctx)
     if args.layers:

@@ -2,10 +2,11 @@
 
     python oracle/make_ref.py            # reads $LOCKS_REFERENCE_SRC or /root/reference/src
 
-Copies, unmodified, the seven files of the reference package (``locks`` v0.1.3)
-that its CPU-runnable selection path consists of -- ``selection/rki4_state.py``,
-``rki4_build.py``, ``build.py``, ``rki4_score_torch.py``, ``select.py`` and the
-two modules they import, ``arch.py`` and ``quant.py`` -- into
+Copies, unmodified, the nine files of the reference package (``locks`` v0.1.3)
+that its CPU-runnable selection paths consist of -- ``selection/rki4_state.py``,
+``rki4_build.py``, ``build.py``, ``rki4_score_torch.py``, ``select.py``, the two
+modules they import (``arch.py``, ``quant.py``) and, for the latent (MLA) path,
+``selection/mla_select.py`` and ``mla_score_torch.py`` -- into
 ``oracle/_ref/locks_ref/`` under the package name ``locks_ref`` (their imports
 are relative, so the copy works under another name and does not collide with
 this repository's own ``locks`` package).  ``oracle/_ref/`` is git-ignored: the
@@ -28,7 +29,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 DST = os.path.join(HERE, "_ref", "locks_ref")
 FILES = ["arch.py", "quant.py", "selection/rki4_state.py",
          "selection/rki4_build.py", "selection/build.py",
-         "selection/rki4_score_torch.py", "selection/select.py"]
+         "selection/rki4_score_torch.py", "selection/select.py",
+         "selection/mla_select.py", "selection/mla_score_torch.py"]
 
 
 def stage(src_root: str | None = None) -> bool:
