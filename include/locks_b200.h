@@ -497,6 +497,24 @@ int locks_mla_build_factors(const void* cache, int64_t stride_block,
                             const int32_t* blocks, int n_blocks, int num_blocks,
                             locks_stream_t stream);
 
+/* Factor bookkeeping of a decode batch ON THE DEVICE (two launches, no host
+ * synchronisation, fixed shape): a gate kernel decides per row whether its
+ * factors are missing or stale -- entries are remembered under the row's first
+ * block id as (content fingerprint of the first and the last covered prompt page,
+ * number of covered pages); a row with no entry, a row that shrank below its
+ * entry, or a fingerprint mismatch (block ids reused by another request) is
+ * flagged -- writes need[row] and n_cache[row] (pages with factors), and the
+ * factor kernel then rebuilds all pages of the flagged rows.  fp_tab (f32) and
+ * nc_tab (i32, initialised to -1) have num_blocks entries per layer.
+ * Replaces the host-side factor cache of backend/mla_attn.py:212-239 and its
+ * per-step .tolist() synchronisations (:118-133). */
+int locks_mla_refresh_rows(const void* cache, int64_t stride_block,
+                           int64_t stride_tok, void* records,
+                           const int32_t* block_table, int64_t bt_stride,
+                           const int32_t* seq_lens, float* fp_tab, int32_t* nc_tab,
+                           int32_t* need, int32_t* n_cache, int n_rows,
+                           int max_pages, int num_blocks, locks_stream_t stream);
+
 /* Per-row page parameters of the MLA keep rule: n_pages = ceil(L/16);
  * n_sel_hi = n_pages - window; b = n_pages when n_pages <= budget_pages (keep
  * all), else budget_pages - |sink pages U last window pages| (>= 0).

@@ -52,8 +52,15 @@ struct FbParams {
     const __nv_bfloat16* cache;
     int64_t sb, st;
     uint8_t* records;
-    const int32_t* blocks;
+    const int32_t* blocks;         // block list, or null: jobs come from the rows
     int n_blocks, num_blocks;
+    // row mode: job bi is page bi % max_pages of row bi / max_pages; it runs when
+    // the row was flagged (need) and the page is one of its n_cache full pages
+    const int32_t* need;
+    const int32_t* n_cache;
+    const int32_t* block_table;
+    int64_t bt_stride;
+    int max_pages;
 };
 
 __global__ void __launch_bounds__(FB_WARPS * 32) mla_factor_kernel(const FbParams p) {
@@ -61,7 +68,14 @@ __global__ void __launch_bounds__(FB_WARPS * 32) mla_factor_kernel(const FbParam
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int bi = blockIdx.x * FB_WARPS + warp;
     if (bi >= p.n_blocks) return;
-    const int blk = p.blocks[bi];
+    int blk;
+    if (p.blocks != nullptr) {
+        blk = p.blocks[bi];
+    } else {
+        const int row = bi / p.max_pages, page = bi - row * p.max_pages;
+        if (!p.need[row] || page >= p.n_cache[row]) return;
+        blk = p.block_table[(int64_t)row * p.bt_stride + page];
+    }
     if (blk < 0 || blk >= p.num_blocks) return;
     FbScratch& ws = reinterpret_cast<FbScratch*>(fb_raw)[warp];
     const __nv_bfloat16* src = p.cache + (int64_t)blk * p.sb;
@@ -162,6 +176,73 @@ __global__ void __launch_bounds__(FB_WARPS * 32) mla_factor_kernel(const FbParam
         dst[0] = reinterpret_cast<const uint4*>(o)[0];
         dst[1] = reinterpret_cast<const uint4*>(o)[1];
     }
+}
+
+// =========================================================================== //
+// Which rows need (new) factors: decided on the device                           //
+// =========================================================================== //
+// One warp per row.  A row's factors are remembered under its FIRST block id:
+// fp_tab[b0] is a content fingerprint, nc_tab[b0] the number of full pages the
+// factors cover (-1: none).  The fingerprint is  f(block b0) + 1.0009 f(block of
+// page nc - 1)  with f = the sum of the first 8 channels over the block's 16
+// tokens: both blocks are full prompt pages, so the value does not change while
+// the request decodes, and a request that reuses a finished one's block ids
+// changes it.  A row is flagged when it has no entry, when it shrank below the
+// stored page count (preemption), or when the fingerprint differs; a flagged
+// row's entry is rewritten for its current length.  Generated pages are not
+// added to an existing entry (they are attended while inside the recent window),
+// as in the reference (backend/mla_attn.py:212-239), whose host-side
+// bookkeeping and per-step .tolist() this kernel replaces.
+struct GateParams {
+    const __nv_bfloat16* cache;
+    int64_t sb, st;
+    const int32_t* block_table;
+    int64_t bt_stride;
+    const int32_t* seq_lens;
+    float* fp_tab;
+    int32_t* nc_tab;
+    int32_t* need;
+    int32_t* n_cache;
+    int n_rows, num_blocks, max_pages;
+};
+
+__device__ __forceinline__ float block_fingerprint(const GateParams& p, int blk, int lane) {
+    // 16 tokens x 8 channels = 128 values, 4 per lane, fixed summation order
+    const int t = lane >> 1, c0 = (lane & 1) * 4;
+    const __nv_bfloat16* src = p.cache + (int64_t)blk * p.sb + (int64_t)t * p.st + c0;
+    float v = __bfloat162float(src[0]) + __bfloat162float(src[1]) +
+              __bfloat162float(src[2]) + __bfloat162float(src[3]);
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__global__ void __launch_bounds__(128) mla_gate_kernel(const GateParams p) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 4 + warp;
+    if (r >= p.n_rows) return;
+    const int sl = p.seq_lens[r];
+    if (sl <= 0) {
+        if (lane == 0) { p.need[r] = 0; p.n_cache[r] = 0; }
+        return;
+    }
+    const int32_t* bt = p.block_table + (int64_t)r * p.bt_stride;
+    const int b0 = min(max(bt[0], 0), p.num_blocks - 1);
+    const int nc_now = min(sl / PG, p.max_pages);
+    const int nc_old = p.nc_tab[b0];
+    const float f0 = block_fingerprint(p, b0, lane);
+    bool need = nc_old < 0 || nc_now < nc_old;
+    if (!need) {
+        const int last = (nc_old > 0) ? min(max(bt[nc_old - 1], 0), p.num_blocks - 1) : b0;
+        const float fp = f0 + 1.0009f * block_fingerprint(p, last, lane);
+        need = !(fp == p.fp_tab[b0]);
+    }
+    if (need) {
+        const int last = (nc_now > 0) ? min(max(bt[nc_now - 1], 0), p.num_blocks - 1) : b0;
+        const float fp = f0 + 1.0009f * block_fingerprint(p, last, lane);
+        if (lane == 0) { p.fp_tab[b0] = fp; p.nc_tab[b0] = nc_now; }
+    }
+    if (lane == 0) { p.need[r] = need ? 1 : 0; p.n_cache[r] = need ? nc_now : nc_old; }
 }
 
 // =========================================================================== //
@@ -736,10 +817,57 @@ extern "C" int locks_mla_build_factors(const void* cache, int64_t stride_block,
     p.sb = stride_block; p.st = stride_tok;
     p.records = static_cast<uint8_t*>(records);
     p.blocks = blocks; p.n_blocks = n_blocks; p.num_blocks = num_blocks;
+    p.need = nullptr; p.n_cache = nullptr; p.block_table = nullptr;
+    p.bt_stride = 0; p.max_pages = 1;
     mla_factor_kernel<<<(n_blocks + FB_WARPS - 1) / FB_WARPS, FB_WARPS * 32, smem,
                         static_cast<cudaStream_t>(stream)>>>(p);
     pdl_break();                       // the scorer prefetches factor records before its wait
     return check_launch("locks_mla_build_factors");
+}
+
+extern "C" int locks_mla_refresh_rows(
+    const void* cache, int64_t stride_block, int64_t stride_tok, void* records,
+    const int32_t* block_table, int64_t bt_stride, const int32_t* seq_lens,
+    float* fp_tab, int32_t* nc_tab, int32_t* need, int32_t* n_cache, int n_rows,
+    int max_pages, int num_blocks, locks_stream_t stream) {
+    LOCKS_REQUIRE(cache && records && block_table && seq_lens && fp_tab && nc_tab &&
+                      need && n_cache,
+                  LOCKS_ERR_ARG, "locks_mla_refresh_rows: null pointer argument");
+    LOCKS_REQUIRE(n_rows >= 0 && max_pages >= 1 && num_blocks >= 1 &&
+                      (int64_t)n_rows * max_pages < (int64_t)1 << 31,
+                  LOCKS_ERR_ARG, "locks_mla_refresh_rows: bad size argument");
+    LOCKS_REQUIRE(stride_block % 8 == 0 && stride_tok % 8 == 0 &&
+                      (reinterpret_cast<uintptr_t>(cache) & 15) == 0 &&
+                      (reinterpret_cast<uintptr_t>(records) & 15) == 0,
+                  LOCKS_ERR_ARG, "locks_mla_refresh_rows: misaligned argument");
+    if (n_rows == 0) return LOCKS_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    GateParams g;
+    g.cache = static_cast<const __nv_bfloat16*>(cache);
+    g.sb = stride_block; g.st = stride_tok;
+    g.block_table = block_table; g.bt_stride = bt_stride; g.seq_lens = seq_lens;
+    g.fp_tab = fp_tab; g.nc_tab = nc_tab; g.need = need; g.n_cache = n_cache;
+    g.n_rows = n_rows; g.num_blocks = num_blocks; g.max_pages = max_pages;
+    mla_gate_kernel<<<(n_rows + 3) / 4, 128, 0, s>>>(g);
+    const int smem = (int)sizeof(FbScratch) * FB_WARPS;
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        cudaFuncSetAttribute(mla_factor_kernel,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        attr_done[dev] = true;
+    }
+    FbParams p;
+    p.cache = g.cache; p.sb = stride_block; p.st = stride_tok;
+    p.records = static_cast<uint8_t*>(records);
+    p.blocks = nullptr; p.n_blocks = n_rows * max_pages; p.num_blocks = num_blocks;
+    p.need = need; p.n_cache = n_cache; p.block_table = block_table;
+    p.bt_stride = bt_stride; p.max_pages = max_pages;
+    mla_factor_kernel<<<(p.n_blocks + FB_WARPS - 1) / FB_WARPS, FB_WARPS * 32, smem,
+                        s>>>(p);
+    pdl_break();
+    return check_launch("locks_mla_refresh_rows");
 }
 
 extern "C" int locks_mla_derive(const int32_t* seq_lens, int n_rows,

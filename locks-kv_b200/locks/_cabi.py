@@ -74,6 +74,8 @@ _SIGNATURES = {
                                     _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I,
                                     _F, _P, _P], 2),
     "locks_mla_build_factors": ([_P, _L, _L, _P, _P, _I, _I, _P], 1),
+    "locks_mla_refresh_rows": ([_P, _L, _L, _P, _P, _L, _P, _P, _P, _P, _P, _I, _I,
+                                _I, _P], 2),
     "locks_mla_derive": ([_P, _I, _I, _I, _I, _P, _P, _P, _P], 1),
     "locks_mla_score": ([_P, _L, _P, _P, _L, _L, _P, _L, _P, _P, _P, _I, _I,
                          _I, _F, _I, _P, _P], 1),

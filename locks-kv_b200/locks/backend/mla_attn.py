@@ -1,7 +1,9 @@
 """MLA decode hook: ``LocksMLAImpl.forward_mqa`` selects pages of the latent
 cache and attends only those; prefill stays stock MLA.  Same hook and result
-``(o, lse)`` as the reference's ``backend/mla_attn.py:86-210``, but every step
-is a kernel launch (no ``.tolist()`` syncs once a row's factors exist).
+``(o, lse)`` as the reference's ``backend/mla_attn.py:86-210``, but the whole
+call is a fixed sequence of kernel launches with no host synchronisation: which
+rows need (new) page factors is decided on the device (``mla_refresh_rows``), so
+the hook can sit inside a captured decode graph.
 """
 from __future__ import annotations
 
@@ -10,8 +12,8 @@ from vllm.v1.attention.backends.mla.triton_mla import (TritonMLABackend,
                                                        TritonMLAImpl)
 
 from ..selection.mla_select import (HEADS, LKV, PAGE, ROPE, MlaState,
-                                    build_page_factors, mla_decode, mla_derive,
-                                    mla_page_score, mla_select_pages)
+                                    mla_decode, mla_derive, mla_page_score,
+                                    mla_refresh_rows, mla_select_pages)
 from . import _runtime
 
 _ANNOUNCED = False
@@ -28,30 +30,26 @@ def _budget_pages(cfg, max_pages: int) -> int:
         "'budget' (fraction) in LOCKS_CONFIG")
 
 
-class _LayerFactors:
-    """Which rows have factors: keyed by a row's first block and a content
-    fingerprint of its first and last prompt blocks, so that a sequence reusing
-    a finished request's block ids rebuilds (reference ``mla_attn.py:212-239``)."""
-
-    def __init__(self):
-        self.entries = {}          # block0 -> (fingerprint, n_cache)
-
-
 class LocksMLAImpl(TritonMLAImpl):
 
     def __init__(self, *args, **kwargs):
         kwargs.pop("topk_indices_buffer", None)      # DSA-only kwarg, unused here
         super().__init__(*args, **kwargs)
         self._locks_state = None
-        self._locks_layers = {}
-        self._locks_out = None
 
     def _state(self, cache, bt, cfg):
+        B, MP = bt.shape
+        st = self._locks_state
+        if st is not None and (B > st.max_rows or MP > st.max_pages or
+                               cache.shape[0] > st.NB):
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("LOCKS MLA: the decode batch outgrew the "
+                                   "selection state during graph capture")
+            st = self._locks_state = None
         if self._locks_state is None:
-            B, MP = bt.shape
             self._locks_state = MlaState(
                 cache.device, num_layers=1, num_blocks=cache.shape[0],
-                max_rows=max(B, 1), max_pages=MP,
+                max_rows=max(B, 64), max_pages=MP,
                 budget_pages=_budget_pages(cfg, MP), sink_pages=cfg.sink_pages,
                 window_pages=cfg.window_pages)
         return self._locks_state
@@ -79,29 +77,9 @@ class LocksMLAImpl(TritonMLAImpl):
             qp[:, :H] = q
             q = qp
         q = q.contiguous()
-        # factors for rows seen for the first time (host bookkeeping, one sync)
-        lay = self._locks_layers.setdefault(id(layer), _LayerFactors())
-        sl_cpu = seq_lens.tolist()
-        b0 = bt[:, 0].tolist()
-        np_all = (seq_lens.clamp(min=1) + PAGE - 1) // PAGE
-        last = torch.gather(bt, 1, (np_all - 1).clamp(min=0)[:, None]).squeeze(1)
-        fp = (cache.index_select(0, bt[:, 0].long()).float()[:, :, :8].sum((1, 2))
-              + 1.0009 * cache.index_select(0, last.long()).float()[:, :, :8]
-              .sum((1, 2))).tolist()
-        n_cache = []
-        for r in range(B):
-            ent = lay.entries.get(b0[r])
-            nc = sl_cpu[r] // PAGE
-            if sl_cpu[r] <= 0:
-                n_cache.append(0)
-                continue
-            if ent is None or ent[0] != fp[r] or nc < ent[1]:
-                if nc > 0:
-                    build_page_factors(st, 0, cache, bt[r, :nc])
-                ent = (fp[r], nc)
-                lay.entries[b0[r]] = ent
-            n_cache.append(ent[1])
-        st.n_cache[:B] = torch.tensor(n_cache, dtype=torch.int32, device=q.device)
+        # factors of rows seen for the first time (or whose blocks were reused):
+        # flagged and rebuilt on the device
+        mla_refresh_rows(st, 0, cache, bt, seq_lens, B)
         scale = float(self.scale)
         out = torch.empty(B, HEADS, LKV, dtype=torch.bfloat16, device=q.device)
         lse = torch.empty(B, HEADS, dtype=torch.float32, device=q.device)

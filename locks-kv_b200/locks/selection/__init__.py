@@ -19,7 +19,7 @@ from .select import (append_advance, derive_page_params, nrmtopb_select,
                      topb_select)
 from .mla_select import (MlaState, build_page_factors, build_prompt_factors,
                          mla_decode, mla_derive, mla_forward, mla_page_score,
-                         mla_select_pages)
+                         mla_refresh_rows, mla_select_pages)
 
 __all__ = [
     "Rki4State", "TAGW", "rki4_build_refresh", "rki4_build_slots",
@@ -28,4 +28,5 @@ __all__ = [
     "nrmtopb_select", "rki4_score_only", "rki4_select_only", "rki4_score_state",
     "MlaState", "build_page_factors", "build_prompt_factors", "mla_derive",
     "mla_page_score", "mla_select_pages", "mla_decode", "mla_forward",
+    "mla_refresh_rows",
 ]

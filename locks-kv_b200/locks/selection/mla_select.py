@@ -51,6 +51,12 @@ class MlaState:
                                      dtype=i32)
         self.page_cnt = torch.zeros(max_rows, 1, device=device, dtype=i32)
         self.status = torch.zeros(1, device=device, dtype=i32)
+        # device-side factor bookkeeping (mla_refresh_rows): per layer and first
+        # block id a content fingerprint and the pages its factors cover
+        self.fp_tab = torch.zeros(num_layers, num_blocks, device=device, dtype=f32)
+        self.nc_tab = torch.full((num_layers, num_blocks), -1, device=device,
+                                 dtype=i32)
+        self.need = torch.zeros(max_rows, device=device, dtype=i32)
 
     def factors(self, layer: int, blocks):
         """(Lf (n,16,8), Rf (n,8,512)) fp32 views of the listed blocks (tests)."""
@@ -103,6 +109,26 @@ def build_prompt_factors(st: MlaState, caches, block_table, seq_lens, rows=None)
     for l, cache in enumerate(caches):
         build_page_factors(st, l, cache, blocks)
     return int(blocks.numel()) * len(caches)
+
+
+def mla_refresh_rows(st: MlaState, layer: int, cache, block_table, seq_lens,
+                     n_rows: int) -> None:
+    """Keep the factors of a decode batch valid with NO host synchronisation:
+    a gate kernel flags the rows whose factors are missing or stale (first
+    decode step, block ids reused by another request, a row that shrank) and
+    sets ``st.n_cache``; the factor kernel rebuilds the flagged rows' pages.
+    Fixed launch shapes: usable inside a captured graph.  What the reference's
+    ``_factors`` does on the host with one ``.tolist()`` per step
+    (``backend/mla_attn.py:118-133, 212-239``)."""
+    _check_cache(cache)
+    assert n_rows <= st.max_rows and block_table.shape[1] <= st.max_pages
+    _cabi.call("locks_mla_refresh_rows", _cabi.ptr(cache), cache.stride(0),
+               cache.stride(1), _cabi.ptr(st.records[layer]),
+               _cabi.ptr(block_table), block_table.stride(0), _cabi.ptr(seq_lens),
+               _cabi.ptr(st.fp_tab[layer]), _cabi.ptr(st.nc_tab[layer]),
+               _cabi.ptr(st.need), _cabi.ptr(st.n_cache), int(n_rows),
+               int(block_table.shape[1]), int(min(st.NB, cache.shape[0])),
+               _cabi.stream())
 
 
 def mla_derive(st: MlaState, seq_lens, n_rows: int) -> None:

@@ -228,3 +228,67 @@ def test_mla_tensor_core_decode_equals_warp_level_decode(lens):
         # kernel, hi+lo split P in the warp-level one)
         torch.testing.assert_close(o1, o0, atol=2e-2, rtol=1e-2)
         torch.testing.assert_close(l1, l0, atol=2e-3, rtol=2e-3)
+
+
+def test_mla_factor_bookkeeping_on_the_device():
+    """``mla_refresh_rows`` (no host synchronisation): first decode step builds
+    every row's factors; steady decode steps (the sequences grow, new tokens land
+    in later pages) flag nothing and keep n_cache; a finished request's block
+    ids handed to a new request are caught by the content fingerprint and
+    rebuilt; a row that shrank (preemption) is rebuilt."""
+    from locks import synth
+    from locks.selection import mla_select as ms
+    sh = synth.MlaShape(n_layers=1, budget_pages=24, sink_pages=1, window_pages=4)
+    lens = [777, 2053, 300, 40]
+    case = synth.make_mla_case(9, sh, lens, device=DEV, n_layers=1, max_pages=160)
+    cache, bt = case.caches[0], case.block_table
+    B, MP, NB = len(lens), int(bt.shape[1]), int(cache.shape[0])
+
+    def state():
+        return ms.MlaState(DEV, num_layers=1, num_blocks=NB, max_rows=8, max_pages=MP,
+                           budget_pages=24, sink_pages=1, window_pages=4)
+    st = state()
+    sl = case.seq_lens.clone()
+    ms.mla_refresh_rows(st, 0, cache, bt, sl, B)
+    torch.cuda.synchronize()
+    assert st.need[:B].tolist() == [1, 1, 1, 1]
+    assert st.n_cache[:B].tolist() == [n // 16 for n in lens]
+    ref = state()
+    ms.build_prompt_factors(ref, [cache], bt, sl)
+    torch.cuda.synchronize()
+    used = torch.cat([bt[r, :lens[r] // 16] for r in range(B)]).long()
+    assert torch.equal(st.records[0][used], ref.records[0][used])
+    # steady decode: 20 more tokens per row, written into the tail pages
+    g = torch.Generator().manual_seed(3)
+    for step in range(20):
+        for r in range(B):
+            tok = lens[r] + step
+            blk = int(bt[r, tok // 16]) if tok // 16 < -(-lens[r] // 16) else None
+            if blk is not None:
+                cache[blk, tok % 16] = torch.randn(576, generator=g).to(torch.bfloat16).to(DEV)
+        sl += 1
+        ms.mla_refresh_rows(st, 0, cache, bt, sl, B)
+    torch.cuda.synchronize()
+    assert st.need[:B].tolist() == [0, 0, 0, 0]
+    assert st.n_cache[:B].tolist() == [n // 16 for n in lens]      # entries as built
+    # row 2 finishes; a new request gets its block ids with other content
+    n2 = 300 // 16
+    cache[bt[2, :n2 + 1].long()] = torch.randn(n2 + 1, 16, 576, generator=g) \
+        .to(torch.bfloat16).to(DEV)
+    sl[2] = 290
+    ms.mla_refresh_rows(st, 0, cache, bt, sl, B)
+    torch.cuda.synchronize()
+    assert st.need[:B].tolist() == [0, 0, 1, 0]
+    assert int(st.n_cache[2]) == 290 // 16
+    ref = state()
+    ms.build_prompt_factors(ref, [cache], bt, sl, rows=[2])
+    torch.cuda.synchronize()
+    b2 = bt[2, :290 // 16].long()
+    assert torch.equal(st.records[0][b2], ref.records[0][b2])
+    # row 1 is preempted and resumes shorter than its entry
+    sl[1] = 1000
+    ms.mla_refresh_rows(st, 0, cache, bt, sl, B)
+    torch.cuda.synchronize()
+    assert st.need[:B].tolist() == [0, 1, 0, 0]
+    assert int(st.n_cache[1]) == 1000 // 16
+    st.check_status()
