@@ -1070,7 +1070,8 @@ def run_gpu_mla(args, seq_len):
                          budget_pages=budget, sink_pages=sh.sink_pages,
                          window_pages=sh.window_pages)
         ms.mla_derive(st, case.seq_lens, B)
-        st.tensor_core = os.environ.get("LOCKS_MLA_TC", "1") != "0"
+        if "LOCKS_MLA_TC" in os.environ:       # A/B switch; default: by tile count
+            st.tensor_core = os.environ["LOCKS_MLA_TC"] != "0"
         return st
     st = state(sh.budget_pages)
     t_build = timed(lambda: ms.build_prompt_factors(st, case.caches, case.block_table,

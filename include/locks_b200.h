@@ -555,7 +555,9 @@ int locks_mla_decode(const void* q, int64_t q_stride_row, const void* cache,
  * TMA tensor copies (2-D map over the cache seen as (num_blocks * 16, 576), box
  * 16 x 64, 128-byte swizzle) -- one copy of a page feeds both products.  Same
  * arguments and results as locks_mla_decode plus num_blocks (the tensor map's
- * extent).  Needs stride_block == 16 * stride_tok (LOCKS_ERR_GEOMETRY
+ * extent) and cnt_hint (the page count a long row is expected to keep, normally
+ * the budget: lets the kernel fetch its first page-table entries together with
+ * the count; any value is correct, a wrong guess costs one round trip).  Needs stride_block == 16 * stride_tok (LOCKS_ERR_GEOMETRY
  * otherwise: use locks_mla_decode).  The reference computes this step with
  * eager fp32 bmm (backend/mla_attn.py:178-201). */
 int locks_mla_decode_tc(const void* q, int64_t q_stride_row, const void* cache,
@@ -563,8 +565,8 @@ int locks_mla_decode_tc(const void* q, int64_t q_stride_row, const void* cache,
                         const int32_t* block_table, int64_t bt_stride,
                         const int32_t* page_table, const int32_t* page_cnt,
                         const int32_t* seq_lens, void* out, float* lse, int n_rows,
-                        int max_pages, int num_blocks, float scale, int* status,
-                        locks_stream_t stream);
+                        int max_pages, int num_blocks, int cnt_hint, float scale,
+                        int* status, locks_stream_t stream);
 
 #ifdef __cplusplus
 }

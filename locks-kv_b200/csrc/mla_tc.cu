@@ -83,6 +83,7 @@ struct TcParams {
     __nv_bfloat16* out;
     float* lse;
     int max_pages, num_blocks;
+    int cnt_hint;                  // pages a long row keeps (the budget): a guess
     float scale;
     int* status;
 };
@@ -201,13 +202,21 @@ mla_tc_decode_kernel(const __grid_constant__ CUtensorMap tmap, const TcParams p)
     }
     pdl_wait();                      // the page table comes from the selector
 
+    const int32_t* tab = p.page_table + (int64_t)row * p.max_pages;
+    const int32_t* bt = p.block_table + (int64_t)row * p.bt_stride;
+    // The first tile's page-table entries are fetched TOGETHER with the page count,
+    // at the place the count is expected to put them (a long row keeps exactly its
+    // budget): one dependent round trip less when the guess holds.
+    const int per_g = (p.cnt_hint + CL - 1) / CL;
+    const int jg = c * per_g + lane;
+    int spec_pt = -1;
+    if (warp == 0 && lane < TILE_PAGES && jg < p.max_pages) spec_pt = __ldcg(&tab[jg]);
     const int seq_len = p.seq_lens[row];
-    const int cnt = min(max(p.page_cnt[row], 0), p.max_pages);
+    const int cnt = min(max(__ldcg(&p.page_cnt[row]), 0), p.max_pages);
     const int per = (cnt + CL - 1) / CL;
     const int j0 = min(c * per, cnt), j1 = min(j0 + per, cnt);
     const int np = j1 - j0;
-    const int32_t* tab = p.page_table + (int64_t)row * p.max_pages;
-    const int32_t* bt = p.block_table + (int64_t)row * p.bt_stride;
+    const bool spec_ok = per == per_g && j0 == c * per_g;
 
     float acc[4][NH];
 #pragma unroll
@@ -227,7 +236,7 @@ mla_tc_decode_kernel(const __grid_constant__ CUtensorMap tmap, const TcParams p)
         if (warp == 0) {
             int pt = -1, blk = 0;
             if (lane < nt) {
-                pt = tab[j0 + t0 + lane];
+                pt = (t0 == 0 && spec_ok) ? spec_pt : tab[j0 + t0 + lane];
                 blk = min(max(bt[max(pt, 0)], 0), p.num_blocks - 1);
                 sm.tile_pt[lane] = pt;
             }
@@ -475,8 +484,8 @@ extern "C" int locks_mla_decode_tc(const void* q, int64_t q_stride_row,
                                    int64_t bt_stride, const int32_t* page_table,
                                    const int32_t* page_cnt, const int32_t* seq_lens,
                                    void* out, float* lse, int n_rows, int max_pages,
-                                   int num_blocks, float scale, int* status,
-                                   locks_stream_t stream) {
+                                   int num_blocks, int cnt_hint, float scale,
+                                   int* status, locks_stream_t stream) {
     LOCKS_REQUIRE(q && cache && block_table && page_table && page_cnt &&
                       seq_lens && out && lse,
                   LOCKS_ERR_ARG, "locks_mla_decode_tc: null pointer argument");
@@ -533,6 +542,7 @@ extern "C" int locks_mla_decode_tc(const void* q, int64_t q_stride_row,
     p.page_table = page_table; p.page_cnt = page_cnt; p.seq_lens = seq_lens;
     p.out = static_cast<__nv_bfloat16*>(out); p.lse = lse;
     p.max_pages = max_pages; p.num_blocks = num_blocks; p.scale = scale;
+    p.cnt_hint = min(max(cnt_hint, 0), max_pages);
     p.status = status;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(cl, n_rows, 1);

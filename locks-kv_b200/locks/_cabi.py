@@ -80,7 +80,7 @@ _SIGNATURES = {
     "locks_mla_score": ([_P, _L, _P, _P, _L, _L, _P, _L, _P, _P, _P, _I, _I,
                          _I, _F, _I, _P, _P], 1),
     "locks_mla_decode_tc": ([_P, _L, _P, _L, _L, _P, _L, _P, _P, _P, _P, _P, _I,
-                             _I, _I, _F, _P, _P], 1),
+                             _I, _I, _I, _F, _P, _P], 1),
     "locks_mla_decode": ([_P, _L, _P, _L, _L, _P, _L, _P, _P, _P, _P, _P, _I,
                           _I, _F, _P, _P], 1),
 }

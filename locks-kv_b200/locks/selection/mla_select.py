@@ -166,20 +166,36 @@ def mla_select_pages(st: MlaState, n_rows: int) -> None:
 def mla_decode(st: MlaState, q, cache, block_table, seq_lens, out, lse,
                n_rows: int, scale: float, tensor_core: bool = None) -> None:
     """o (rows,16,512) bf16 and lse (rows,16) f32 over the kept pages.
-    ``tensor_core``: the tcgen05 kernel (tokens in the M dimension, TMA page
-    gather) -- the default when the cache layout allows a tensor map (token rows
-    evenly spaced across blocks); False = the warp-level kernel."""
+    ``tensor_core``: True = the tcgen05 kernel (tokens in the M dimension, TMA
+    page gather; needs token rows evenly spaced across blocks), False = the
+    warp-level kernel.  Default (None, or ``st.tensor_core`` when set): the
+    tcgen05 kernel when a CTA's share of a row exceeds one 8-page tile -- many
+    pages kept, or many rows (measured: every page kept 3.5 against 4.2 ms per
+    4-layer step) -- and the warp-level kernel for the one-tile case, where the
+    two are latency chains within 2 % of each other and the warp-level one is
+    ahead (config 3: 150.5 against 153.6 us per layer)."""
     _check_cache(cache)
     if tensor_core is None:
-        tensor_core = getattr(st, "tensor_core", True) and \
-            cache.stride(0) == PAGE * cache.stride(1)
+        tensor_core = getattr(st, "tensor_core", None)
+    can_tc = cache.stride(0) == PAGE * cache.stride(1)
+    if tensor_core is None:
+        want = 148 // max(1, int(n_rows))
+        cl = 1
+        while cl * 2 <= want and cl < 8:
+            cl *= 2
+        if cl == 8 and 16 * int(n_rows) <= 148:
+            cl = 16
+        share = -(-min(st.budget_pages, st.max_pages) // cl)
+        tensor_core = share > 8
+    tensor_core = bool(tensor_core) and can_tc
     if tensor_core:
         _cabi.call("locks_mla_decode_tc", _cabi.ptr(q), q.stride(0),
                    _cabi.ptr(cache), cache.stride(0), cache.stride(1),
                    _cabi.ptr(block_table), block_table.stride(0),
                    _cabi.ptr(st.page_table), _cabi.ptr(st.page_cnt),
                    _cabi.ptr(seq_lens), _cabi.ptr(out), _cabi.ptr(lse), int(n_rows),
-                   int(st.max_pages), int(cache.shape[0]), float(scale),
+                   int(st.max_pages), int(cache.shape[0]),
+                   int(min(st.budget_pages, st.max_pages)), float(scale),
                    _cabi.ptr(st.status), _cabi.stream())
         return
     _cabi.call("locks_mla_decode", _cabi.ptr(q), q.stride(0), _cabi.ptr(cache),
