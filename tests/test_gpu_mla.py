@@ -178,6 +178,12 @@ def test_mla_full_size_properties():
                                   np.full(64, sh.page), case.scale)
         np.testing.assert_allclose(t2n(score[r, pages.to(dev)]), want, rtol=3e-3,
                                    atol=3e-3)
+    out_tc = torch.zeros_like(out)
+    lse_tc = torch.zeros_like(lse)
+    ms.mla_decode(st, case.q[0], case.caches[0], case.block_table, case.seq_lens,
+                  out_tc, lse_tc, B, case.scale, tensor_core=True)
+    torch.cuda.synchronize()
+    st.check_status()
     # attention over the kept pages, plain torch fp32
     for r in (0, 3, B - 1):
         pg = tab[r, :A].long()
@@ -189,6 +195,10 @@ def test_mla_full_size_properties():
         o_ref = torch.softmax(s_, -1) @ kv[:, :sh.kv_lora_rank]
         torch.testing.assert_close(out[r].float(), o_ref, atol=2e-2, rtol=1e-2)
         torch.testing.assert_close(lse[r], torch.logsumexp(s_, -1), atol=2e-2,
+                                   rtol=1e-2)
+        # the tcgen05 kernel on the same kept pages
+        torch.testing.assert_close(out_tc[r].float(), o_ref, atol=2e-2, rtol=1e-2)
+        torch.testing.assert_close(lse_tc[r], torch.logsumexp(s_, -1), atol=2e-2,
                                    rtol=1e-2)
 
 
