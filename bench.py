@@ -882,7 +882,7 @@ def cp_record(args, dev, rank, world, layers=8):
     def run(transport, solo=False):
         cp = ContextParallelHotPath(caches, bt, seq_len=seq_len, p0=p0, p1=p1,
                                     n_kv=sh.n_kv, G=sh.G, scale=scale, cfg=cfg,
-                                    transport=transport,
+                                    transport=transport, loopback=solo,
                                     group=None)
         if solo:          # every rank alone on its range: no peer in the links
             for d in cp._links:
@@ -897,9 +897,11 @@ def cp_record(args, dev, rank, world, layers=8):
     status = int(cp.st.status.item())
     rec.update({"us_per_layer": ms * 1e3 / layers, "ms_per_step": ms,
                 "launches_per_layer": 3, "status_word": status,
+                "path": ("in-kernel exchanges over NVLink peer memory" if world > 1
+                         else "one rank: the single-GPU kernels, nothing to exchange"),
                 "build_bulk_ms": t_build})
     recs = cp.st.pp_rec
-    # the streaming work alone (no exchange): same kernels, links to itself
+    # the exchange code with no peer: same kernels, links to the rank itself
     solo = run("fused", solo=True)
     solo.st.pp_rec.copy_(recs)
     solo.q.copy_(q)

@@ -71,7 +71,12 @@ class ContextParallelHotPath:
     def __init__(self, kv_caches: List[torch.Tensor], block_table: torch.Tensor,
                  *, seq_len: int, p0: int, p1: int, n_kv: int, G: int,
                  scale: float, cfg: LocksConfig, group=None,
-                 split: Optional[int] = None, transport: str = "fused"):
+                 split: Optional[int] = None, transport: str = "fused",
+                 loopback: bool = False):
+        """``loopback``: with ONE rank, still run the in-kernel exchanges, against
+        the rank's own link region (tests, and timing the exchange code without a
+        peer); by default a single rank has nothing to exchange and runs the
+        plain single-GPU kernels."""
         dev = kv_caches[0].device
         self.device, self.cfg, self.group = dev, cfg, group
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -142,7 +147,8 @@ class ContextParallelHotPath:
         # over NVLink peer memory (locks_cp_exchange), "nccl" = library
         # collectives (kept as the baseline the fused kernel is measured against)
         assert transport in ("fused", "peer", "nccl")
-        self.transport = transport if (self.world > 1 or transport == "fused") \
+        self.transport = transport if (self.world > 1 or
+                                       (transport == "fused" and loopback)) \
             else "none"
         self.hm_pad = None
         self.link = None
@@ -283,6 +289,18 @@ class ContextParallelHotPath:
             self._layers_fused()
             return
         st = self.st
+        if self.world == 1:
+            # one rank holds the whole sequence: the single-GPU kernels
+            from .attention import sparse_paged_decode_fused
+            for l in range(len(self.kv_caches)):
+                rki4_score_only(st, l, self.q[l], self.block_table, self.seq_lens,
+                                1, self.scale)
+                nrmtopb_select(st, 1, has_hmax=True)
+                sparse_paged_decode_fused(self.q[l], self.kv_caches[l],
+                                          self.block_table, self.seq_lens, st,
+                                          self.out[l], self.vsources[l],
+                                          scale=self.scale)
+            return
         for l in range(len(self.kv_caches)):
             rki4_score_only(st, l, self.q[l], self.block_table, self.seq_lens, 1,
                             self.scale)

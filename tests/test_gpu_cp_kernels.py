@@ -177,7 +177,7 @@ def _single_rank_pair(seq_len, seed=11, n_layers=3):
     hp.build_all(); hp.derive(); hp.q.copy_(q)
     cp = ContextParallelHotPath(caches, bt, seq_len=seq_len, p0=0, p1=npg,
                                 n_kv=shape.n_kv, G=shape.G, scale=scale, cfg=cfg,
-                                transport="fused")
+                                transport="fused", loopback=True)
     cp.st.pp_rec.copy_(hp.st.pp_rec)
     cp.q.copy_(q)
     return hp, cp, shape
