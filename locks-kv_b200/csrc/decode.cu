@@ -199,7 +199,9 @@ __device__ __forceinline__ void issue_page(DecSmem& sm, const DecParams& p,
     cp_async_commit();
 }
 
-template <bool G_HI, bool CLUSTER>
+// CP: context parallel (cluster mode only): the partial exchange with the peer
+// ranks is compiled in.
+template <bool G_HI, bool CLUSTER, bool CP = false>
 __global__ void __launch_bounds__(DTHREADS)
 decode_kernel(const DecParams p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -481,7 +483,7 @@ decode_kernel(const DecParams p) {
                 o += wt * sm.xacc[c * per_e + (e - sp * per_e)];
             }
         }
-        if (p.cp.world > 0) cp_merge_element(p.cp, kh, G, g, dd, M, Lsum, o, p.status);
+        if constexpr (CP) cp_merge_element(p.cp, kh, G, g, dd, M, Lsum, o, p.status);
         const float val = (Lsum > 0.f) ? o / Lsum : 0.f;
         p.out[(int64_t)r * p.out_stride_req + (int64_t)(kh * G + g) * HD + dd] =
             __float2bfloat16_rn(val);
@@ -591,6 +593,10 @@ int launch_decode(const char* who, const DecParams& p, int n_req, int grid_x,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         cudaFuncSetAttribute(decode_kernel<true, true>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaFuncSetAttribute(decode_kernel<false, true, true>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaFuncSetAttribute(decode_kernel<true, true, true>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         attr_done[dev] = true;
     }
     dim3 grid(grid_x, p.n_kv, n_req);
@@ -615,9 +621,13 @@ int launch_decode(const char* who, const DecParams& p, int n_req, int grid_x,
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
-    cudaError_t e = (p.G > 8)
-        ? cudaLaunchKernelEx(&cfg, decode_kernel<true, true>, p)
-        : cudaLaunchKernelEx(&cfg, decode_kernel<false, true>, p);
+    cudaError_t e;
+    if (p.cp.world > 0)
+        e = (p.G > 8) ? cudaLaunchKernelEx(&cfg, decode_kernel<true, true, true>, p)
+                      : cudaLaunchKernelEx(&cfg, decode_kernel<false, true, true>, p);
+    else
+        e = (p.G > 8) ? cudaLaunchKernelEx(&cfg, decode_kernel<true, true>, p)
+                      : cudaLaunchKernelEx(&cfg, decode_kernel<false, true>, p);
     if (e != cudaSuccess)
         return fail(LOCKS_ERR_LAUNCH, "%s: %s", who, cudaGetErrorString(e));
     return check_launch(who);
