@@ -201,6 +201,27 @@ int locks_decode_fused(const void* q, int64_t q_stride_req, const void* k_cache,
                        int head_dim, int page, int max_pages, float scale,
                        int* status, locks_stream_t stream);
 
+/* locks_decode_fused with the K/V pages staged by tiled tensor-map copies
+ * (cp.async.bulk.tensor.2d into 128-byte-swizzled shared memory, two 16 x 64
+ * boxes per plane and page) instead of 16-byte cp.async.  Same arguments plus
+ * num_blocks (the planes' block count: the maps' row extent); same results.
+ * The planes must be device memory laid out (num_blocks, 16, n_kv, 128) with
+ * kv_stride_block a multiple of kv_stride_tok (16 x for separate planes, 32 x
+ * for K and V interleaved per block) and kv_stride_head a multiple of 64
+ * (LOCKS_ERR_GEOMETRY otherwise: use locks_decode_fused).  The maps cover the
+ * launching GPU's memory only; no load is multicast.  No counterpart in the
+ * reference (its decode stages pages with cp.async, attention/decode_cuda.py:
+ * 269-584). */
+int locks_decode_fused_tma(const void* q, int64_t q_stride_req, const void* k_cache,
+                           const void* v_cache, int64_t kv_stride_block,
+                           int64_t kv_stride_tok, int64_t kv_stride_head,
+                           const int32_t* block_table, int64_t bt_stride,
+                           const int32_t* page_table, const int32_t* page_cnt,
+                           const int32_t* seq_lens, void* out,
+                           int64_t out_stride_req, int n_req, int n_kv, int G,
+                           int head_dim, int page, int max_pages, int num_blocks,
+                           float scale, int* status, locks_stream_t stream);
+
 /* Merge of split partials gathered from several ranks (context parallel: every
  * rank decodes the selected pages it holds, the partial sets are all-gathered,
  * every rank merges them).  No counterpart in the reference, which is single

@@ -23,9 +23,11 @@
 // output row directly: no partial buffers in HBM and no merge launch.
 #include <cooperative_groups.h>
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 #include "cp_link.cuh"
+#include "tma.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -77,6 +79,28 @@ struct __align__(128) DecSmem {
     float xacc[16 * HD + 16];
 };
 
+// TMA variant: a page of one kv-head arrives as two boxes of 16 rows x 64
+// columns per plane, each a [16][128 B] tile with the 128-byte swizzle (no row
+// padding needed: ldmatrix walks the swizzled pieces without bank conflicts).
+constexpr int HALF_TILE = PAGE_T * 128;           // bytes of one box
+constexpr int PAGE_TX = 4 * HALF_TILE;            // K + V bytes of one page
+struct WarpBufT {
+    uint8_t k[DSTAGES][2][PAGE_T][128];
+    uint8_t v[DSTAGES][2][PAGE_T][128];
+};
+static_assert(sizeof(WarpBufT) >= 16 * ACC_PITCH * 4, "combine buffer must fit");
+static_assert(sizeof(WarpBufT) % 1024 == 0, "swizzled tiles need 1 KiB alignment");
+
+struct __align__(1024) DecSmemT {
+    WarpBufT wb[DW];
+    float cm[DW][16];
+    float cl[DW][16];
+    float xm[8][16];
+    float xl[8][16];
+    float xacc[16 * HD + 16];
+    uint64_t full[DW][DSTAGES];    // one mbarrier per warp and ring stage
+};
+
 struct DecParams {
     const __nv_bfloat16* q;
     int64_t q_stride_req;
@@ -94,6 +118,7 @@ struct DecParams {
     __nv_bfloat16* out;            // fused mode only
     int64_t out_stride_req;
     int n_kv, G, max_pages, split, pps_min, fused;
+    int rows_per_block;            // tensor-map variant: token rows between blocks
     float scale;
     int* status;
     CpLink cp;          // context parallel: partials meet the peers' (world > 0)
@@ -199,13 +224,45 @@ __device__ __forceinline__ void issue_page(DecSmem& sm, const DecParams& p,
     cp_async_commit();
 }
 
+// TMA variant of issue_page: lanes 0-3 each issue one box (K low / K high /
+// V low / V high half of the head's 128 columns) of the page's 16 token rows.
+// The whole block row range is copied; V rows past seq_len are cleared by the
+// consumer and K rows past it only reach masked scores.
+__device__ __forceinline__ void issue_page_tma(DecSmemT& sm, const DecParams& p,
+                                               const CUtensorMap* tmk,
+                                               const CUtensorMap* tmv, int warp,
+                                               int lane, int stage, int kh, int pt,
+                                               int blk, int seq_len,
+                                               int& n_valid_out) {
+    n_valid_out = (pt >= 0) ? min(max(seq_len - pt * PAGE_T, 0), PAGE_T) : 0;
+    blk = max(blk, 0);
+    uint64_t* bar = &sm.full[warp][stage];
+    fence_proxy_async();
+    if (lane == 0) mbar_expect_tx(bar, PAGE_TX);
+    __syncwarp();
+    if (lane < 4) {
+        const int half = lane & 1;
+        uint8_t* dst = (lane < 2) ? &sm.wb[warp].k[stage][half][0][0]
+                                  : &sm.wb[warp].v[stage][half][0][0];
+        tma_load_2d(dst, (lane < 2) ? tmk : tmv,
+                    kh * (int)p.stride_head + 64 * half, blk * p.rows_per_block, bar);
+    }
+}
+
 // CP: context parallel (cluster mode only): the partial exchange with the peer
 // ranks is compiled in.
-template <bool G_HI, bool CLUSTER, bool CP = false>
-__global__ void __launch_bounds__(DTHREADS)
-decode_kernel(const DecParams p) {
+// TMA: K/V pages arrive by tiled tensor-map copies (cp.async.bulk.tensor.2d,
+// completion on a per-warp mbarrier) instead of 16-byte cp.async.
+template <bool G_HI, bool CLUSTER, bool CP, bool TMA>
+__device__ __forceinline__ void decode_body(const DecParams& p, const CUtensorMap* tmk,
+                                            const CUtensorMap* tmv) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    DecSmem& sm = *reinterpret_cast<DecSmem*>(smem_raw);
+    using Smem = typename std::conditional<TMA, DecSmemT, DecSmem>::type;
+    // the swizzled tiles of the TMA variant sit on 1 KiB boundaries
+    Smem& sm = *reinterpret_cast<Smem*>(
+        TMA ? reinterpret_cast<uint8_t*>(
+                  (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023))
+            : smem_raw);
 
     const int sp = blockIdx.x, kh = blockIdx.y, r = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -213,6 +270,13 @@ decode_kernel(const DecParams p) {
     const int G = p.G;
     const int64_t row = (int64_t)r * p.n_kv + kh;
     pdl_trigger();            // the next layer's scorer may start prefetching
+    if constexpr (TMA) {
+        if (lane == 0) {
+            for (int s = 0; s < DSTAGES; ++s) mbar_init(&sm.full[warp][s], 1);
+            mbar_fence_init();
+        }
+        __syncwarp();
+    }
     // remote shared memory may be written once every CTA of the cluster runs;
     // this barrier costs nothing while the selector is still at work
     if (CLUSTER) cg::this_cluster().sync();
@@ -264,8 +328,12 @@ decode_kernel(const DecParams p) {
     auto issue_it = [&](int it) {
         const int pt = __shfl_sync(0xffffffffu, win_pt, it & 31);
         const int blk = __shfl_sync(0xffffffffu, win_blk, it & 31);
-        issue_page(sm, p, warp, lane, it % DSTAGES, kh, pt, blk, seq_len,
-                   nv[it % DSTAGES]);
+        if constexpr (TMA)
+            issue_page_tma(sm, p, tmk, tmv, warp, lane, it % DSTAGES, kh, pt, blk,
+                           seq_len, nv[it % DSTAGES]);
+        else
+            issue_page(sm, p, warp, lane, it % DSTAGES, kh, pt, blk, seq_len,
+                       nv[it % DSTAGES]);
     };
     if (!CLUSTER) load_window(0);
     for (int it = 0; it < DSTAGES && it < n_mine; ++it) issue_it(it);
@@ -296,22 +364,42 @@ decode_kernel(const DecParams p) {
 
     for (int it = 0; it < n_mine; ++it) {
         const int stage = it % DSTAGES;
-        // groups complete in order; at most the next page's is younger
-        if (it + 1 < n_mine) cp_async_wait<1>(); else cp_async_wait<0>();
-        __syncwarp();                               // every lane's copies landed
         const int n_valid = nv[stage];
+        if constexpr (TMA) {
+            mbar_wait(&sm.full[warp][stage], (uint32_t)((it / DSTAGES) & 1), p.status);
+            if (n_valid > 0 && n_valid < PAGE_T) {
+                // rows past the sequence end hold whatever the block held before:
+                // clear them in V (P is 0 there, but 0 x NaN is not)
+                uint8_t* vt = reinterpret_cast<uint8_t*>(&sm.wb[warp].v[stage]);
+                for (int i = lane; i < (PAGE_T - n_valid) * 16; i += 32) {
+                    const int row = n_valid + (i >> 4), c = i & 15;
+                    *reinterpret_cast<uint4*>(vt + (c >> 3) * HALF_TILE + row * 128 +
+                                              (c & 7) * 16) = make_uint4(0, 0, 0, 0);
+                }
+                __syncwarp();
+            }
+        } else {
+            // groups complete in order; at most the next page's is younger
+            if (it + 1 < n_mine) cp_async_wait<1>(); else cp_async_wait<0>();
+            __syncwarp();                           // every lane's copies landed
+        }
         if (n_valid > 0) {
-            const uint32_t kbase = smem_u32(&sm.wb[warp].k[stage][0][0]);
-            const uint32_t vbase = smem_u32(&sm.wb[warp].v[stage][0][0]);
+            const uint32_t kbase = smem_u32(&sm.wb[warp].k[stage]);
+            const uint32_t vbase = smem_u32(&sm.wb[warp].v[stage]);
             // ---- S = Q K^T : two 16x8 token tiles ----------------------------
             float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
             {
                 const int t = (lane & 7) + 8 * ((lane >> 4) & 1);
-                const uint32_t a0 = kbase + t * ROWB + 16 * ((lane >> 3) & 1);
+                const int pc = (lane >> 3) & 1;             // 16-byte piece parity
+                const uint32_t a0 = TMA ? kbase + t * 128
+                                        : kbase + t * ROWB + 16 * pc;
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
                     uint32_t kb[4];
-                    ldmatrix_x4(kb, a0 + 32 * ks);
+                    // swizzled tile: piece 2*(ks&3)+pc of half ks>>2, XOR row&7
+                    ldmatrix_x4(kb, TMA ? a0 + (ks >> 2) * HALF_TILE +
+                                              (((2 * (ks & 3) + pc) ^ (lane & 7)) << 4)
+                                        : a0 + 32 * ks);
                     mma_bf16_k16(s0, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3],
                                  kb[0], kb[1]);
                     mma_bf16_k16(s1, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3],
@@ -370,11 +458,15 @@ decode_kernel(const DecParams p) {
             // ---- O += P V ------------------------------------------------------
             {
                 const int t = (lane & 7) + 8 * ((lane >> 3) & 1);
-                const uint32_t a0 = vbase + t * ROWB + 16 * ((lane >> 4) & 1);
+                const int pc = (lane >> 4) & 1;
+                const uint32_t a0 = TMA ? vbase + t * 128
+                                        : vbase + t * ROWB + 16 * pc;
 #pragma unroll
                 for (int dp = 0; dp < 8; ++dp) {
                     uint32_t vb[4];
-                    ldmatrix_x4_trans(vb, a0 + 32 * dp);
+                    ldmatrix_x4_trans(vb, TMA ? a0 + (dp >> 2) * HALF_TILE +
+                                                    (((2 * (dp & 3) + pc) ^ (lane & 7)) << 4)
+                                              : a0 + 32 * dp);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) vb[i] = bf16x2_to_f16x2(vb[i]);
                     mma_f16_k16(acc[2 * dp], ph[0], ph[1], ph[2], ph[3], vb[0], vb[1]);
@@ -488,6 +580,20 @@ decode_kernel(const DecParams p) {
         p.out[(int64_t)r * p.out_stride_req + (int64_t)(kh * G + g) * HD + dd] =
             __float2bfloat16_rn(val);
     }
+}
+
+template <bool G_HI, bool CLUSTER, bool CP = false>
+__global__ void __launch_bounds__(DTHREADS)
+decode_kernel(const DecParams p) {
+    decode_body<G_HI, CLUSTER, CP, false>(p, nullptr, nullptr);
+}
+
+// fused (cluster) decode with the pages staged by tensor-map copies
+template <bool G_HI>
+__global__ void __launch_bounds__(DTHREADS)
+decode_tma_kernel(const __grid_constant__ CUtensorMap tmk,
+                  const __grid_constant__ CUtensorMap tmv, const DecParams p) {
+    decode_body<G_HI, true, false, true>(p, &tmk, &tmv);
 }
 
 struct MergeParams {
@@ -773,6 +879,103 @@ extern "C" int locks_decode_fused(
     return launch_decode("locks_decode_fused", p, n_req,
                          fused_cluster_size(n_req, n_kv),
                          static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int locks_decode_fused_tma(
+    const void* q, int64_t q_stride_req, const void* k_cache,
+    const void* v_cache, int64_t kv_stride_block, int64_t kv_stride_tok,
+    int64_t kv_stride_head, const int32_t* block_table, int64_t bt_stride,
+    const int32_t* page_table, const int32_t* page_cnt, const int32_t* seq_lens,
+    void* out, int64_t out_stride_req, int n_req, int n_kv, int G, int head_dim,
+    int page, int max_pages, int num_blocks, float scale, int* status,
+    locks_stream_t stream) {
+    LOCKS_REQUIRE(q && k_cache && v_cache && block_table && page_table &&
+                      page_cnt && seq_lens && out,
+                  LOCKS_ERR_ARG, "locks_decode_fused_tma: null pointer argument");
+    int rc = check_geometry("locks_decode_fused_tma", G, head_dim, page);
+    if (rc) return rc;
+    rc = check_kv("locks_decode_fused_tma", q, k_cache, v_cache, q_stride_req,
+                  kv_stride_block, kv_stride_tok, kv_stride_head);
+    if (rc) return rc;
+    LOCKS_REQUIRE(n_req >= 0 && n_req <= 65535 && n_kv >= 1 && n_kv <= 65535 &&
+                      max_pages >= 1 && num_blocks >= 1,
+                  LOCKS_ERR_ARG, "locks_decode_fused_tma: bad size argument");
+    // the tensor maps see each plane as one matrix of token rows, kv_stride_tok
+    // apart, whose boxes start at row blk * (block stride / token stride) and
+    // column kh * head stride: a block's 16 rows evenly spaced, the block stride
+    // a whole number of rows (16 for separate planes, 32 for K and V interleaved
+    // per block), a head's 128 columns contiguous and inside the row
+    LOCKS_REQUIRE(kv_stride_tok > 0 && kv_stride_block % kv_stride_tok == 0 &&
+                      kv_stride_block / kv_stride_tok >= PAGE_T &&
+                      kv_stride_head >= HD &&
+                      (int64_t)(n_kv - 1) * kv_stride_head + HD <= kv_stride_tok &&
+                      kv_stride_head % 64 == 0 &&
+                      (int64_t)num_blocks * (kv_stride_block / kv_stride_tok) <
+                          (int64_t)1 << 31,
+                  LOCKS_ERR_GEOMETRY,
+                  "locks_decode_fused_tma: the cache planes must be (num_blocks, 16, "
+                  "n_kv, 128) with a block stride that is a multiple of the token "
+                  "stride (got %lld, %lld, %lld); use locks_decode_fused for other "
+                  "layouts",
+                  (long long)kv_stride_block, (long long)kv_stride_tok,
+                  (long long)kv_stride_head);
+    const int64_t rpb = kv_stride_block / kv_stride_tok;
+    const uint64_t rows = (uint64_t)(num_blocks - 1) * rpb + PAGE_T;
+    if (n_req == 0) return LOCKS_OK;
+    CUtensorMap tmk, tmv;
+    CUresult cr = encode_bf16_rows_sw128(&tmk, k_cache, (uint64_t)kv_stride_tok, rows,
+                                         (uint64_t)kv_stride_tok, PAGE_T);
+    if (cr == CUDA_SUCCESS)
+        cr = encode_bf16_rows_sw128(&tmv, v_cache, (uint64_t)kv_stride_tok, rows,
+                                    (uint64_t)kv_stride_tok, PAGE_T);
+    LOCKS_REQUIRE(cr == CUDA_SUCCESS, LOCKS_ERR_LAUNCH,
+                  "locks_decode_fused_tma: cuTensorMapEncodeTiled failed (%d)", (int)cr);
+    DecParams p{};
+    p.q = static_cast<const __nv_bfloat16*>(q); p.q_stride_req = q_stride_req;
+    p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
+    p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
+    p.stride_block = kv_stride_block; p.stride_tok = kv_stride_tok;
+    p.stride_head = kv_stride_head;
+    p.block_table = block_table; p.bt_stride = bt_stride;
+    p.page_table = page_table; p.page_cnt = page_cnt; p.seq_lens = seq_lens;
+    p.out = static_cast<__nv_bfloat16*>(out); p.out_stride_req = out_stride_req;
+    p.n_kv = n_kv; p.G = G; p.max_pages = max_pages; p.split = 1;
+    p.pps_min = 1; p.fused = 1; p.scale = scale; p.status = status;
+    p.rows_per_block = (int)rpb;
+
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int smem = (int)sizeof(DecSmemT) + 1024;     // room to align to 1 KiB
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        cudaFuncSetAttribute(decode_tma_kernel<false>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaFuncSetAttribute(decode_tma_kernel<true>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        attr_done[dev] = true;
+    }
+    const int cl = fused_cluster_size(n_req, n_kv);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(cl, n_kv, n_req);
+    cfg.blockDim = dim3(DTHREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cl;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    const cudaError_t e =
+        (G > 8) ? cudaLaunchKernelEx(&cfg, decode_tma_kernel<true>, tmk, tmv, p)
+                : cudaLaunchKernelEx(&cfg, decode_tma_kernel<false>, tmk, tmv, p);
+    if (e != cudaSuccess)
+        return fail(LOCKS_ERR_LAUNCH, "locks_decode_fused_tma: %s",
+                    cudaGetErrorString(e));
+    return check_launch("locks_decode_fused_tma");
 }
 
 extern "C" int locks_decode_fused_cp(

@@ -37,6 +37,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -135,14 +136,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x,
-                                            int y, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%2, %3}], [%4];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
-        : "memory");
 }
 // byte offset of (row, byte-in-row) inside a [rows][128 B] tile with the 128-byte
 // swizzle (16-byte pieces of a row XORed with the row number mod 8)
@@ -453,26 +446,6 @@ mla_tc_decode_kernel(const __grid_constant__ CUtensorMap tmap, const TcParams p)
     }
 }
 
-// cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time
-// dependency on the driver library)
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault,
-                                    &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(sym);
-    }
-    return fn;
-}
-
 }  // namespace
 }  // namespace locks
 
@@ -504,19 +477,10 @@ extern "C" int locks_mla_decode_tc(const void* q, int64_t q_stride_row,
                   "locks_mla_decode for other layouts",
                   (long long)stride_block, (long long)stride_tok);
     if (n_rows == 0) return LOCKS_OK;
-    EncodeTiledFn enc = encode_tiled();
-    LOCKS_REQUIRE(enc != nullptr, LOCKS_ERR_LAUNCH,
-                  "locks_mla_decode_tc: cuTensorMapEncodeTiled is not available");
     CUtensorMap tmap;
-    const cuuint64_t gdim[2] = {(cuuint64_t)WIDTH, (cuuint64_t)num_blocks * PG};
-    const cuuint64_t gstride[1] = {(cuuint64_t)stride_tok * 2};
-    const cuuint32_t box[2] = {64, (cuuint32_t)PG};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult cr = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                            const_cast<void*>(cache), gdim, gstride, box, estr,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUresult cr = encode_bf16_rows_sw128(&tmap, cache, WIDTH,
+                                               (uint64_t)num_blocks * PG,
+                                               (uint64_t)stride_tok, PG);
     LOCKS_REQUIRE(cr == CUDA_SUCCESS, LOCKS_ERR_LAUNCH,
                   "locks_mla_decode_tc: cuTensorMapEncodeTiled failed (%d)", (int)cr);
     const int smem = (int)sizeof(TcSmem) + 1024;       // room to align to 1 KiB

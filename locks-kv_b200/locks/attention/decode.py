@@ -9,6 +9,8 @@ is fixed-shape, allocation-free and sync-free.
 """
 from __future__ import annotations
 
+import os
+
 import math
 from typing import Protocol, Tuple
 
@@ -164,15 +166,46 @@ def sparse_paged_decode_batched(q, kv_cache, block_table, seq_lens, st, out,
                int(st.split), int(pps_min), _cabi.stream())
 
 
+# Page staging of the fused decode: False = 16-byte cp.async copies (any cache
+# strides, V may live in pinned host memory), True = tiled tensor-map copies
+# (cp.async.bulk.tensor.2d; needs both planes resident as (num_blocks, 16, n_kv,
+# 128) matrices).  LOCKS_DECODE_TMA=0/1 overrides for A/B timing.
+FUSED_TMA_DEFAULT = False
+
+
+def _tma_layout_ok(k, v, vsource) -> bool:
+    return (isinstance(vsource, ResidentVSource) and v.is_cuda
+            and k.stride(1) > 0 and k.stride(0) % k.stride(1) == 0
+            and k.stride(0) >= 16 * k.stride(1) and k.stride(2) % 64 == 0
+            and k.stride(2) >= 128
+            and (k.shape[2] - 1) * k.stride(2) + 128 <= k.stride(1))
+
+
 def sparse_paged_decode_fused(q, kv_cache, block_table, seq_lens, st, out,
-                              vsource, *, scale: float = None) -> None:
+                              vsource, *, scale: float = None,
+                              tma: bool = None) -> None:
     """One-launch decode: a CTA per (kv-head, request) walks every selected
     page and writes the final output (the reference's ``locks_decode_fused``,
-    ``attention/decode_cuda.py:587-884``; preferred at large batch)."""
+    ``attention/decode_cuda.py:587-884``; preferred at large batch).  ``tma``
+    picks the page staging (see ``FUSED_TMA_DEFAULT``)."""
     if scale is None:
         scale = st.scale
     n_req = int(seq_lens.shape[0])
     k, v = _kv_args(kv_cache, vsource)
+    if tma is None:                 # by default only where the layout allows it
+        env = os.environ.get("LOCKS_DECODE_TMA")
+        tma = (FUSED_TMA_DEFAULT if env is None else env == "1") and \
+            _tma_layout_ok(k, v, vsource)
+    if tma:
+        _cabi.call("locks_decode_fused_tma", _cabi.ptr(q), q.stride(0),
+                   _cabi.ptr(k), _cabi.ptr(v), k.stride(0), k.stride(1),
+                   k.stride(2), _cabi.ptr(block_table), block_table.stride(0),
+                   _cabi.ptr(st.page_table), _cabi.ptr(st.page_cnt),
+                   _cabi.ptr(seq_lens), _cabi.ptr(out), out.stride(0), n_req,
+                   int(st.n_kv), int(st.G), int(st.d), int(st.page),
+                   int(st.max_pages), int(k.shape[0]), float(scale),
+                   _cabi.ptr(st.status), _cabi.stream())
+        return
     _cabi.call("locks_decode_fused", _cabi.ptr(q), q.stride(0), _cabi.ptr(k),
                _cabi.ptr(v), k.stride(0), k.stride(1), k.stride(2),
                _cabi.ptr(block_table), block_table.stride(0),

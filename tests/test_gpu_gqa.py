@@ -235,6 +235,15 @@ def test_derive_score_select_decode(name):
                                   case.seq_lens, st, out2, vs, scale=case.scale)
         torch.cuda.synchronize()
         np.testing.assert_allclose(t2n(out2[:R]), ref64, atol=2e-2, rtol=1e-2)
+        # the same with the pages staged by tensor-map copies: same arithmetic
+        # in the same order, so the rows are bit-equal
+        out3 = torch.full_like(out, float("nan"))
+        sparse_paged_decode_fused(q[:R], case.kv_caches[l], case.block_table,
+                                  case.seq_lens, st, out3, vs, scale=case.scale,
+                                  tma=True)
+        torch.cuda.synchronize()
+        st.check_status()
+        assert torch.equal(out3[:R], out2[:R])
 
 
 def _assert_sets(tab, cnt, tab_ref, cnt_ref, score_ref, nsh, sink, tol=1e-3):

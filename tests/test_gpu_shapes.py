@@ -199,6 +199,50 @@ def test_decode_reads_v_from_pinned_host_memory():
     assert (out2[:2].float() - ref[:2].float()).abs().max().item() <= 2e-2
 
 
+def test_fused_decode_with_tensor_map_copies_ignores_stale_rows():
+    """The tensor-map variant copies whole 16-row pages; rows past the sequence
+    end (here filled with NaN and huge values) must not reach the output.  G = 4
+    and G = 16, ragged lengths with partial last pages, against the cp.async
+    variant (bit-equal) and the fp64 oracle."""
+    from locks import LocksConfig, synth
+    from locks.attention import ResidentVSource, sparse_paged_decode_fused
+    from locks.hotpath import HotPath
+    for n_kv, G in ((8, 4), (2, 16)):
+        sh = synth.GqaShape(n_layers=1, n_kv=n_kv, G=G, d=128, page=16,
+                            budget_pages=24, sink_pages=1, window_pages=3,
+                            n_needles=4, n_outlier=4)
+        lens = [3001, 517, 16 * 40, 33]
+        case = synth.make_gqa_case(21, sh, lens, device="cuda")
+        cache = case.kv_caches[0]
+        bt = case.block_table.cpu().numpy()
+        for r, n in enumerate(lens):          # poison the tail of the last page
+            if n % 16:
+                blk = int(bt[r, n // 16])
+                cache[blk, 0, n % 16:] = float("nan")
+                cache[blk, 1, n % 16:] = float("inf")
+        cfg = LocksConfig(budget_pages=24, sink_pages=1, window_pages=3)
+        hp = HotPath(case.kv_caches, case.block_table, case.seq_lens, n_kv=n_kv,
+                     G=G, scale=1 / math.sqrt(128), cfg=cfg)
+        hp.build_all(); hp.derive(); hp.q.copy_(case.q)
+        ref = hp.step_eager()[0].clone()              # cp.async staging
+        R = len(lens)
+        out = torch.full_like(ref, float("nan"))
+        sparse_paged_decode_fused(hp.q[0, :R], cache, case.block_table,
+                                  case.seq_lens, hp.st, out,
+                                  ResidentVSource(cache), scale=hp.scale, tma=True)
+        torch.cuda.synchronize()
+        hp.st.check_status()
+        assert torch.isfinite(out[:R].float()).all()
+        assert torch.equal(out[:R], ref[:R])
+        c = cache.float().cpu().numpy()
+        ref64, _ = orc.attention_over_pages(
+            hp.q[0, :R].float().cpu().numpy(), c[:, 0], c[:, 1], bt,
+            hp.st.page_table[:R].cpu().numpy(), hp.st.page_cnt[:R].cpu().numpy(),
+            case.seq_lens.cpu().numpy(), hp.scale, n_kv, G)
+        np.testing.assert_allclose(out[:R].float().cpu().numpy(), ref64,
+                                   atol=2e-2, rtol=1e-2)
+
+
 def test_ragged_batch_scores_equal_single_request_scores():
     """The scorer deals the CTAs of a kv-head to the requests of a batch by
     length; whatever the split, a request's scores must be bit-identical to the
