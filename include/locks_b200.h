@@ -222,6 +222,47 @@ int locks_decode_fused_tma(const void* q, int64_t q_stride_req, const void* k_ca
                            int head_dim, int page, int max_pages, int num_blocks,
                            float scale, int* status, locks_stream_t stream);
 
+/* locks_decode_fused with V behind a two-level tier (the decode seam of the
+ * reference's DRAM V tier: attention/decode.py:52-100, tier/decode_mem.py:
+ * 168-180, pool tier/pool.py:104-184).  K stays in the engine cache.  The V of
+ * EVERY physical block lives in v_host, a pinned host pool mapped into the
+ * device address space, laid out with the K plane's strides; v_hot is a bounded
+ * staging buffer in device memory (slots hot_stride_block elements apart, token
+ * and head strides as K's) and v_map[block] the block's slot in it, or -1.  A
+ * page whose block has a slot is read from v_hot, any other page in place from
+ * v_host over the host link: the same bytes either way, so the output equals
+ * locks_decode_fused on a resident V plane bit for bit.
+ * Residency notes for the host, written by the same launch: slot_ref[slot] = 1
+ * for every slot read; the block of every COMPLETE page that missed is appended
+ * once to miss_list (pending[block], one int32 per block, is the "already
+ * listed" flag; *miss_cnt counts every append, entries beyond miss_cap are
+ * dropped).  Who fills v_hot and v_map, and when, is the caller's business
+ * (locks.attention.vtier: one copy-engine cudaMemcpyAsync per run of contiguous
+ * blocks on a side stream between steps); the kernel only requires that a slot
+ * named by v_map holds its block's V while the kernel runs. */
+int locks_decode_fused_vtier(const void* q, int64_t q_stride_req, const void* k_cache,
+                             const void* v_host, int64_t kv_stride_block,
+                             int64_t kv_stride_tok, int64_t kv_stride_head,
+                             const void* v_hot, int64_t hot_stride_block,
+                             const int32_t* v_map, uint8_t* slot_ref,
+                             int32_t* pending, int32_t* miss_list, int32_t* miss_cnt,
+                             int miss_cap, const int32_t* block_table,
+                             int64_t bt_stride, const int32_t* page_table,
+                             const int32_t* page_cnt, const int32_t* seq_lens,
+                             void* out, int64_t out_stride_req, int n_req, int n_kv,
+                             int G, int head_dim, int page, int max_pages,
+                             float scale, int* status, locks_stream_t stream);
+
+/* V tier promotion: n_blocks consecutive blocks of the pinned host pool into
+ * n_blocks consecutive slots of the staging buffer as ONE copy-engine transfer
+ * (cudaMemcpyAsync, or cudaMemcpy2DAsync with one row per block when a side is
+ * pitched) on `stream` -- the reference's CopyEngine.memcpy_async /
+ * memcpy_2d_async (tier/dma.py:103-125).  No SM takes part.  src must be pinned
+ * for the copy to overlap the kernels of other streams. */
+int locks_vtier_copy_run(void* dst, int64_t dst_pitch_bytes, const void* src,
+                         int64_t src_pitch_bytes, int64_t block_bytes, int n_blocks,
+                         locks_stream_t stream);
+
 /* Merge of split partials gathered from several ranks (context parallel: every
  * rank decodes the selected pages it holds, the partial sets are all-gathered,
  * every rank merges them).  No counterpart in the reference, which is single

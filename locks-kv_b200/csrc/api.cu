@@ -67,6 +67,29 @@ int locks_version(void) { return LOCKS_ABI_VERSION; }
 
 const char* locks_last_error(void) { return locks::g_err; }
 
+int locks_vtier_copy_run(void* dst, int64_t dst_pitch_bytes, const void* src,
+                         int64_t src_pitch_bytes, int64_t block_bytes, int n_blocks,
+                         locks_stream_t stream) {
+    if (!dst || !src || block_bytes <= 0 || n_blocks < 0 ||
+        dst_pitch_bytes < block_bytes || src_pitch_bytes < block_bytes)
+        return locks::fail(LOCKS_ERR_ARG, "locks_vtier_copy_run: bad argument");
+    if (n_blocks == 0) return LOCKS_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // one copy-engine transfer for the whole run: plain when both sides are
+    // dense, a pitched 2-D copy (one row per block) otherwise
+    const cudaError_t e =
+        (dst_pitch_bytes == block_bytes && src_pitch_bytes == block_bytes)
+            ? cudaMemcpyAsync(dst, src, (size_t)block_bytes * n_blocks,
+                              cudaMemcpyHostToDevice, s)
+            : cudaMemcpy2DAsync(dst, (size_t)dst_pitch_bytes, src,
+                                (size_t)src_pitch_bytes, (size_t)block_bytes,
+                                (size_t)n_blocks, cudaMemcpyHostToDevice, s);
+    if (e != cudaSuccess)
+        return locks::fail(LOCKS_ERR_LAUNCH, "locks_vtier_copy_run: %s",
+                           cudaGetErrorString(e));
+    return LOCKS_OK;
+}
+
 int locks_record_bytes(int head_dim, int page) {
     if (head_dim != 128 || page != 16)
         return locks::fail(LOCKS_ERR_GEOMETRY,

@@ -119,6 +119,19 @@ struct DecParams {
     int64_t out_stride_req;
     int n_kv, G, max_pages, split, pps_min, fused;
     int rows_per_block;            // tensor-map variant: token rows between blocks
+    // V tier: v_cache is the pinned host pool (K's strides; read in place on a
+    // miss), v_hot the staging buffer in device memory (slots hot_stride_block
+    // apart, token and head strides as K's), v_map[block] the block's slot there
+    // or -1.  Residency notes for the host: a hit marks vt_ref[slot]; a miss on a
+    // complete page appends the block to vt_miss once (vt_pending[block] guards).
+    const int32_t* v_map;
+    const __nv_bfloat16* v_hot;
+    int64_t hot_stride_block;
+    uint8_t* vt_ref;
+    int32_t* vt_pending;
+    int32_t* vt_miss;
+    int32_t* vt_miss_cnt;
+    int vt_miss_cap;
     float scale;
     int* status;
     CpLink cp;          // context parallel: partials meet the peers' (world > 0)
@@ -199,9 +212,12 @@ __device__ __forceinline__ void cp_async_wait() {
 
 // One commit group per page: lane (h, c) = (lane >> 4, lane & 15) copies the
 // 16-byte chunk c of rows h, h + 2, ..., h + 14 of K and of V.
+// TIER: the V page comes from the staging buffer (slot >= 0) or, on a miss, in
+// place from the pinned host pool -- the same bytes either way.
+template <bool TIER>
 __device__ __forceinline__ void issue_page(DecSmem& sm, const DecParams& p,
                                            int warp, int lane, int stage,
-                                           int kh, int pt, int blk,
+                                           int kh, int pt, int blk, int slot,
                                            int seq_len, int& n_valid_out) {
     const int n_valid = (pt >= 0) ? min(max(seq_len - pt * PAGE_T, 0), PAGE_T) : 0;
     blk = max(blk, 0);
@@ -211,6 +227,11 @@ __device__ __forceinline__ void issue_page(DecSmem& sm, const DecParams& p,
                         8 * c;
     const __nv_bfloat16* ksrc = p.k_cache + off;
     const __nv_bfloat16* vsrc = p.v_cache + off;
+    if constexpr (TIER) {
+        if (slot >= 0)
+            vsrc = p.v_hot + (int64_t)slot * p.hot_stride_block +
+                   (int64_t)kh * p.stride_head + 8 * c;
+    }
     const uint32_t kdst = smem_u32(&sm.wb[warp].k[stage][0][16 * c]);
     const uint32_t vdst = smem_u32(&sm.wb[warp].v[stage][0][16 * c]);
 #pragma unroll
@@ -253,7 +274,7 @@ __device__ __forceinline__ void issue_page_tma(DecSmemT& sm, const DecParams& p,
 // ranks is compiled in.
 // TMA: K/V pages arrive by tiled tensor-map copies (cp.async.bulk.tensor.2d,
 // completion on a per-warp mbarrier) instead of 16-byte cp.async.
-template <bool G_HI, bool CLUSTER, bool CP, bool TMA>
+template <bool G_HI, bool CLUSTER, bool CP, bool TMA, bool TIER = false>
 __device__ __forceinline__ void decode_body(const DecParams& p, const CUtensorMap* tmk,
                                             const CUtensorMap* tmv) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -288,7 +309,7 @@ __device__ __forceinline__ void decode_body(const DecParams& p, const CUtensorMa
     // does not depend on the page count, so the count, the first window of
     // page-table entries and (one round trip later) their physical blocks are
     // fetched together.  Split mode gives a CTA a contiguous run of entries.
-    int win_pt = -1, win_blk = 0;
+    int win_pt = -1, win_blk = 0, win_slot = -1;
     const int stride = CLUSTER ? DW * (int)gridDim.x : DW;
     if (CLUSTER) {
         const int j = sp * DW + warp + lane * stride;
@@ -297,8 +318,25 @@ __device__ __forceinline__ void decode_body(const DecParams& p, const CUtensorMa
     }
     const int cnt = p.page_cnt ? __ldcg(&p.page_cnt[row])
                                : (max(seq_len, 0) + PAGE_T - 1) / PAGE_T;
-    if (CLUSTER)
+    // V tier: what the host needs to keep the staging buffer useful
+    auto tier_note = [&](int pt, int blk, int slot) {
+        if (pt < 0) return;
+        if (slot >= 0) {
+            p.vt_ref[slot] = 1;
+        } else if ((pt + 1) * PAGE_T <= seq_len &&      // complete pages only
+                   atomicExch(&p.vt_pending[blk], 1) == 0) {
+            const int idx = atomicAdd(p.vt_miss_cnt, 1);
+            if (idx < p.vt_miss_cap) p.vt_miss[idx] = blk;
+            else p.vt_pending[blk] = 0;      // not listed: may be noted again
+        }
+    };
+    if (CLUSTER) {
         win_blk = p.block_table[(int64_t)r * p.bt_stride + max(win_pt, 0)];
+        if constexpr (TIER) {
+            win_slot = p.v_map[max(win_blk, 0)];
+            tier_note(win_pt, max(win_blk, 0), win_slot);
+        }
+    }
     int first, jend;
     if (CLUSTER) {
         // an empty share still takes part in the cluster barrier below
@@ -318,11 +356,15 @@ __device__ __forceinline__ void decode_body(const DecParams& p, const CUtensorMa
     // loads are paid once per window instead of once per page.
     auto load_window = [&](int it0) {
         const int it = it0 + lane;
-        win_pt = -1; win_blk = 0;
+        win_pt = -1; win_blk = 0; win_slot = -1;
         if (it < n_mine) {
             const int j = first + it * stride;
             win_pt = p.page_table ? p.page_table[row * p.max_pages + j] : j;
             win_blk = p.block_table[(int64_t)r * p.bt_stride + max(win_pt, 0)];
+            if constexpr (TIER) {
+                win_slot = p.v_map[max(win_blk, 0)];
+                tier_note(win_pt, max(win_blk, 0), win_slot);
+            }
         }
     };
     auto issue_it = [&](int it) {
@@ -332,8 +374,9 @@ __device__ __forceinline__ void decode_body(const DecParams& p, const CUtensorMa
             issue_page_tma(sm, p, tmk, tmv, warp, lane, it % DSTAGES, kh, pt, blk,
                            seq_len, nv[it % DSTAGES]);
         else
-            issue_page(sm, p, warp, lane, it % DSTAGES, kh, pt, blk, seq_len,
-                       nv[it % DSTAGES]);
+            issue_page<TIER>(sm, p, warp, lane, it % DSTAGES, kh, pt, blk,
+                             TIER ? __shfl_sync(0xffffffffu, win_slot, it & 31) : -1,
+                             seq_len, nv[it % DSTAGES]);
     };
     if (!CLUSTER) load_window(0);
     for (int it = 0; it < DSTAGES && it < n_mine; ++it) issue_it(it);
@@ -586,6 +629,14 @@ template <bool G_HI, bool CLUSTER, bool CP = false>
 __global__ void __launch_bounds__(DTHREADS)
 decode_kernel(const DecParams p) {
     decode_body<G_HI, CLUSTER, CP, false>(p, nullptr, nullptr);
+}
+
+// fused (cluster) decode whose V pages come from the tier (staging buffer in
+// device memory, pinned host pool on a miss)
+template <bool G_HI>
+__global__ void __launch_bounds__(DTHREADS)
+decode_vtier_kernel(const DecParams p) {
+    decode_body<G_HI, true, false, false, true>(p, nullptr, nullptr);
 }
 
 // fused (cluster) decode with the pages staged by tensor-map copies
@@ -976,6 +1027,83 @@ extern "C" int locks_decode_fused_tma(
         return fail(LOCKS_ERR_LAUNCH, "locks_decode_fused_tma: %s",
                     cudaGetErrorString(e));
     return check_launch("locks_decode_fused_tma");
+}
+
+extern "C" int locks_decode_fused_vtier(
+    const void* q, int64_t q_stride_req, const void* k_cache, const void* v_host,
+    int64_t kv_stride_block, int64_t kv_stride_tok, int64_t kv_stride_head,
+    const void* v_hot, int64_t hot_stride_block, const int32_t* v_map,
+    uint8_t* slot_ref, int32_t* pending, int32_t* miss_list, int32_t* miss_cnt,
+    int miss_cap, const int32_t* block_table, int64_t bt_stride,
+    const int32_t* page_table, const int32_t* page_cnt, const int32_t* seq_lens,
+    void* out, int64_t out_stride_req, int n_req, int n_kv, int G, int head_dim,
+    int page, int max_pages, float scale, int* status, locks_stream_t stream) {
+    LOCKS_REQUIRE(q && k_cache && v_host && v_hot && v_map && slot_ref && pending &&
+                      miss_list && miss_cnt && block_table && page_table &&
+                      page_cnt && seq_lens && out,
+                  LOCKS_ERR_ARG, "locks_decode_fused_vtier: null pointer argument");
+    int rc = check_geometry("locks_decode_fused_vtier", G, head_dim, page);
+    if (rc) return rc;
+    rc = check_kv("locks_decode_fused_vtier", q, k_cache, v_host, q_stride_req,
+                  kv_stride_block, kv_stride_tok, kv_stride_head);
+    if (rc) return rc;
+    LOCKS_REQUIRE((reinterpret_cast<uintptr_t>(v_hot) & 15) == 0 &&
+                      hot_stride_block % 8 == 0 && miss_cap >= 0,
+                  LOCKS_ERR_ARG,
+                  "locks_decode_fused_vtier: the staging buffer must be 16-byte "
+                  "aligned with a slot stride that is a multiple of 8 elements");
+    LOCKS_REQUIRE(n_req >= 0 && n_req <= 65535 && n_kv >= 1 && n_kv <= 65535 &&
+                      max_pages >= 1,
+                  LOCKS_ERR_ARG, "locks_decode_fused_vtier: bad size argument");
+    if (n_req == 0) return LOCKS_OK;
+    DecParams p{};
+    p.q = static_cast<const __nv_bfloat16*>(q); p.q_stride_req = q_stride_req;
+    p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
+    p.v_cache = static_cast<const __nv_bfloat16*>(v_host);
+    p.v_hot = static_cast<const __nv_bfloat16*>(v_hot);
+    p.v_map = v_map; p.hot_stride_block = hot_stride_block;
+    p.vt_ref = slot_ref; p.vt_pending = pending; p.vt_miss = miss_list;
+    p.vt_miss_cnt = miss_cnt; p.vt_miss_cap = miss_cap;
+    p.stride_block = kv_stride_block; p.stride_tok = kv_stride_tok;
+    p.stride_head = kv_stride_head;
+    p.block_table = block_table; p.bt_stride = bt_stride;
+    p.page_table = page_table; p.page_cnt = page_cnt; p.seq_lens = seq_lens;
+    p.out = static_cast<__nv_bfloat16*>(out); p.out_stride_req = out_stride_req;
+    p.n_kv = n_kv; p.G = G; p.max_pages = max_pages; p.split = 1;
+    p.pps_min = 1; p.fused = 1; p.scale = scale; p.status = status;
+
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int smem = (int)sizeof(DecSmem);
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        cudaFuncSetAttribute(decode_vtier_kernel<false>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaFuncSetAttribute(decode_vtier_kernel<true>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        attr_done[dev] = true;
+    }
+    const int cl = fused_cluster_size(n_req, n_kv);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(cl, n_kv, n_req);
+    cfg.blockDim = dim3(DTHREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cl;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    const cudaError_t e = (G > 8) ? cudaLaunchKernelEx(&cfg, decode_vtier_kernel<true>, p)
+                                  : cudaLaunchKernelEx(&cfg, decode_vtier_kernel<false>, p);
+    if (e != cudaSuccess)
+        return fail(LOCKS_ERR_LAUNCH, "locks_decode_fused_vtier: %s",
+                    cudaGetErrorString(e));
+    return check_launch("locks_decode_fused_vtier");
 }
 
 extern "C" int locks_decode_fused_cp(

@@ -190,6 +190,10 @@ def sparse_paged_decode_fused(q, kv_cache, block_table, seq_lens, st, out,
     picks the page staging (see ``FUSED_TMA_DEFAULT``)."""
     if scale is None:
         scale = st.scale
+    if hasattr(vsource, "tier"):    # V behind the two-level tier (vtier.py)
+        vsource.tier.decode(vsource.layer, q, kv_cache, block_table, seq_lens, st,
+                            out, scale)
+        return
     n_req = int(seq_lens.shape[0])
     k, v = _kv_args(kv_cache, vsource)
     if tma is None:                 # by default only where the layout allows it

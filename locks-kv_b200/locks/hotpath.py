@@ -69,6 +69,7 @@ class HotPath:
         self.out = torch.zeros(LL, st.max_reqs, H, d, device=dev, dtype=torch.bfloat16)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.launches_per_step = 0
+        self.vtier = None
 
     # ---- summaries ---------------------------------------------------------
     def build_all(self) -> int:
@@ -99,8 +100,25 @@ class HotPath:
                                      self.cfg)
 
     def step_eager(self) -> torch.Tensor:
+        if self.vtier is not None:
+            self.vtier.promote()         # last step's missed blocks come in
         self._layers()
+        if self.vtier is not None:
+            self.vtier.end_step()        # this step's residency notes go back
         return self.out
+
+    def enable_vtier(self, n_slots: int, **kw):
+        """Move V behind the two-level tier (``locks.attention.vtier``): the V
+        planes are copied to pinned host memory, the decode reads selected pages
+        from a staging buffer of ``n_slots`` blocks per layer or, on a miss, in
+        place from the host; ``step_eager`` / ``step`` promote the misses
+        between steps.  The resident V halves are no longer read."""
+        from .attention.vtier import VTier
+        assert self.launch_layers == len(self.kv_caches)
+        self.vtier = VTier(self.kv_caches, n_slots, **kw)
+        self.vsources = [self.vtier.vsource(l) for l in range(len(self.kv_caches))]
+        self.graph = None
+        return self.vtier
 
     def capture(self) -> None:
         """Warm up (first-launch attribute set-up must happen outside capture)
@@ -121,7 +139,12 @@ class HotPath:
     def step(self) -> torch.Tensor:
         if self.graph is None:
             self.capture()
+        if self.vtier is not None:       # the promotion copies stay outside the graph
+            self.vtier.promote()
+            self.vtier.wait_all()
         self.graph.replay()
+        if self.vtier is not None:
+            self.vtier.end_step()
         return self.out
 
     # ---- one step fed from, and read back to, host memory ----------------------
