@@ -66,7 +66,7 @@ def workload(name: str, ctx: int | None):
     from locks import synth
     if name == "c0":
         sh, c = synth.CONFIG0, 4096
-    elif name == "c1":
+    elif name in ("c1", "c1vt"):
         sh, c = synth.CONFIG1, 131072
     elif name in ("c4", "c4cp"):
         sh, c = synth.CONFIG4, 1048576
@@ -1249,6 +1249,81 @@ def c2_line(args, dev, rank, world):
     }
 
 
+def vtier_line(args, sh, seq_len, dev):
+    """Config-1 geometry on a few layers with V behind the two-level tier:
+    resident V, tier with every selected block staged (steady state), tier with
+    nothing staged (every page read in place over the host link), and the cold
+    promotion (copy-engine runs) timed by itself."""
+    import dataclasses
+    from locks import LocksConfig
+    from locks.hotpath import HotPath
+    L = args.layers or 16
+    sh = dataclasses.replace(sh, n_layers=L)
+    caches, qs, bt, sl = make_device_case(sh, seq_len, dev, seed=1)
+    cfg = LocksConfig(budget_pages=sh.budget_pages, sink_pages=sh.sink_pages,
+                      window_pages=sh.window_pages)
+
+    def mk():
+        hp = HotPath(caches, bt, sl, n_kv=sh.n_kv, G=sh.G, scale=sh.d ** -0.5, cfg=cfg)
+        hp.build_all(); hp.derive()
+        hp.q[:, :1].copy_(qs)
+        return hp
+
+    def ms(step, n):
+        for _ in range(max(args.warmup, 3)):
+            step()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            step()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n
+
+    n = args.steps
+    hp = mk()
+    resident_ms = ms(hp.step, n)
+    want = hp.out.clone()
+    # nothing staged, nothing promoted: every V page crosses the host link
+    cold = mk()
+    cold.enable_vtier(8, max_promote_blocks=0)
+    inplace_ms = ms(cold.step, n)
+    same_inplace = bool(torch.equal(cold.out, want))
+    del cold
+    hot = mk()
+    tier = hot.enable_vtier(2048)
+    hot.step()                                   # notes the misses of the cold step
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    tier.promote(block=True); tier.wait_all(); torch.cuda.synchronize()
+    cold_promote_s = time.perf_counter() - t0
+    promoted = tier.stats["promoted_blocks"]
+    runs = tier.stats["copy_runs"]
+    blk_bytes = tier.block_elems * 2
+    staged_ms = ms(hot.step, n)
+    same_staged = bool(torch.equal(hot.out, want))
+    tier.promote(block=True); tier.wait_all(); tier.check()
+    return {
+        "metric": "sparse_decode_tokens_per_s", "value": 1e3 / staged_ms,
+        "unit": "tokens/s", "n_gpus": 1, "steps": n, "warmup": max(args.warmup, 3),
+        "ms_per_step": staged_ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"c1 geometry, {L} layers, ctx {seq_len - 1}, V behind "
+                   "the two-level tier (pinned host pool + 2048-block staging "
+                   "buffer per layer), step = CUDA-graph replay + host-side "
+                   "promotion calls"},
+        "gpu_launches": hot.launches_per_step * n,
+        "vtier": {"resident_v_ms": resident_ms, "staged_ms": staged_ms,
+                  "all_pages_in_place_over_host_link_ms": inplace_ms,
+                  "bit_equal_staged": same_staged, "bit_equal_in_place": same_inplace,
+                  "cold_promotion": {"blocks": promoted, "copy_runs": runs,
+                                     "seconds": cold_promote_s,
+                                     "gb_per_s": promoted * blk_bytes / cold_promote_s / 1e9},
+                  "steady_state_missed_blocks": tier.last_missed},
+    }
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1286,7 +1361,10 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    if args.workload_name == "c2":
+    if args.workload_name == "c1vt":
+        line = vtier_line(args, sh, seq_len, dev) \
+            if rank == 0 else None
+    elif args.workload_name == "c2":
         line = c2_line(args, dev, rank, world)
     elif args.workload_name == "c4cp":
         rec = cp_record(args, dev, rank, world, layers=args.layers or 8)

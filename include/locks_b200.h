@@ -234,9 +234,12 @@ int locks_decode_fused_tma(const void* q, int64_t q_stride_req, const void* k_ca
  * locks_decode_fused on a resident V plane bit for bit.
  * Residency notes for the host, written by the same launch: slot_ref[slot] = 1
  * for every slot read; the block of every COMPLETE page that missed is appended
- * once to miss_list (pending[block], one int32 per block, is the "already
- * listed" flag; *miss_cnt counts every append, entries beyond miss_cap are
- * dropped).  Who fills v_hot and v_map, and when, is the caller's business
+ * to miss_list once per note round (*note_round, a positive device word the
+ * host advances whenever it has consumed the list; pending[block], one int32
+ * per block, initially 0, remembers the round a block was last listed in;
+ * *miss_cnt counts every append, entries beyond miss_cap are dropped and may be
+ * listed again).  The host may clear miss_cnt and slot_ref while kernels run: a
+ * note lost that way comes back in the next round.  Who fills v_hot and v_map, and when, is the caller's business
  * (locks.attention.vtier: one copy-engine cudaMemcpyAsync per run of contiguous
  * blocks on a side stream between steps); the kernel only requires that a slot
  * named by v_map holds its block's V while the kernel runs. */
@@ -246,7 +249,8 @@ int locks_decode_fused_vtier(const void* q, int64_t q_stride_req, const void* k_
                              const void* v_hot, int64_t hot_stride_block,
                              const int32_t* v_map, uint8_t* slot_ref,
                              int32_t* pending, int32_t* miss_list, int32_t* miss_cnt,
-                             int miss_cap, const int32_t* block_table,
+                             int miss_cap, const int32_t* note_round,
+                             const int32_t* block_table,
                              int64_t bt_stride, const int32_t* page_table,
                              const int32_t* page_cnt, const int32_t* seq_lens,
                              void* out, int64_t out_stride_req, int n_req, int n_kv,

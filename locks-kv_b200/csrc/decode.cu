@@ -123,7 +123,8 @@ struct DecParams {
     // miss), v_hot the staging buffer in device memory (slots hot_stride_block
     // apart, token and head strides as K's), v_map[block] the block's slot there
     // or -1.  Residency notes for the host: a hit marks vt_ref[slot]; a miss on a
-    // complete page appends the block to vt_miss once (vt_pending[block] guards).
+    // complete page appends the block to vt_miss once per note round
+    // (vt_pending[block] holds the round, *vt_epoch, in which it was last listed).
     const int32_t* v_map;
     const __nv_bfloat16* v_hot;
     int64_t hot_stride_block;
@@ -131,6 +132,7 @@ struct DecParams {
     int32_t* vt_pending;
     int32_t* vt_miss;
     int32_t* vt_miss_cnt;
+    const int32_t* vt_epoch;
     int vt_miss_cap;
     float scale;
     int* status;
@@ -323,11 +325,13 @@ __device__ __forceinline__ void decode_body(const DecParams& p, const CUtensorMa
         if (pt < 0) return;
         if (slot >= 0) {
             p.vt_ref[slot] = 1;
-        } else if ((pt + 1) * PAGE_T <= seq_len &&      // complete pages only
-                   atomicExch(&p.vt_pending[blk], 1) == 0) {
-            const int idx = atomicAdd(p.vt_miss_cnt, 1);
-            if (idx < p.vt_miss_cap) p.vt_miss[idx] = blk;
-            else p.vt_pending[blk] = 0;      // not listed: may be noted again
+        } else if ((pt + 1) * PAGE_T <= seq_len) {      // complete pages only
+            const int round = __ldcg(p.vt_epoch);
+            if (atomicExch(&p.vt_pending[blk], round) != round) {
+                const int idx = atomicAdd(p.vt_miss_cnt, 1);
+                if (idx < p.vt_miss_cap) p.vt_miss[idx] = blk;
+                else p.vt_pending[blk] = 0;  // not listed: may be noted again
+            }
         }
     };
     if (CLUSTER) {
@@ -1034,13 +1038,14 @@ extern "C" int locks_decode_fused_vtier(
     int64_t kv_stride_block, int64_t kv_stride_tok, int64_t kv_stride_head,
     const void* v_hot, int64_t hot_stride_block, const int32_t* v_map,
     uint8_t* slot_ref, int32_t* pending, int32_t* miss_list, int32_t* miss_cnt,
-    int miss_cap, const int32_t* block_table, int64_t bt_stride,
+    int miss_cap, const int32_t* note_round, const int32_t* block_table,
+    int64_t bt_stride,
     const int32_t* page_table, const int32_t* page_cnt, const int32_t* seq_lens,
     void* out, int64_t out_stride_req, int n_req, int n_kv, int G, int head_dim,
     int page, int max_pages, float scale, int* status, locks_stream_t stream) {
     LOCKS_REQUIRE(q && k_cache && v_host && v_hot && v_map && slot_ref && pending &&
-                      miss_list && miss_cnt && block_table && page_table &&
-                      page_cnt && seq_lens && out,
+                      miss_list && miss_cnt && note_round && block_table &&
+                      page_table && page_cnt && seq_lens && out,
                   LOCKS_ERR_ARG, "locks_decode_fused_vtier: null pointer argument");
     int rc = check_geometry("locks_decode_fused_vtier", G, head_dim, page);
     if (rc) return rc;
@@ -1063,7 +1068,7 @@ extern "C" int locks_decode_fused_vtier(
     p.v_hot = static_cast<const __nv_bfloat16*>(v_hot);
     p.v_map = v_map; p.hot_stride_block = hot_stride_block;
     p.vt_ref = slot_ref; p.vt_pending = pending; p.vt_miss = miss_list;
-    p.vt_miss_cnt = miss_cnt; p.vt_miss_cap = miss_cap;
+    p.vt_miss_cnt = miss_cnt; p.vt_miss_cap = miss_cap; p.vt_epoch = note_round;
     p.stride_block = kv_stride_block; p.stride_tok = kv_stride_tok;
     p.stride_head = kv_stride_head;
     p.block_table = block_table; p.bt_stride = bt_stride;

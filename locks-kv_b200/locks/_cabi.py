@@ -70,8 +70,8 @@ _SIGNATURES = {
                             _L, _I, _I, _I, _I, _I, _I, _F, _P, _P], 1),
     "locks_vtier_copy_run": ([_P, _L, _P, _L, _L, _I, _P], 0),
     "locks_decode_fused_vtier": ([_P, _L, _P, _P, _L, _L, _L, _P, _L, _P, _P, _P,
-                                  _P, _P, _I, _P, _L, _P, _P, _P, _P, _L, _I, _I,
-                                  _I, _I, _I, _I, _F, _P, _P], 1),
+                                  _P, _P, _I, _P, _P, _L, _P, _P, _P, _P, _L, _I,
+                                  _I, _I, _I, _I, _I, _F, _P, _P], 1),
     "locks_decode_fused_tma": ([_P, _L, _P, _P, _L, _L, _L, _P, _L, _P, _P, _P, _P,
                                 _L, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P], 1),
     "locks_dense_decode": ([_P, _L, _P, _P, _L, _L, _L, _P, _L, _P, _P, _P, _P,

@@ -13,13 +13,18 @@ GPU with a fast host link:
   from its slot when it has one and in place from the pool otherwise (same
   bytes, same output), marks the slots it read and lists the blocks of complete
   pages that missed;
-* between steps the host reads the lists back, picks victims with a CLOCK hand
-  that skips slots read in the last step, and brings the missed blocks in with
-  ONE ``cudaMemcpyAsync`` per run of contiguous blocks (runs land in contiguous
-  slots) on a side stream that is never captured -- the copy engine, no SM
-  involved -- layer by layer, each layer's map update behind its copies.  The
-  next step's decode of layer l waits for layer l's event only, so the copies
-  of later layers overlap the earlier layers' kernels.
+* after a step the notes are read back on a side stream; before a later step
+  the host -- without ever waiting for the GPU -- picks victims with a CLOCK
+  hand that skips slots read since the last round and brings the missed blocks
+  in with ONE ``cudaMemcpyAsync`` per run of contiguous blocks (runs land in
+  contiguous slots) on that side stream, which is never captured -- the copy
+  engine, no SM involved -- layer by layer, each layer's map update behind its
+  copies.  The copies start behind everything already enqueued (no decode that
+  could read a victim slot is in flight) and the next decode of layer l waits
+  for layer l's event only, so the copies of later layers overlap the earlier
+  layers' kernels.  With nothing to promote no stream waits for anything.  A
+  miss therefore costs one or two steps of in-place reads (the reference's
+  promote-at-graph-head protocol takes two, ``tier/k5.py:1-69``).
 
 Invariants kept (and asserted by ``VTier.check()``): every block's V is in the
 pool (I1); the host mirror, the device map and the slot owners agree (I2); no
@@ -155,6 +160,9 @@ class VTier:
         self.pending = torch.zeros(self.L, self.NB, device=dev, dtype=torch.int32)
         self.miss = torch.zeros(self.L, self.miss_cap, device=dev, dtype=torch.int32)
         self.miss_cnt = torch.zeros(self.L, device=dev, dtype=torch.int32)
+        self.round = 1
+        self.note_round = torch.full((1,), self.round, device=dev, dtype=torch.int32)
+        self.last_missed = 0
         # pinned landing buffers of the read-back
         self.h_ref = torch.zeros(self.L, self.n_slots, dtype=torch.uint8,
                                  pin_memory=True)
@@ -201,7 +209,8 @@ class VTier:
                    self.hot[layer].stride(0), _cabi.ptr(self.v_map[layer]),
                    _cabi.ptr(self.ref[layer]), _cabi.ptr(self.pending[layer]),
                    _cabi.ptr(self.miss[layer]), _cabi.ptr(self.miss_cnt[layer:]),
-                   self.miss_cap, _cabi.ptr(block_table), block_table.stride(0),
+                   self.miss_cap, _cabi.ptr(self.note_round), _cabi.ptr(block_table),
+                   block_table.stride(0),
                    _cabi.ptr(st.page_table), _cabi.ptr(st.page_cnt),
                    _cabi.ptr(seq_lens), _cabi.ptr(out), out.stride(0), n_req,
                    int(st.n_kv), int(st.G), int(st.d), int(st.page),
@@ -210,8 +219,12 @@ class VTier:
 
     # ---- between steps -------------------------------------------------------------
     def end_step(self) -> None:
-        """After the step's last decode was enqueued: start reading the
-        residency notes back (side stream, behind the step)."""
+        """After a step's last decode was enqueued: start reading the residency
+        notes back (side stream, behind the step) unless an earlier read-back
+        is still waiting to be consumed -- the notes keep accumulating."""
+        self.stats["steps"] += 1
+        if self._readback_pending:
+            return
         ev = torch.cuda.Event()
         ev.record(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(self.side):
@@ -221,36 +234,57 @@ class VTier:
             self.h_cnt.copy_(self.miss_cnt, non_blocking=True)
             self.ev_read.record(self.side)
         self._readback_pending = True
-        self.stats["steps"] += 1
 
-    def promote(self) -> None:
-        """Before the next step is enqueued: bring last step's misses in.
-        Blocks the host until the read-back has landed (the step is over by
-        then in a serving loop: sampling sits in between)."""
+    def promote(self, block: bool = False) -> bool:
+        """Before a step is enqueued: consume the last read-back and bring the
+        listed blocks in.  Never waits for the GPU unless ``block``: when the
+        read-back has not landed yet the step simply runs with what is staged
+        (a miss is read in place) and the promotion happens one step later.
+        True when a read-back was consumed."""
         if not self._readback_pending:
-            return
+            return False
+        if block:
+            self.ev_read.synchronize()
+        elif not self.ev_read.query():
+            return False
         self._readback_pending = False
-        self.ev_read.synchronize()
-        cnt = self.h_cnt.numpy()
+        cnt = self.h_cnt.numpy().copy()
+        plans = []
+        for l in range(self.L):
+            n = int(cnt[l])
+            listed = self.h_miss[l, :min(n, self.miss_cap)].numpy().copy()
+            self.stats["missed_blocks"] += n
+            self.stats["dropped_notes"] += max(0, n - self.miss_cap)
+            runs, upd = self.clock[l].plan(listed, self.h_ref[l].numpy(),
+                                           self.max_promote) if n else ([], [])
+            plans.append((runs, upd))
+        self.last_missed = int(cnt.sum())
+        main = torch.cuda.current_stream(self.device)
+        busy = any(upd for _, upd in plans)
+        ev_main = None
+        if busy:
+            # a slot may be overwritten only when no decode that could still
+            # read it is in flight: the copies start behind everything enqueued
+            ev_main = torch.cuda.Event()
+            ev_main.record(main)
         with torch.cuda.stream(self.side):
-            # the notes were read: clear them before any layer is released
+            # a new note round: blocks listed so far may be listed again; notes
+            # written while these three run are lost and come back next round
+            self.round += 1
+            self.note_round.fill_(self.round)
             self.ref.zero_()
             self.miss_cnt.zero_()
-            for l in range(self.L):
-                n = int(cnt[l])
-                listed = self.h_miss[l, :min(n, self.miss_cap)].numpy().copy()
-                self.stats["missed_blocks"] += n
-                self.stats["dropped_notes"] += max(0, n - self.miss_cap)
-                runs, upd = self.clock[l].plan(listed, self.h_ref[l].numpy(),
-                                               self.max_promote)
-                if n or upd:
-                    self._apply(l, runs, upd, listed)
-                self.ev_layer[l].record(self.side)
-                self._layer_ready[l] = False
+            if busy:
+                self.side.wait_event(ev_main)
+                for l, (runs, upd) in enumerate(plans):
+                    if upd:
+                        self._apply(l, runs, upd)
+                    self.ev_layer[l].record(self.side)
+                    self._layer_ready[l] = False
+        return True
 
-    def _apply(self, l, runs, upd, listed) -> None:
-        """Side stream: unmap the victims, copy the runs, map the new blocks,
-        re-arm the 'already listed' flags of everything that was listed."""
+    def _apply(self, l, runs, upd) -> None:
+        """Side stream: unmap the victims, copy the runs, map the new blocks."""
         dev = self.device
         if upd:
             blk = torch.tensor([b for b, _ in upd], dtype=torch.int64)
@@ -273,9 +307,6 @@ class VTier:
             # 3. the new owners become visible behind their copies
             self.v_map[l].index_copy_(0, blk.to(dev, non_blocking=True),
                                       new.to(dev, non_blocking=True))
-        if len(listed):
-            idx = torch.from_numpy(np.asarray(listed, dtype=np.int64))
-            self.pending[l].index_fill_(0, idx.to(dev, non_blocking=True), 0)
 
     def invalidate_blocks(self, blocks: Sequence[int]) -> None:
         """Blocks whose content now belongs to another sequence: forget them in

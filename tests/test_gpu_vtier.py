@@ -49,10 +49,10 @@ def test_tiered_decode_equals_resident_decode_while_selections_move():
         torch.cuda.synchronize()
         tiered.st.check_status()
         assert torch.equal(got[:, :R], want[:, :R]), f"step {step}"
-        tier.promote()                   # bring this step's misses in, then check
+        tier.promote(block=True)         # bring this step's misses in, then check
         tier.wait_all()
         tier.check()
-        if int(tier.h_cnt.sum()) == 0:
+        if tier.last_missed == 0:
             hit_steps += 1
     assert tier.stats["promoted_blocks"] > 0
     assert tier.stats["copy_runs"] <= tier.stats["promoted_blocks"]
@@ -72,7 +72,7 @@ def test_small_staging_buffer_evicts_and_stays_exact():
         got = tiered.step_eager().clone()
         torch.cuda.synchronize()
         assert torch.equal(got[:, :R], want[:, :R]), f"step {step}"
-        tier.promote(); tier.wait_all(); tier.check()
+        tier.promote(block=True); tier.wait_all(); tier.check()
         for l in range(tier.L):
             assert tier.resident_blocks(l) <= 20
     assert tier.stats["missed_blocks"] > tier.stats["promoted_blocks"] > 20
@@ -84,7 +84,7 @@ def test_block_handed_to_another_sequence_is_dropped():
     for _ in range(3):                   # stage what the query selects
         ref.q.copy_(case.q); tiered.q.copy_(case.q)
         ref.step_eager(); tiered.step_eager()
-    tier.promote(); tier.wait_all(); tier.check()
+    tier.promote(block=True); tier.wait_all(); tier.check()
     l = 0
     staged = (tier.clock[l].slot_of >= 0).nonzero()[0][:5].tolist()
     assert staged
@@ -100,7 +100,7 @@ def test_block_handed_to_another_sequence_is_dropped():
         got = tiered.step_eager().clone()
         torch.cuda.synchronize()
         assert torch.equal(got[:, :1], want[:, :1])
-    tier.promote(); tier.wait_all(); tier.check()
+    tier.promote(block=True); tier.wait_all(); tier.check()
 
 
 def test_tiered_step_as_a_graph_replay():
@@ -112,5 +112,5 @@ def test_tiered_step_as_a_graph_replay():
         got = tiered.step().clone()
         torch.cuda.synchronize()
         assert torch.equal(got[:, :2], want[:, :2])
-    tier.promote(); tier.wait_all(); tier.check()
-    assert int(tier.h_cnt.sum()) == 0 or tier.stats["promoted_blocks"] > 0
+    tier.promote(block=True); tier.wait_all(); tier.check()
+    assert tier.last_missed == 0 or tier.stats["promoted_blocks"] > 0
