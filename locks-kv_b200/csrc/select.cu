@@ -130,11 +130,6 @@ constexpr int HCOPIES = 4;                        // histogram copies, by lane &
 constexpr int RBITS0 = 11, RBITS1 = 11, RBITS2 = 10;
 constexpr int NBINS = 1 << RBITS0;                // 2048 (largest digit)
 constexpr int MAX_CL = 16;            // > 8 needs the non-portable cluster attribute
-// two-level selection of long rows: candidate slots in CTA 0 (keys, then pages),
-// followed by one spare 128-key row per warp that reads as holes
-constexpr int CAND_CAP = 4096;
-constexpr int CAND_PAGES_AT = CAND_CAP + 128;
-constexpr int CAND_WORDS = CAND_PAGES_AT + CAND_CAP;
 
 struct SelSmem {
     int tot[NBINS];                // sliced mode: cluster totals of the digit (CTA 0)
@@ -453,131 +448,6 @@ __device__ __forceinline__ void cp_global_cut(const CpLink& cp, int kh,
     if (tid == 0) *cnt_out = base;
 }
 
-// Exact top-b over keys[0, n) held in this CTA's shared memory, all NT threads:
-// the radix threshold search on local histograms (h4), then the ascending
-// compaction.  Keys 0 are holes, keys 0xFFFFFFFF always stay, of the others the
-// b largest stay with ties going to the lower index; `n_sel` is how many of the
-// others there are.  emit(slot, index, key) is called once per kept key, slots
-// ascending with the index; returns the number kept.  keys[] must be readable
-// (holes) up to n rounded up to 128 per warp share.
-template <int NT, class Emit>
-__device__ __forceinline__ int select_in_cta(SelSmem& sm, const uint32_t* keys,
-                                             int* h4, int n, int b, int n_sel,
-                                             Emit emit) {
-    constexpr int NW = NT / 32;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    uint32_t tau_key = 0u;
-    int quota = 0;
-    if (b <= 0) {
-        tau_key = 0xFFFFFFFEu;
-    } else if (b < n_sel) {
-        uint32_t prefix = 0u, mask = 0u;
-        int k = b, shift = 32;
-        bool whole_bin = false;
-#pragma unroll 1
-        for (int pass = 0; pass < 3 && !whole_bin; ++pass) {
-            const int bits = (pass == 0) ? RBITS0 : (pass == 1) ? RBITS1 : RBITS2;
-            const int nb = 1 << bits;
-            shift -= bits;
-            const uint32_t dmask = (uint32_t)nb - 1u;
-            for (int base = 4 * tid; base < n; base += 4 * NT) {
-                const uint4 kv = *reinterpret_cast<const uint4*>(&keys[base]);
-                const uint32_t kk[4] = {kv.x, kv.y, kv.z, kv.w};
-#pragma unroll
-                for (int s = 0; s < 4; ++s) {
-                    const uint32_t key = kk[s];
-                    if (key - 1u < 0xFFFFFFFEu && (key & mask) == prefix)
-                        atomicAdd(&h4[(hslot((key >> shift) & dmask) << 2) |
-                                      (lane & 3)], 1);
-                }
-            }
-            __syncthreads();
-            if (warp < AW) find_digit_active<true>(sm, h4, nb, k);
-            __syncthreads();
-            prefix |= (uint32_t)sm.sh_i0 << shift;
-            k = sm.sh_i1;
-            mask |= dmask << shift;
-            whole_bin = (sm.sh_i2 == k);
-        }
-        if (whole_bin) { tau_key = prefix ? prefix - 1u : 0u; quota = 0; }
-        else { tau_key = prefix; quota = k; }
-    }
-    const uint32_t lt_mask = (1u << lane) - 1u;
-    const int WS = (((n + NW - 1) / NW) + 127) & ~127;
-    const int w0 = min(warp * WS, n), w1 = min(w0 + WS, n);
-    const bool ties = quota > 0;
-    int c_sure = 0, c_eq = 0;
-    for (int it = w0; it < w1; it += 128) {
-        const uint4 kv = *reinterpret_cast<const uint4*>(&keys[it + 4 * lane]);
-        c_sure += (kv.x > tau_key) + (kv.y > tau_key) + (kv.z > tau_key) +
-                  (kv.w > tau_key);
-        c_eq += (kv.x == tau_key) + (kv.y == tau_key) + (kv.z == tau_key) +
-                (kv.w == tau_key);
-    }
-#pragma unroll
-    for (int o = 16; o >= 1; o >>= 1) {
-        c_eq += __shfl_xor_sync(0xffffffffu, c_eq, o);
-        c_sure += __shfl_xor_sync(0xffffffffu, c_sure, o);
-    }
-    __syncthreads();                        // wtot may still be read by a scan
-    if (lane == 0) { sm.wtot[warp] = c_eq; sm.wtot2[warp] = c_sure; }
-    __syncthreads();
-    const int e_w = (lane < NW) ? sm.wtot[lane] : 0;
-    const int s_w = (lane < NW) ? sm.wtot2[lane] : 0;
-    int einc = e_w;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int t = __shfl_up_sync(0xffffffffu, einc, o);
-        if (lane >= o) einc += t;
-    }
-    const int k_w = s_w + min(max(quota - (einc - e_w), 0), e_w);
-    int kinc = k_w;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int t = __shfl_up_sync(0xffffffffu, kinc, o);
-        if (lane >= o) kinc += t;
-    }
-    int pos = __shfl_sync(0xffffffffu, kinc - k_w, warp);
-    int eqr = __shfl_sync(0xffffffffu, einc - e_w, warp);
-    const int cnt = __shfl_sync(0xffffffffu, kinc, 31);
-    for (int it = w0; it < w1; it += 128) {
-        const int base = it + 4 * lane;
-        const uint4 kv = *reinterpret_cast<const uint4*>(&keys[base]);
-        const uint32_t kk[4] = {kv.x, kv.y, kv.z, kv.w};
-        bool keep[4];
-#pragma unroll
-        for (int s = 0; s < 4; ++s) keep[s] = kk[s] > tau_key;
-        if (ties) {
-            uint32_t eb[4];
-            int lower = 0, total = 0;
-#pragma unroll
-            for (int s = 0; s < 4; ++s) {
-                eb[s] = __ballot_sync(0xffffffffu, kk[s] == tau_key);
-                lower += __popc(eb[s] & lt_mask);
-                total += __popc(eb[s]);
-            }
-            int rank = eqr + lower;
-#pragma unroll
-            for (int s = 0; s < 4; ++s) {
-                if (kk[s] == tau_key) { keep[s] = rank < quota; ++rank; }
-            }
-            eqr += total;
-        }
-        int slot = pos, total = 0;
-#pragma unroll
-        for (int s = 0; s < 4; ++s) {
-            const uint32_t kb = __ballot_sync(0xffffffffu, keep[s]);
-            slot += __popc(kb & lt_mask);
-            total += __popc(kb);
-        }
-#pragma unroll
-        for (int s = 0; s < 4; ++s)
-            if (keep[s]) emit(slot++, base + s, kk[s]);
-        pos += total;
-    }
-    return cnt;
-}
-
 // NT threads per CTA.  OWNER: CTA 0 selects the whole row, the other CTAs of the
 // cluster only combine (or there is no cluster); otherwise every CTA of the
 // cluster keeps and selects the keys of its page slice.
@@ -763,59 +633,6 @@ topb_kernel(const SelParams p) {
         // single CTA: every thread has read the keys; a cluster of slices re-arms
         // behind the exchange of the compaction totals below
         if (rearm && CL_phys == 1 && tid < G) p.hmax[row * G + tid] = 0u;
-    }
-
-    // ============ long rows, small budget: two-level selection ===================
-    // The b best pages of the row are among the b best of every slice.  Each CTA
-    // selects in its own slice (no traffic between the CTAs), leaves its kept
-    // (key, page) pairs -- ascending, forced pages included -- in its run of CTA
-    // 0's candidate array, and after ONE cluster barrier CTA 0 selects among the
-    // candidates and writes the table.  The sliced search below costs two cluster
-    // barriers per radix digit and remote histogram merges instead; it remains
-    // for budgets whose candidates do not fit the array.
-    if constexpr (!OWNER && !CP) {
-        const int forced = lo + max(npg - hi, 0);
-        const int capc = (max(b, 0) + forced + 3) & ~3;       // candidate slots per CTA
-        if (CL > 1 && !keep_all && CL * capc <= CAND_CAP) {
-            uint32_t* cand = keys + p.key_cap + HSLOTS * HCOPIES;     // key | page
-            uint32_t* cand0 = cluster.map_shared_rank(cand, 0);
-            auto sel_in = [&](int cc) -> int {       // selectable pages of slice cc
-                const int a0 = min(cc * cper, span), a1 = min(a0 + cper, span);
-                return max(0, min(hi, a1) - max(lo, a0));
-            };
-            uint32_t* my_key = cand0 + c * capc;
-            uint32_t* my_page = cand0 + CAND_PAGES_AT + c * capc;
-            const int kept = select_in_cta<NT>(
-                sm, keys, h4, n_loc, b, sel_in(c),
-                [&](int slot, int idx, uint32_t key) {
-                    my_key[slot] = key;
-                    my_page[slot] = (uint32_t)(s0 + idx);
-                });
-            for (int i = kept + tid; i < capc; i += NT) my_key[i] = 0u;   // holes
-            if (c == 0 && tid < 128) cand[CL * capc + tid] = 0u;      // read as holes
-            cluster.sync();                  // every CTA's candidates are in CTA 0
-            int32_t* tabp = p.page_table + row * MP;
-            const int cnt_max = min(npg, (npg - L) + min(max(b, 0), L));
-            if (c != 0) {
-                for (int i = cnt_max + (c - 1) * NT + tid; i < MP; i += (CL - 1) * NT)
-                    tabp[i] = -1;
-                if constexpr (APPEND) {
-                    if (c == CL - 1 && tid < p.app.head_dim)
-                        kv_append_elem(p.app, r, kh, tid);
-                }
-                return;
-            }
-            if (rearm && tid < G) p.hmax[row * G + tid] = 0u;
-            int n_sel = 0;
-            for (int cc = 0; cc < CL; ++cc) n_sel += min(max(b, 0), sel_in(cc));
-            const uint32_t* cpage = cand + CAND_PAGES_AT;
-            const int cnt = select_in_cta<NT>(
-                sm, cand, h4, CL * capc, b, n_sel,
-                [&](int slot, int idx, uint32_t) { tabp[slot] = (int32_t)cpage[idx]; });
-            for (int i = cnt + tid; i < cnt_max; i += NT) tabp[i] = -1;
-            if (tid == 0) p.page_cnt[row] = cnt;
-            return;
-        }
     }
 
     // ============ selection over keys[0, n_loc) (local index j = page - s0) ======
@@ -1213,9 +1030,8 @@ static int topb_select_impl(
                                  : ((((max_pages + cl - 1) / cl) + 31) & ~31);
     const int per_cta = ((slice + 127) & ~127) + 128;
     p.key_cap = per_cta;
-    const int dyn_smem =
-        (per_cta + HSLOTS * HCOPIES + (owner_mode ? 0 : CAND_WORDS)) * 4;
-    const int smem_max = (KEYS_PER_CTA + 512 + HSLOTS * HCOPIES + CAND_WORDS) * 4;
+    const int dyn_smem = (per_cta + HSLOTS * HCOPIES) * 4;
+    const int smem_max = (KEYS_PER_CTA + 512 + HSLOTS * HCOPIES) * 4;
     static bool attr_done[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);

@@ -371,6 +371,41 @@ def test_topb_long_context(MP, combine):
     np.testing.assert_array_equal(t2n(st.page_table), tab_o)
 
 
+@pytest.mark.parametrize("MP,kind,budget", [
+    (65536, "equal", 128), (65536, "one_slice", 128), (40000, "coarse", 1),
+    (131072, "coarse", 200), (20000, "equal", 500), (65536, "fine", 230)])
+def test_topb_long_rows_small_budget(MP, kind, budget):
+    """Long rows (kept as per-CTA slices) with a small page budget: all-equal
+    scores (ties across slice borders: the lowest pages win), the best pages all
+    in one slice, budget 1, a second row that fills only part of the slices;
+    tables equal the oracle's bit for bit."""
+    from locks.selection import Rki4State, derive_page_params, topb_select
+    rng = np.random.default_rng(MP + budget)
+    n_kv, R = 2, 2
+    st = Rki4State(DEV, num_layers=1, num_blocks=4, n_kv=n_kv, G=1,
+                   head_dim=128, page=16, max_reqs=R, max_pages=MP,
+                   budget_pages=budget, sink_pages=2, window_pages=4,
+                   combine="nrm")
+    sl = np.array([MP * 16 - 3, (MP // 2 + 7) * 16], dtype=np.int32)
+    derive_page_params(st, torch.from_numpy(sl).to(DEV), R)
+    npg, nsh, b = orc.derive_page_params(sl, 16, 4, 2, budget)
+    if kind == "equal":
+        score = np.full((R, n_kv, MP), 0.25, np.float32)
+    elif kind == "coarse":
+        score = (np.round(rng.random((R, n_kv, MP)) * 64) / 64).astype(np.float32)
+    elif kind == "one_slice":
+        score = rng.random((R, n_kv, MP)).astype(np.float32)
+        score[..., MP // 2 - 300:MP // 2 - 300 + 2 * budget] += 5.0
+    else:
+        score = rng.standard_normal((R, n_kv, MP)).astype(np.float32)
+    st.score.copy_(torch.from_numpy(score).to(DEV))
+    topb_select(st, R)
+    torch.cuda.synchronize()
+    tab_o, cnt_o = orc.topb_select(score, npg, nsh, b, 2)
+    np.testing.assert_array_equal(t2n(st.page_cnt), cnt_o)
+    np.testing.assert_array_equal(t2n(st.page_table), tab_o)
+
+
 @pytest.mark.parametrize("MP,kind", [(40000, "equal"), (131072, "coarse"),
                                      (16385, "equal"), (65536, "fine"),
                                      (200000, "coarse")])
