@@ -999,6 +999,26 @@ def c2_record(args, dev, rank, world, full_line=False):
             rki4_score_only(st, l % n_slabs, hp.q[l, :R], bt, sl, R, hp.scale)
     ms_score = timed(g.replay, max(args.steps // 4, 8)) / L
     st.hmax.zero_()
+    # the other two stages the same way (the selector from the scores the last
+    # scorer launch left, sweeping the maxima itself)
+    from locks.attention import sparse_paged_decode_fused
+    from locks.selection import rki4_select_only
+
+    def stage_ms(fn):
+        for l in range(L):
+            fn(l)
+        torch.cuda.synchronize()
+        gs = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gs):
+            for l in range(L):
+                fn(l)
+        return timed(gs.replay, max(args.steps // 4, 8)) / L
+
+    ms_sel = stage_ms(lambda l: rki4_select_only(st, R, has_hmax=False))
+    ms_dec = stage_ms(lambda l: sparse_paged_decode_fused(
+        hp.q[l, :R], caches[l % n_slabs], bt, sl, st, hp.out[l],
+        hp.vsources[l % n_slabs], scale=hp.scale))
+    hp.step()                       # leave a consistent selection behind
     b_score, b_dec, b_dense, nsh, _ = algo_bytes(sh, my_lens, my_budgets)
     tot = torch.tensor([float(b_score), float(b_dec), float(tok), float(len(mine)),
                         ms_score], device=dev, dtype=torch.float64)
@@ -1033,6 +1053,10 @@ def c2_record(args, dev, rank, world, full_line=False):
                      or None,
                      "peak_source": peak_src, "us_per_launch": ms_score * 1e3,
                      "note": "rank 0's launch"},
+        "stages_us_per_layer": {"score": ms_score * 1e3, "select": ms_sel * 1e3,
+                                "decode_fused": ms_dec * 1e3,
+                                "decode_gbs": b_dec / L / (ms_dec * 1e-3) / 1e9,
+                                "note": "rank 0's launches"},
         "load_balance": {"max_rank_bytes": float(mx[0] + mx[1]),
                          "mean_rank_bytes": (all_score + all_dec) / world},
         "gpu_launches_per_step": hp.launches_per_step,
@@ -1211,13 +1235,18 @@ def c2_line(args, dev, rank, world):
             order = sorted(range(len(my_lens)), key=lambda i: my_lens[i])
             i = order[len(order) // 2]
             shs = dataclasses.replace(sh, budget_pages=my_budgets[i])
-            arm = CpuArm(shs, my_lens[i])
-            arm.step()
-            t_one = float(np.mean([arm.step() for _ in range(3)]))
+            if reference_available():      # the reference's own CPU code
+                arm, kind = RefArm(shs, my_lens[i], layers=1), "reference"
+                arm.step()
+                t_one = float(np.mean([arm.step() for _ in range(3)])) * sh.n_layers
+            else:
+                arm, kind = CpuArm(shs, my_lens[i]), "port"
+                arm.step()
+                t_one = float(np.mean([arm.step() for _ in range(3)]))
             bs, bd, _, _, _ = algo_bytes(shs, my_lens[i])
             share = (bs + bd) / rec["step_roofline"]["algorithmic_bytes"]
             cpu = {"value": 64 / (t_one / share), "unit": "tokens/s",
-                   "cores": os.cpu_count(), "kind": "port",
+                   "cores": os.cpu_count(), "kind": kind,
                    "sample": f"sequence of {my_lens[i] - 1} tokens, budget "
                              f"{my_budgets[i]}: " + arm.sample +
                              f"; scaled by its {share:.4f} share of the batch's "
@@ -1243,6 +1272,7 @@ def c2_line(args, dev, rank, world):
                 "d2h_bytes_per_step": d2h},
         "gpu_launches": rec["gpu_launches_per_step"] * args.steps,
         "roofline": rec["roofline"], "step_roofline": rec["step_roofline"],
+        "stages_us_per_layer": rec["stages_us_per_layer"],
         "load_balance": rec["load_balance"],
         "build": {"bulk_ms": rec["build_bulk_ms"]},
         "cpu_baseline": cpu,

@@ -552,7 +552,14 @@ extern "C" int locks_rki4_score_bt(
     // wave dealt by length -- the short rows' CTAs retire at once and the long
     // rows still get their share of the resident slots)
     const int slots = (CTAS_PER_SM * sm_count()) / max(1, n_kv);
-    const int Zt = (4 * n_req <= slots) ? slots : n_req + slots;
+    // Many requests: four whole waves of CTAs.  A request gets 1 + floor(extra *
+    // its share) CTAs, so with few CTAs to deal a mid-size row loses up to half of
+    // its share to the rounding (one wave: the slowest CTA carried 1.7x the mean
+    // and the launch ran at 0.67 of the copy rate on 64 rows of 4K-250K tokens;
+    // four waves: 0.76); whole waves, because a last wave that fills only part of
+    // the GPU is pure tail.
+    const int Zt = (4 * n_req <= slots)
+        ? slots : ((n_req + 3 * slots + slots - 1) / slots) * slots;
     const bool ragged = zsplit <= 0 && n_req > 1 && n_req <= 1024;
 
     ScoreParams p;
