@@ -1021,7 +1021,8 @@ def c2_record(args, dev, rank, world, full_line=False):
     hp.step()                       # leave a consistent selection behind
     b_score, b_dec, b_dense, nsh, _ = algo_bytes(sh, my_lens, my_budgets)
     tot = torch.tensor([float(b_score), float(b_dec), float(tok), float(len(mine)),
-                        ms_score], device=dev, dtype=torch.float64)
+                        ms_score, float(b_score + b_dec)], device=dev,
+                       dtype=torch.float64)
     mx = tot.clone()
     if world > 1:
         dist.all_reduce(tot)
@@ -1057,7 +1058,7 @@ def c2_record(args, dev, rank, world, full_line=False):
                                 "decode_fused": ms_dec * 1e3,
                                 "decode_gbs": b_dec / L / (ms_dec * 1e-3) / 1e9,
                                 "note": "rank 0's launches"},
-        "load_balance": {"max_rank_bytes": float(mx[0] + mx[1]),
+        "load_balance": {"max_rank_bytes": float(mx[5]),
                          "mean_rank_bytes": (all_score + all_dec) / world},
         "gpu_launches_per_step": hp.launches_per_step,
         "build_bulk_ms": t_build,
