@@ -193,3 +193,48 @@ def test_mixed_prefill_decode_steps_are_split(stock):
     assert act is not None and act["dense"] == 0, act
     # 2 x 40 decode rows in all; some of them rode along with prefill chunks
     assert act["sparse"] >= 78, act
+
+
+def _run_mla(mode, model_dir, out, budget=None):
+    cmd = [sys.executable, os.path.join(ROOT, "tests", "vllm_mla_worker.py"), mode,
+           model_dir, out] + ([str(budget)] if budget is not None else [])
+    env = dict(os.environ)
+    env.pop("LOCKS_CONFIG", None)
+    env.pop("LOCKS_DISABLE", None)
+    try:
+        p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=480)
+    except subprocess.TimeoutExpired:
+        return None, "timed out"
+    log = p.stdout + p.stderr
+    if p.returncode != 0 or "WORKER_DONE" not in log or not os.path.exists(out):
+        return None, log
+    with open(out) as fh:
+        return json.load(fh), log
+
+
+def test_mla_hook_inside_a_vllm_engine(tmp_path):
+    """The MLA decode hook (``LocksMLAImpl.forward_mqa``: device-side factor
+    gate, page scores, selection, sparse latent attention) inside a real vLLM
+    engine on a two-layer DeepSeek-V2-shaped model (latent cache 512 + 64, 16
+    heads, dense MLPs, random weights), Triton MLA backend replaced by
+    ``register()``.  With every page kept the greedy tokens equal stock vLLM's
+    (their log-probabilities to 0.05); a run with a selective budget must
+    complete.  The numerics of the functions the hook calls are checked against
+    the oracle in ``tests/test_gpu_mla.py``; this test is about the hook's place
+    in the engine."""
+    pytest.importorskip("vllm")
+    model_dir = str(tmp_path / "tiny_deepseek_v2")
+    want, log = _run_mla("stock", model_dir, str(tmp_path / "stock.json"))
+    if want is None:
+        pytest.skip("stock vLLM (Triton MLA) did not start here: " + log[-300:])
+    got, log = _run_mla("locks", model_dir, str(tmp_path / "locks.json"))
+    assert got is not None, log[-3000:]
+    assert "[locks] ACTIVE (MLA)" in log, log[-3000:]
+    assert [len(x) for x in got["ids"]] == [24, 24]
+    assert got["ids"] == want["ids"]
+    for a, b in zip(got["logprobs"], want["logprobs"]):
+        assert max(abs(x - y) for x, y in zip(a, b)) <= 0.05
+    sel, log = _run_mla("locks", model_dir, str(tmp_path / "sel.json"), budget=24)
+    assert sel is not None, log[-3000:]
+    assert "[locks] ACTIVE (MLA) budget_pages=24" in log
+    assert [len(x) for x in sel["ids"]] == [24, 24]
