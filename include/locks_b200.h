@@ -201,6 +201,38 @@ int locks_decode_fused(const void* q, int64_t q_stride_req, const void* k_cache,
                        int head_dim, int page, int max_pages, float scale,
                        int* status, locks_stream_t stream);
 
+/* Launch order for large ragged batches.  No counterpart in the reference.
+ * CTAs start roughly in grid order; with several hundred (request, kv-head)
+ * rows of very different lengths over ~150-300 resident CTAs, a long row that
+ * happens to start last is the whole tail of the launch.  locks_row_order ranks
+ * the requests of the step on the device (one small launch, after the page
+ * parameters were derived; n_req <= 4096): order_select[z] = the request with
+ * the z-th most pages to select from, order_decode[z] = the request whose
+ * decode attends the z-th most pages (ties by index; both permutations of
+ * [0, n_req)).  locks_topb_select_rows / locks_decode_fused_rows are
+ * locks_topb_select / locks_decode_fused whose grid row z handles request
+ * row_order[z]; results are identical. */
+int locks_row_order(const int32_t* n_pages, const int32_t* n_sel_hi,
+                    const int32_t* b_fix, int n_req, int sink_pages,
+                    int32_t* order_select, int32_t* order_decode,
+                    locks_stream_t stream);
+int locks_topb_select_rows(int combine, const float* score_h, float* score,
+                           uint32_t* hmax, const int32_t* n_pages,
+                           const int32_t* n_sel_hi, const int32_t* b_fix,
+                           int32_t* page_table, int32_t* page_cnt, int n_req,
+                           int n_kv, int G, int max_pages, int sink_pages,
+                           const int32_t* row_order, locks_stream_t stream);
+int locks_decode_fused_rows(const void* q, int64_t q_stride_req, const void* k_cache,
+                            const void* v_cache, int64_t kv_stride_block,
+                            int64_t kv_stride_tok, int64_t kv_stride_head,
+                            const int32_t* block_table, int64_t bt_stride,
+                            const int32_t* page_table, const int32_t* page_cnt,
+                            const int32_t* seq_lens, void* out,
+                            int64_t out_stride_req, int n_req, int n_kv, int G,
+                            int head_dim, int page, int max_pages,
+                            const int32_t* row_order, float scale, int* status,
+                            locks_stream_t stream);
+
 /* locks_decode_fused with the K/V pages staged by tiled tensor-map copies
  * (cp.async.bulk.tensor.2d into 128-byte-swizzled shared memory, two 16 x 64
  * boxes per plane and page) instead of 16-byte cp.async.  Same arguments plus

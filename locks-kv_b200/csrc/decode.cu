@@ -136,6 +136,7 @@ struct DecParams {
     int vt_miss_cap;
     float scale;
     int* status;
+    const int32_t* row_order;      // grid row z handles request row_order[z] (or z)
     CpLink cp;          // context parallel: partials meet the peers' (world > 0)
 };
 
@@ -287,7 +288,8 @@ __device__ __forceinline__ void decode_body(const DecParams& p, const CUtensorMa
                   (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023))
             : smem_raw);
 
-    const int sp = blockIdx.x, kh = blockIdx.y, r = blockIdx.z;
+    const int sp = blockIdx.x, kh = blockIdx.y;
+    const int r = p.row_order ? p.row_order[blockIdx.z] : (int)blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gid = lane >> 2, tig = lane & 3;
     const int G = p.G;
@@ -901,7 +903,8 @@ extern "C" int locks_merge_gathered(
     return check_launch("locks_merge_gathered");
 }
 
-extern "C" int locks_decode_fused(
+static int decode_fused_impl(
+    const int32_t* row_order,
     const void* q, int64_t q_stride_req, const void* k_cache,
     const void* v_cache, int64_t kv_stride_block, int64_t kv_stride_tok,
     int64_t kv_stride_head, const int32_t* block_table, int64_t bt_stride,
@@ -931,6 +934,7 @@ extern "C" int locks_decode_fused(
     p.out = static_cast<__nv_bfloat16*>(out); p.out_stride_req = out_stride_req;
     p.n_kv = n_kv; p.G = G; p.max_pages = max_pages; p.split = 1;
     p.pps_min = 1; p.fused = 1; p.scale = scale; p.status = status;
+    p.row_order = row_order;
     return launch_decode("locks_decode_fused", p, n_req,
                          fused_cluster_size(n_req, n_kv),
                          static_cast<cudaStream_t>(stream));
@@ -1031,6 +1035,35 @@ extern "C" int locks_decode_fused_tma(
         return fail(LOCKS_ERR_LAUNCH, "locks_decode_fused_tma: %s",
                     cudaGetErrorString(e));
     return check_launch("locks_decode_fused_tma");
+}
+
+extern "C" int locks_decode_fused(
+    const void* q, int64_t q_stride_req, const void* k_cache,
+    const void* v_cache, int64_t kv_stride_block, int64_t kv_stride_tok,
+    int64_t kv_stride_head, const int32_t* block_table, int64_t bt_stride,
+    const int32_t* page_table, const int32_t* page_cnt, const int32_t* seq_lens,
+    void* out, int64_t out_stride_req, int n_req, int n_kv, int G, int head_dim,
+    int page, int max_pages, float scale, int* status, locks_stream_t stream) {
+    return decode_fused_impl(nullptr, q, q_stride_req, k_cache, v_cache,
+                             kv_stride_block, kv_stride_tok, kv_stride_head,
+                             block_table, bt_stride, page_table, page_cnt, seq_lens,
+                             out, out_stride_req, n_req, n_kv, G, head_dim, page,
+                             max_pages, scale, status, stream);
+}
+
+extern "C" int locks_decode_fused_rows(
+    const void* q, int64_t q_stride_req, const void* k_cache,
+    const void* v_cache, int64_t kv_stride_block, int64_t kv_stride_tok,
+    int64_t kv_stride_head, const int32_t* block_table, int64_t bt_stride,
+    const int32_t* page_table, const int32_t* page_cnt, const int32_t* seq_lens,
+    void* out, int64_t out_stride_req, int n_req, int n_kv, int G, int head_dim,
+    int page, int max_pages, const int32_t* row_order, float scale, int* status,
+    locks_stream_t stream) {
+    return decode_fused_impl(row_order, q, q_stride_req, k_cache, v_cache,
+                             kv_stride_block, kv_stride_tok, kv_stride_head,
+                             block_table, bt_stride, page_table, page_cnt, seq_lens,
+                             out, out_stride_req, n_req, n_kv, G, head_dim, page,
+                             max_pages, scale, status, stream);
 }
 
 extern "C" int locks_decode_fused_vtier(

@@ -117,7 +117,35 @@ struct SelParams {
     KvAppend app;       // optional: the new token's K/V store of this layer (key != null)
     CpLink cp;          // context parallel: exchanges with the peer ranks (world > 0)
     int* status;        // bounded-wait status word (context parallel only)
+    const int32_t* row_order;   // grid row z handles request row_order[z] (or z)
 };
+
+// Launch order of the rows of a large ragged batch: longest first, so that the
+// last CTAs to start are the short ones (CTAs start roughly in grid order; with a
+// few hundred rows of very different lengths over ~300 resident CTAs a long row
+// that starts last is the whole tail).  One block; rank sort, ties by index.
+// order_sel: by pages to select from; order_dec: by pages the decode will attend.
+__global__ void row_order_kernel(const int32_t* __restrict__ n_pages,
+                                 const int32_t* __restrict__ n_sel_hi,
+                                 const int32_t* __restrict__ b_fix, int n_req,
+                                 int sink, int32_t* __restrict__ order_sel,
+                                 int32_t* __restrict__ order_dec) {
+    for (int i = threadIdx.x; i < n_req; i += blockDim.x) {
+        const int si = n_sel_hi[i];
+        const int di = min(b_fix[i], max(n_sel_hi[i] - sink, 0)) +
+                       (n_pages[i] - n_sel_hi[i]);
+        int rs = 0, rd = 0;
+        for (int j = 0; j < n_req; ++j) {
+            const int sj = n_sel_hi[j];
+            const int dj = min(b_fix[j], max(n_sel_hi[j] - sink, 0)) +
+                           (n_pages[j] - n_sel_hi[j]);
+            rs += (sj > si || (sj == si && j < i)) ? 1 : 0;
+            rd += (dj > di || (dj == di && j < i)) ? 1 : 0;
+        }
+        order_sel[rs] = i;
+        order_dec[rd] = i;
+    }
+}
 
 
 constexpr int KEYS_PER_CTA = 16384;               // shared-memory key capacity
@@ -465,7 +493,8 @@ topb_kernel(const SelParams p) {
 
     pdl_trigger();               // the decode may be scheduled; it waits for us
     const int c_phys = blockIdx.x, CL_phys = gridDim.x;   // rank / size of cluster
-    const int kh = blockIdx.y, r = blockIdx.z;
+    const int kh = blockIdx.y;
+    const int r = p.row_order ? p.row_order[blockIdx.z] : (int)blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int MP = p.max_pages, G = p.G;
     const int npg = min(max(p.n_pages[r], 0), MP);
@@ -934,7 +963,7 @@ static int topb_select_impl(
     int32_t* page_table, int32_t* page_cnt, int n_req, int n_kv, int G,
     int max_pages, int sink_pages, const locks_kv_append_t* app,
     locks_stream_t stream, const locks_cp_link_t* link = nullptr,
-    int* status = nullptr) {
+    int* status = nullptr, const int32_t* row_order = nullptr) {
     using namespace locks;
     LOCKS_REQUIRE(combine >= 0 && combine <= 2, LOCKS_ERR_ARG,
                   "locks_topb_select: combine must be 0, 1 or 2, got %d", combine);
@@ -956,6 +985,7 @@ static int topb_select_impl(
     p.app = KvAppend{};
     p.cp = CpLink{};
     p.status = status;
+    p.row_order = row_order;
     if (link != nullptr) {
         LOCKS_REQUIRE(n_req == 1 && combine == LOCKS_COMBINE_NRM && hmax != nullptr,
                       LOCKS_ERR_ARG,
@@ -1097,6 +1127,33 @@ extern "C" int locks_topb_select(
     return topb_select_impl(combine, score_h, score, hmax, n_pages, n_sel_hi, b_fix,
                             page_table, page_cnt, n_req, n_kv, G, max_pages,
                             sink_pages, nullptr, stream);
+}
+
+extern "C" int locks_topb_select_rows(
+    int combine, const float* score_h, float* score, uint32_t* hmax,
+    const int32_t* n_pages, const int32_t* n_sel_hi, const int32_t* b_fix,
+    int32_t* page_table, int32_t* page_cnt, int n_req, int n_kv, int G,
+    int max_pages, int sink_pages, const int32_t* row_order,
+    locks_stream_t stream) {
+    return topb_select_impl(combine, score_h, score, hmax, n_pages, n_sel_hi, b_fix,
+                            page_table, page_cnt, n_req, n_kv, G, max_pages,
+                            sink_pages, nullptr, stream, nullptr, nullptr, row_order);
+}
+
+extern "C" int locks_row_order(const int32_t* n_pages, const int32_t* n_sel_hi,
+                               const int32_t* b_fix, int n_req, int sink_pages,
+                               int32_t* order_select, int32_t* order_decode,
+                               locks_stream_t stream) {
+    using namespace locks;
+    LOCKS_REQUIRE(n_pages && n_sel_hi && b_fix && order_select && order_decode,
+                  LOCKS_ERR_ARG, "locks_row_order: null pointer argument");
+    LOCKS_REQUIRE(n_req >= 0 && n_req <= 4096 && sink_pages >= 0, LOCKS_ERR_ARG,
+                  "locks_row_order: supports up to 4096 rows, got %d", n_req);
+    if (n_req == 0) return LOCKS_OK;
+    row_order_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        n_pages, n_sel_hi, b_fix, n_req, sink_pages, order_select, order_decode);
+    pdl_break();
+    return check_launch("locks_row_order");
 }
 
 extern "C" int locks_topb_select_cp(

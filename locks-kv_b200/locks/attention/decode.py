@@ -210,6 +210,16 @@ def sparse_paged_decode_fused(q, kv_cache, block_table, seq_lens, st, out,
                    int(st.max_pages), int(k.shape[0]), float(scale),
                    _cabi.ptr(st.status), _cabi.stream())
         return
+    if getattr(st, "row_order_n", 0) == n_req:      # large batch: longest row first
+        _cabi.call("locks_decode_fused_rows", _cabi.ptr(q), q.stride(0),
+                   _cabi.ptr(k), _cabi.ptr(v), k.stride(0), k.stride(1),
+                   k.stride(2), _cabi.ptr(block_table), block_table.stride(0),
+                   _cabi.ptr(st.page_table), _cabi.ptr(st.page_cnt),
+                   _cabi.ptr(seq_lens), _cabi.ptr(out), out.stride(0), n_req,
+                   int(st.n_kv), int(st.G), int(st.d), int(st.page),
+                   int(st.max_pages), _cabi.ptr(st.order_dec), float(scale),
+                   _cabi.ptr(st.status), _cabi.stream())
+        return
     _cabi.call("locks_decode_fused", _cabi.ptr(q), q.stride(0), _cabi.ptr(k),
                _cabi.ptr(v), k.stride(0), k.stride(1), k.stride(2),
                _cabi.ptr(block_table), block_table.stride(0),

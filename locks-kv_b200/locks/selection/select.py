@@ -13,6 +13,29 @@ from .. import _cabi
 COMBINE_NONE, COMBINE_NRM, COMBINE_MAX = 0, 1, 2
 
 
+# A batch with more (request, kv-head) rows than this many resident CTAs gets
+# its rows launched longest first (``locks_row_order``): the selector holds two
+# CTAs per SM, the decode one.
+ROW_ORDER_MIN_ROWS = 148
+
+
+def _row_order(st, n_req: int) -> None:
+    """Longest-first launch order of the step's rows for the selector and the
+    decode (device-side rank sort of the page parameters just derived); small
+    batches keep grid order."""
+    if n_req * st.n_kv <= ROW_ORDER_MIN_ROWS or n_req > 4096:
+        st.row_order_n = 0
+        return
+    if getattr(st, "order_sel", None) is None:
+        st.order_sel = torch.zeros(st.max_reqs, device=st.n_pages.device,
+                                   dtype=torch.int32)
+        st.order_dec = torch.zeros_like(st.order_sel)
+    _cabi.call("locks_row_order", _cabi.ptr(st.n_pages), _cabi.ptr(st.n_sel_hi),
+               _cabi.ptr(st.b_fix), int(n_req), int(st.sink_pages),
+               _cabi.ptr(st.order_sel), _cabi.ptr(st.order_dec), _cabi.stream())
+    st.row_order_n = int(n_req)
+
+
 def derive_page_params(st, seq_lens, n_req: int) -> None:
     """Refresh ``st.n_pages / n_sel_hi / b_fix`` for this decode step."""
     assert n_req <= st.max_reqs
@@ -22,12 +45,13 @@ def derive_page_params(st, seq_lens, n_req: int) -> None:
                    _cabi.ptr(st.budget_req), float(st.budget),
                    _cabi.ptr(st.n_pages), _cabi.ptr(st.n_sel_hi),
                    _cabi.ptr(st.b_fix), _cabi.stream())
-        return
-    _cabi.call("locks_derive_page_params", _cabi.ptr(seq_lens), int(n_req),
-               int(st.page), int(st.window_pages), int(st.sink_pages),
-               int(getattr(st, "budget_abs", 0)), float(st.budget),
-               _cabi.ptr(st.n_pages), _cabi.ptr(st.n_sel_hi),
-               _cabi.ptr(st.b_fix), _cabi.stream())
+    else:
+        _cabi.call("locks_derive_page_params", _cabi.ptr(seq_lens), int(n_req),
+                   int(st.page), int(st.window_pages), int(st.sink_pages),
+                   int(getattr(st, "budget_abs", 0)), float(st.budget),
+                   _cabi.ptr(st.n_pages), _cabi.ptr(st.n_sel_hi),
+                   _cabi.ptr(st.b_fix), _cabi.stream())
+    _row_order(st, n_req)
 
 
 def append_advance(st, seq_lens, block_table, n_req: int, slot, slot_prev,
@@ -65,7 +89,10 @@ def _select(st, n_req: int, combine: int, use_hmax: bool, append=None) -> None:
             _cabi.ptr(st.b_fix), _cabi.ptr(st.page_table),
             _cabi.ptr(st.page_cnt), int(n_req), int(st.n_kv), int(st.G),
             int(st.max_pages), int(st.sink_pages))
-    if append is None:
+    if append is None and getattr(st, "row_order_n", 0) == n_req:
+        _cabi.call("locks_topb_select_rows", *args, _cabi.ptr(st.order_sel),
+                   _cabi.stream())
+    elif append is None:
         _cabi.call("locks_topb_select", *args, _cabi.stream())
     else:       # a KvAppendDesc (attention.kv_append_desc): the layer's KV write
         import ctypes

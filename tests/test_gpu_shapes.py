@@ -243,6 +243,41 @@ def test_fused_decode_with_tensor_map_copies_ignores_stale_rows():
                                    atol=2e-2, rtol=1e-2)
 
 
+def test_large_batch_rows_launched_longest_first_give_the_same_result():
+    """More (request, kv-head) rows than resident CTAs: the selector and the
+    decode handle the rows longest first (``locks_row_order``).  The orders are
+    permutations sorted as documented, and tables and outputs equal those of the
+    grid-order launch bit for bit."""
+    from locks import LocksConfig, synth
+    from locks.hotpath import HotPath
+    sh = synth.GqaShape(n_layers=1, n_kv=8, G=4, d=128, page=16, budget_pages=16,
+                        sink_pages=1, window_pages=2, n_needles=2, n_outlier=2)
+    rng = np.random.default_rng(3)
+    lens = [int(x) for x in rng.integers(40, 2500, size=40)]
+    budgets = [int(x) for x in rng.choice([4, 8, 16, 32], size=40)]
+    case = synth.make_gqa_case(17, sh, lens, device="cuda")
+    cfg = LocksConfig(budget_pages=32, sink_pages=1, window_pages=2)
+    hp = HotPath(case.kv_caches, case.block_table, case.seq_lens, n_kv=8, G=4,
+                 scale=1 / math.sqrt(128), cfg=cfg, budget_pages_req=budgets)
+    hp.build_all(); hp.derive(); hp.q.copy_(case.q)
+    st, R = hp.st, len(lens)
+    assert st.row_order_n == R
+    torch.cuda.synchronize()
+    npg, nsh, b = (t2n(x[:R]) for x in (st.n_pages, st.n_sel_hi, st.b_fix))
+    o_sel, o_dec = t2n(st.order_sel[:R]), t2n(st.order_dec[:R])
+    assert sorted(o_sel.tolist()) == list(range(R)) == sorted(o_dec.tolist())
+    assert (np.diff(nsh[o_sel]) <= 0).all()
+    att = np.minimum(b, np.maximum(nsh - 1, 0)) + (npg - nsh)
+    assert (np.diff(att[o_dec]) <= 0).all()
+    out_a = hp.step_eager()[0].clone()
+    tab_a, cnt_a = st.page_table[:R].clone(), st.page_cnt[:R].clone()
+    st.row_order_n = 0                               # grid order
+    out_b = hp.step_eager()[0].clone()
+    torch.cuda.synchronize()
+    assert torch.equal(tab_a, st.page_table[:R]) and torch.equal(cnt_a, st.page_cnt[:R])
+    assert torch.equal(out_a[:R], out_b[:R])
+
+
 def test_ragged_batch_scores_equal_single_request_scores():
     """The scorer deals the CTAs of a kv-head to the requests of a batch by
     length; whatever the split, a request's scores must be bit-identical to the
