@@ -211,11 +211,21 @@ int locks_decode_fused(const void* q, int64_t q_stride_req, const void* k_cache,
  * decode attends the z-th most pages (ties by index; both permutations of
  * [0, n_req)).  locks_topb_select_rows / locks_decode_fused_rows are
  * locks_topb_select / locks_decode_fused whose grid row z handles request
- * row_order[z]; results are identical. */
+ * row_order[z]; locks_rki4_score_bt_rows is locks_rki4_score_bt dealing the
+ * CTAs of a kv-head to the requests in that order when it shares them by
+ * length (several requests); results are identical. */
 int locks_row_order(const int32_t* n_pages, const int32_t* n_sel_hi,
                     const int32_t* b_fix, int n_req, int sink_pages,
                     int32_t* order_select, int32_t* order_decode,
                     locks_stream_t stream);
+int locks_rki4_score_bt_rows(const void* q, int64_t q_stride_req,
+                             const void* records_layer, const int32_t* block_table,
+                             int64_t bt_stride, const int32_t* n_sel_hi,
+                             float* score_h, uint32_t* hmax, int n_req, int n_kv,
+                             int G, int head_dim, int page, int max_pages,
+                             int bt_width, int num_blocks, float scale, int zsplit,
+                             const int32_t* row_order, int* status,
+                             locks_stream_t stream);
 int locks_topb_select_rows(int combine, const float* score_h, float* score,
                            uint32_t* hmax, const int32_t* n_pages,
                            const int32_t* n_sel_hi, const int32_t* b_fix,

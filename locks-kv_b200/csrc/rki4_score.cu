@@ -56,6 +56,7 @@ struct ScoreParams {
     uint32_t* hmax;
     int n_kv, G, max_pages, bt_width, num_blocks;
     int n_req, ragged;
+    const int32_t* row_order;  // ragged: the requests are dealt in this order (or 0, 1, ...)
     float scale;
     int* status;
 };
@@ -165,9 +166,12 @@ rki4_score_kernel(const ScoreParams p) {
         // request is the one whose run of CTAs contains blockIdx.x.
         const int R = p.n_req, cap0 = min(p.max_pages, p.bt_width);
         const int extra = (int)gridDim.x - R, b = (int)blockIdx.x;
+        // (with a launch order the longest requests come first in the grid, so
+        // the CTAs that start last are the light ones)
+        auto req_at = [&](int i) -> int { return p.row_order ? p.row_order[i] : i; };
         int total = 0;
         for (int i = lane; i < R; i += 32)
-            total += (min(max(p.n_sel_hi[i], 0), cap0) + CHUNK - 1) / CHUNK;
+            total += (min(max(p.n_sel_hi[req_at(i)], 0), cap0) + CHUNK - 1) / CHUNK;
 #pragma unroll
         for (int o = 16; o >= 1; o >>= 1)
             total += __shfl_xor_sync(0xffffffffu, total, o);
@@ -178,8 +182,9 @@ rki4_score_kernel(const ScoreParams p) {
         r = -1;
         for (int i0 = 0; i0 < R && r < 0; i0 += 32) {
             const int i = i0 + lane;
+            const int ri = (i < R) ? req_at(i) : 0;
             const int ci = (i < R)
-                ? (min(max(p.n_sel_hi[i], 0), cap0) + CHUNK - 1) / CHUNK : 0;
+                ? (min(max(p.n_sel_hi[ri], 0), cap0) + CHUNK - 1) / CHUNK : 0;
             int inc = ci;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -193,7 +198,7 @@ rki4_score_kernel(const ScoreParams p) {
             const uint32_t m = __ballot_sync(0xffffffffu, hit);
             if (m) {
                 const int src = __ffs(m) - 1;
-                r = i0 + src;
+                r = __shfl_sync(0xffffffffu, ri, src);
                 z = b - __shfl_sync(0xffffffffu, beg, src);
                 Z = __shfl_sync(0xffffffffu, end - beg, src);
             }
@@ -500,12 +505,12 @@ rki4_score_kernel(const ScoreParams p) {
 }  // namespace locks
 
 
-extern "C" int locks_rki4_score_bt(
+static int score_impl(
     const void* q, int64_t q_stride_req, const void* records_layer,
     const int32_t* block_table, int64_t bt_stride, const int32_t* n_sel_hi,
     float* score_h, uint32_t* hmax, int n_req, int n_kv, int G, int head_dim,
     int page, int max_pages, int bt_width, int num_blocks, float scale,
-    int zsplit, int* status, locks_stream_t stream) {
+    int zsplit, const int32_t* row_order, int* status, locks_stream_t stream) {
     using namespace locks;
     LOCKS_REQUIRE(q && records_layer && block_table && n_sel_hi && score_h,
                   LOCKS_ERR_ARG, "locks_rki4_score_bt: null pointer argument");
@@ -574,6 +579,7 @@ extern "C" int locks_rki4_score_bt(
     p.n_kv = n_kv; p.G = G; p.max_pages = max_pages; p.bt_width = bt_width;
     p.num_blocks = num_blocks; p.scale = scale; p.status = status;
     p.n_req = n_req; p.ragged = ragged ? 1 : 0;
+    p.row_order = ragged ? row_order : nullptr;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = ragged ? dim3(Zt, n_kv, 1) : dim3(Z, n_kv, n_req);
     cfg.blockDim = dim3(NTHREADS, 1, 1);
@@ -591,4 +597,28 @@ extern "C" int locks_rki4_score_bt(
         return fail(LOCKS_ERR_LAUNCH, "locks_rki4_score_bt: %s",
                     cudaGetErrorString(e));
     return check_launch("locks_rki4_score_bt");
+}
+
+extern "C" int locks_rki4_score_bt(
+    const void* q, int64_t q_stride_req, const void* records_layer,
+    const int32_t* block_table, int64_t bt_stride, const int32_t* n_sel_hi,
+    float* score_h, uint32_t* hmax, int n_req, int n_kv, int G, int head_dim,
+    int page, int max_pages, int bt_width, int num_blocks, float scale,
+    int zsplit, int* status, locks_stream_t stream) {
+    return score_impl(q, q_stride_req, records_layer, block_table, bt_stride,
+                      n_sel_hi, score_h, hmax, n_req, n_kv, G, head_dim, page,
+                      max_pages, bt_width, num_blocks, scale, zsplit, nullptr, status,
+                      stream);
+}
+
+extern "C" int locks_rki4_score_bt_rows(
+    const void* q, int64_t q_stride_req, const void* records_layer,
+    const int32_t* block_table, int64_t bt_stride, const int32_t* n_sel_hi,
+    float* score_h, uint32_t* hmax, int n_req, int n_kv, int G, int head_dim,
+    int page, int max_pages, int bt_width, int num_blocks, float scale,
+    int zsplit, const int32_t* row_order, int* status, locks_stream_t stream) {
+    return score_impl(q, q_stride_req, records_layer, block_table, bt_stride,
+                      n_sel_hi, score_h, hmax, n_req, n_kv, G, head_dim, page,
+                      max_pages, bt_width, num_blocks, scale, zsplit, row_order,
+                      status, stream);
 }

@@ -74,6 +74,8 @@ _SIGNATURES = {
                                   _I, _I, _I, _I, _I, _F, _P, _P], 1),
     "locks_decode_fused_rows": ([_P, _L, _P, _P, _L, _L, _L, _P, _L, _P, _P, _P, _P,
                                  _L, _I, _I, _I, _I, _I, _I, _P, _F, _P, _P], 1),
+    "locks_rki4_score_bt_rows": ([_P, _L, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I,
+                                  _I, _I, _I, _I, _F, _I, _P, _P, _P], 1),
     "locks_topb_select_rows": ([_I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I,
                                 _I, _P, _P], 1),
     "locks_row_order": ([_P, _P, _P, _I, _I, _P, _P, _P], 1),

@@ -21,6 +21,15 @@ def rki4_score_only(st, lidx: int, q, block_table, seq_lens, n_req: int,
     assert block_table.dtype == torch.int32 and block_table.stride(1) == 1
     rec = st.pp_rec[lidx]
     hmax = st.hmax if (publish_hmax and st.hmax is not None) else None
+    if getattr(st, "row_order_n", 0) == n_req:      # large batch: longest row first
+        _cabi.call("locks_rki4_score_bt_rows", _cabi.ptr(q), q.stride(0),
+                   _cabi.ptr(rec), _cabi.ptr(block_table), block_table.stride(0),
+                   _cabi.ptr(st.n_sel_hi), _cabi.ptr(st.score_h), _cabi.ptr(hmax),
+                   int(n_req), int(st.n_kv), int(st.G), int(st.d), int(st.page),
+                   int(st.max_pages), int(block_table.shape[1]), int(st.NB),
+                   float(scale), int(st.zsplit or 0), _cabi.ptr(st.order_sel),
+                   _cabi.ptr(st.status), _cabi.stream())
+        return
     _cabi.call("locks_rki4_score_bt", _cabi.ptr(q), q.stride(0),
                _cabi.ptr(rec), _cabi.ptr(block_table), block_table.stride(0),
                _cabi.ptr(st.n_sel_hi), _cabi.ptr(st.score_h), _cabi.ptr(hmax),
