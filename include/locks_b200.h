@@ -675,6 +675,12 @@ int locks_mla_decode_tc(const void* q, int64_t q_stride_row, const void* cache,
                         const int32_t* seq_lens, void* out, float* lse, int n_rows,
                         int max_pages, int num_blocks, int cnt_hint, float scale,
                         int* status, locks_stream_t stream);
+/* The thread-block cluster size (CTAs per row) locks_mla_decode_tc will use for
+ * n_rows rows whose page lists hold about pages_hint entries: host-side query,
+ * no launch.  A caller choosing between locks_mla_decode_tc and locks_mla_decode
+ * by the number of 8-page tiles a CTA would walk needs it. */
+int locks_mla_decode_tc_cluster_size(int n_rows, int pages_hint);
+
 
 #ifdef __cplusplus
 }

@@ -188,4 +188,30 @@ __device__ __forceinline__ float bf16_bits_to_f32(uint32_t b16) {
 #endif  // __CUDACC__
 
 
+// How many clusters of `cluster` CTAs of `kernel` (blocks of `threads`, `smem`
+// bytes of dynamic shared memory) the device can hold at once; 0 if the query
+// fails.  A 16-CTA cluster needs 16 free SMs inside one GPC, so fewer of them
+// fit than SMs / 16 suggests -- a launch with more clusters than fit runs in
+// two rounds.
+template <class Kernel>
+inline int max_active_clusters(Kernel kernel, int cluster, int threads, int smem) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(cluster, 1, 1);
+    cfg.blockDim = dim3(threads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
 }  // namespace locks

@@ -980,8 +980,14 @@ extern "C" int locks_mla_decode(const void* q, int64_t q_stride_row,
     {
         const int want = sm_count() / max(1, n_rows);
         while (cl * 2 <= want && cl < 8) cl *= 2;
-        // 16-CTA clusters each need a whole GPC: only for a few rows
-        if (cl == 8 && 16 * n_rows <= sm_count()) cl = MD_MAX_CL;
+        // 16-CTA clusters each need 16 free SMs of one GPC: only when all rows'
+        // clusters fit at once (otherwise the launch runs in two rounds)
+        static int fit16[64] = {0};
+        if (cl == 8 && 16 * n_rows <= sm_count() && dev >= 0 && dev < 64) {
+            if (fit16[dev] == 0)
+                fit16[dev] = max(1, max_active_clusters(mla_decode_kernel, MD_MAX_CL, MD_THREADS, smem));
+            if (n_rows <= fit16[dev]) cl = MD_MAX_CL;
+        }
     }
     MlaDecParams p;
     p.q = static_cast<const __nv_bfloat16*>(q); p.q_stride_row = q_stride_row;

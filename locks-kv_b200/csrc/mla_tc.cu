@@ -449,6 +449,35 @@ mla_tc_decode_kernel(const __grid_constant__ CUtensorMap tmap, const TcParams p)
 }  // namespace
 }  // namespace locks
 
+// Cluster size of a launch: as many CTAs per row as fit in one wave, a power of
+// two up to 8; 16 (non-portable) only when every row's cluster fits at once AND
+// eight CTAs would each walk more than four tiles -- for a short list two tiles in
+// an 8-CTA cluster cost less than one tile plus a 16-CTA exchange.
+static int tc_cluster_size(int n_rows, int pages_hint, int dev, int smem) {
+    using namespace locks;
+    int cl = 1;
+    const int want = sm_count() / max(1, n_rows);
+    while (cl * 2 <= want && cl < 8) cl *= 2;
+    static int fit16[64] = {0};
+    const int tiles_at_8 = (pages_hint + 8 * TILE_PAGES - 1) / (8 * TILE_PAGES);
+    if (cl == 8 && 16 * n_rows <= sm_count() && tiles_at_8 > 4 && dev >= 0 &&
+        dev < 64) {
+        if (fit16[dev] == 0)
+            fit16[dev] = max(1, max_active_clusters(mla_tc_decode_kernel, TC_MAX_CL,
+                                                    TC_THREADS, smem));
+        if (n_rows <= fit16[dev]) cl = TC_MAX_CL;
+    }
+    return cl;
+}
+
+extern "C" int locks_mla_decode_tc_cluster_size(int n_rows, int pages_hint) {
+    using namespace locks;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return tc_cluster_size(max(n_rows, 1), max(pages_hint, 0), dev,
+                           (int)sizeof(TcSmem) + 1024);
+}
+
 using namespace locks;
 
 extern "C" int locks_mla_decode_tc(const void* q, int64_t q_stride_row,
@@ -494,12 +523,8 @@ extern "C" int locks_mla_decode_tc(const void* q, int64_t q_stride_row,
                              cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         attr_done[dev] = true;
     }
-    int cl = 1;
-    {
-        const int want = sm_count() / max(1, n_rows);
-        while (cl * 2 <= want && cl < 8) cl *= 2;
-        if (cl == 8 && 16 * n_rows <= sm_count()) cl = TC_MAX_CL;
-    }
+    const int p_hint = min(max(cnt_hint, 0), max_pages);
+    const int cl = tc_cluster_size(n_rows, p_hint, dev, smem);
     TcParams p;
     p.q = static_cast<const __nv_bfloat16*>(q); p.q_stride_row = q_stride_row;
     p.block_table = block_table; p.bt_stride = bt_stride;

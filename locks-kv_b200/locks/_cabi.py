@@ -78,6 +78,7 @@ _SIGNATURES = {
                                   _I, _I, _I, _I, _F, _I, _P, _P, _P], 1),
     "locks_topb_select_rows": ([_I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I,
                                 _I, _P, _P], 1),
+    "locks_mla_decode_tc_cluster_size": ([_I, _I], 0),
     "locks_row_order": ([_P, _P, _P, _I, _I, _P, _P, _P], 1),
     "locks_decode_fused_tma": ([_P, _L, _P, _P, _L, _L, _L, _P, _L, _P, _P, _P, _P,
                                 _L, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P], 1),

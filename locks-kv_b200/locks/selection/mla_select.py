@@ -169,23 +169,20 @@ def mla_decode(st: MlaState, q, cache, block_table, seq_lens, out, lse,
     ``tensor_core``: True = the tcgen05 kernel (tokens in the M dimension, TMA
     page gather; needs token rows evenly spaced across blocks), False = the
     warp-level kernel.  Default (None, or ``st.tensor_core`` when set): the
-    tcgen05 kernel when a CTA's share of a row exceeds one 8-page tile -- many
-    pages kept, or many rows (measured: every page kept 3.5 against 4.2 ms per
-    4-layer step) -- and the warp-level kernel for the one-tile case, where the
-    two are latency chains within 2 % of each other and the warp-level one is
-    ahead (config 3: 150.5 against 153.6 us per layer)."""
+    tcgen05 kernel when a CTA of the cluster the library would launch
+    (``locks_mla_decode_tc_cluster_size``) walks more than one 8-page tile, the
+    warp-level kernel for the one-tile case.  Measured at config 3 (8 rows x
+    128 kept pages): tcgen05 with two tiles per CTA in 8-CTA clusters 19.3 us,
+    warp-level kernel 24.2 us; every page kept 3.5 against 4.2 ms per 4-layer
+    step."""
     _check_cache(cache)
     if tensor_core is None:
         tensor_core = getattr(st, "tensor_core", None)
     can_tc = cache.stride(0) == PAGE * cache.stride(1)
     if tensor_core is None:
-        want = 148 // max(1, int(n_rows))
-        cl = 1
-        while cl * 2 <= want and cl < 8:
-            cl *= 2
-        if cl == 8 and 16 * int(n_rows) <= 148:
-            cl = 16
-        share = -(-min(st.budget_pages, st.max_pages) // cl)
+        pages = min(st.budget_pages, st.max_pages)
+        cl = _cabi.lib().locks_mla_decode_tc_cluster_size(int(n_rows), int(pages))
+        share = -(-pages // max(1, cl))
         tensor_core = share > 8
     tensor_core = bool(tensor_core) and can_tc
     if tensor_core:
