@@ -424,7 +424,7 @@ rki4_score_kernel(const ScoreParams p) {
         } else {
             // ---- one page per pass, rows = heads (8, or 16 with the hi rows) --
             // as above: no exit test inside the unrolled group of pages
-#pragma unroll 4
+#pragma unroll 8
             for (int i = 0; i < CHUNK; ++i) {
                 const uint8_t* rec = crec + i * REC_BYTES;
                 int c1[4];
