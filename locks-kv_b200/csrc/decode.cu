@@ -57,6 +57,7 @@ __device__ __forceinline__ void mma_f16_k16(float (&d)[4], uint32_t a0, uint32_t
 constexpr int DW = 8;                 // warps per CTA
 constexpr int DTHREADS = DW * 32;
 constexpr int DSTAGES = 2;
+constexpr int MAX_DCL = 16;             // largest cluster of the fused decode (non-portable size)
 constexpr int PAGE_T = 16;
 constexpr int HD = 128;
 constexpr int ROWB = HD * 2 + 16;     // 272 B row pitch: conflict-free ldmatrix
@@ -74,8 +75,8 @@ struct __align__(128) DecSmem {
     float cl[DW][16];
     // cluster exchange (fused mode): CTA c pushes its (m, l) to every CTA and
     // the slice of its O that CTA d normalises into xacc[c] of CTA d
-    float xm[8][16];
-    float xl[8][16];
+    float xm[MAX_DCL][16];
+    float xl[MAX_DCL][16];
     float xacc[16 * HD + 16];
 };
 
@@ -95,8 +96,8 @@ struct __align__(1024) DecSmemT {
     WarpBufT wb[DW];
     float cm[DW][16];
     float cl[DW][16];
-    float xm[8][16];
-    float xl[8][16];
+    float xm[MAX_DCL][16];
+    float xl[MAX_DCL][16];
     float xacc[16 * HD + 16];
     uint64_t full[DW][DSTAGES];    // one mbarrier per warp and ring stage
 };
@@ -607,17 +608,17 @@ __device__ __forceinline__ void decode_body(const DecParams& p, const CUtensorMa
     cluster.sync();                               // every CTA's pushes have landed
     for (int e = sp * per_e + tid; e < min((sp + 1) * per_e, n_el); e += DTHREADS) {
         const int g = e / HD, dd = e % HD;
-        float mw[8], lw[8];
+        float mw[MAX_DCL], lw[MAX_DCL];
         float M = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < MAX_DCL; ++c) {
             mw[c] = (c < CL) ? sm.xm[c][g] : -INFINITY;
             lw[c] = (c < CL) ? sm.xl[c][g] : 0.f;
             M = fmaxf(M, mw[c]);
         }
         float Lsum = 0.f, o = 0.f;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < MAX_DCL; ++c) {
             if (c < CL) {
                 const float wt = (lw[c] > 0.f) ? __expf(mw[c] - M) : 0.f;
                 Lsum += wt * lw[c];
@@ -733,11 +734,17 @@ int check_geometry(const char* who, int G, int head_dim, int page) {
 
 // cluster size of the fused decode: as many CTAs as fit in ONE wave (a CTA's
 // rings take more than half an SM's shared memory, so one CTA per SM), a power
-// of two, at most 8 (the portable cluster limit)
-int fused_cluster_size(int n_req, int n_kv) {
+// of two, at most 8 (the portable cluster limit) -- or, where the caller's kernel
+// allows it (`fit16` = how many 16-CTA clusters of it the device holds at once,
+// 0 = not allowed), 16 when every row's cluster fits at once: the launch is a
+// latency chain whose page loop shortens with every CTA added (config 1, 137
+// pages per row: 15.9 / 10.7 / 8.2 us with 2 / 4 / 8 CTAs per row)
+int fused_cluster_size(int n_req, int n_kv, int fit16 = 0) {
     const int want = sm_count() / max(1, n_req * n_kv);
     int cl = 1;
     while (cl * 2 <= want && cl < 8) cl *= 2;
+    // (a few rows only: 16-CTA clusters each take 16 SMs of one GPC)
+    if (cl == 8 && want >= 32 && n_req * n_kv <= fit16) cl = MAX_DCL;
     return cl;
 }
 
@@ -935,8 +942,27 @@ static int decode_fused_impl(
     p.n_kv = n_kv; p.G = G; p.max_pages = max_pages; p.split = 1;
     p.pps_min = 1; p.fused = 1; p.scale = scale; p.status = status;
     p.row_order = row_order;
+    // 16-CTA clusters (non-portable size) where all of them fit at once
+    static int fit16[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int fit = 0;
+    if (dev >= 0 && dev < 64 && sm_count() / max(1, n_req * n_kv) >= 32) {
+        if (fit16[dev] == 0) {
+            cudaFuncSetAttribute(decode_kernel<false, true>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)sizeof(DecSmem));
+            cudaFuncSetAttribute(decode_kernel<false, true>,
+                                 cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            cudaFuncSetAttribute(decode_kernel<true, true>,
+                                 cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            fit16[dev] = max(1, max_active_clusters(decode_kernel<false, true>, MAX_DCL,
+                                                    DTHREADS, (int)sizeof(DecSmem)));
+        }
+        fit = fit16[dev];
+    }
     return launch_decode("locks_decode_fused", p, n_req,
-                         fused_cluster_size(n_req, n_kv),
+                         fused_cluster_size(n_req, n_kv, fit),
                          static_cast<cudaStream_t>(stream));
 }
 
