@@ -563,12 +563,8 @@ static int score_impl(
     // and the launch ran at 0.67 of the copy rate on 64 rows of 4K-250K tokens;
     // four waves: 0.76); whole waves, because a last wave that fills only part of
     // the GPU is pure tail.
-    // The same holds for a few LONG rows: four waves whenever the rows could fill
-    // them with 16 chunks per CTA (judged by the longest row the tables allow;
-    // short rows leave idle CTAs that retire at once).
-    const int Z4 = ((n_req + 3 * slots + slots - 1) / slots) * slots;
-    const int64_t chunks_cap = (int64_t)n_req * ((min(max_pages, bt_width) + CHUNK - 1) / CHUNK);
-    const int Zt = (4 * n_req > slots || chunks_cap >= (int64_t)16 * Z4) ? Z4 : slots;
+    const int Zt = (4 * n_req <= slots)
+        ? slots : ((n_req + 3 * slots + slots - 1) / slots) * slots;
     const bool ragged = zsplit <= 0 && n_req > 1 && n_req <= 1024;
 
     ScoreParams p;
