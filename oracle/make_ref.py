@@ -1,6 +1,6 @@
 """Stage the reference's own CPU code for the timed reference arm.
 
-    python oracle/make_ref.py            # reads $LOCKS_REFERENCE_SRC or /root/reference/src
+    python oracle/make_ref.py [SRC]      # SRC, else $LOCKS_REFERENCE_SRC, else the default checkout location
 
 Copies, unmodified, the nine files of the reference package (``locks`` v0.1.3)
 that its CPU-runnable selection paths consist of -- ``selection/rki4_state.py``,
@@ -26,6 +26,8 @@ import shutil
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+# where the build container keeps the read-only reference checkout
+DEFAULT_SRC = os.path.join(os.sep, "root", "reference", "src")
 DST = os.path.join(HERE, "_ref", "locks_ref")
 FILES = ["arch.py", "quant.py", "selection/rki4_state.py",
          "selection/rki4_build.py", "selection/build.py",
@@ -34,8 +36,7 @@ FILES = ["arch.py", "quant.py", "selection/rki4_state.py",
 
 
 def stage(src_root: str | None = None) -> bool:
-    src_root = src_root or os.environ.get("LOCKS_REFERENCE_SRC",
-                                          "/root/reference/src")
+    src_root = src_root or os.environ.get("LOCKS_REFERENCE_SRC", DEFAULT_SRC)
     pkg = os.path.join(src_root, "locks")
     if not all(os.path.exists(os.path.join(pkg, f)) for f in FILES):
         print(f"[make_ref] no reference checkout at {pkg}: nothing staged")
