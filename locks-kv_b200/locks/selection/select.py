@@ -23,7 +23,7 @@ def _row_order(st, n_req: int) -> None:
     """Longest-first launch order of the step's rows for the selector and the
     decode (device-side rank sort of the page parameters just derived); small
     batches keep grid order."""
-    if n_req * st.n_kv <= ROW_ORDER_MIN_ROWS or n_req > 4096:
+    if n_req * st.n_kv <= ROW_ORDER_MIN_ROWS or n_req > 2048:    # (rank sort: O(n^2))
         st.row_order_n = 0
         return
     if getattr(st, "order_sel", None) is None:
