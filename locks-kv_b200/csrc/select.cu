@@ -1036,9 +1036,10 @@ static int topb_select_impl(
     const bool owner_mode = max_pages <= KEYS_PER_CTA;
     if (owner_mode) {
         const int want = sm_count() / max(1, n_kv * n_req);
-        // (at least 1024 pages per CTA; measured at 8192 pages x 8 rows: 15.7 /
-        // 12.9 / 10.9 / 9.9 us with 1 / 2 / 4 / 8 CTAs per row)
-        const int useful = (max_pages + 1023) / 1024;
+        // (rows of at least 1024 pages, at least 256 pages per CTA; measured with 8
+        // rows: 8192 pages 15.7 / 12.9 / 10.9 / 9.9 us with 1 / 2 / 4 / 8 CTAs per
+        // row, 2048 pages 8.2 / 7.0 us with 2 / 8, 512 pages 6.5 / 6.7 with 1 / 2)
+        const int useful = (max_pages >= 1024) ? (max_pages + 255) / 256 : 1;
         while (cl * 2 <= want && cl * 2 <= useful && cl < 8) cl *= 2;
     } else {
         while (cl < MAX_CL && (max_pages + cl - 1) / cl > KEYS_PER_CTA) cl *= 2;
