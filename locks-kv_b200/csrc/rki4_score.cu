@@ -563,7 +563,9 @@ static int score_impl(
     // and the launch ran at 0.67 of the copy rate on 64 rows of 4K-250K tokens;
     // four waves: 0.76); whole waves, because a last wave that fills only part of
     // the GPU is pure tail.
-    const int Zt = (4 * n_req <= slots)
+    // (measured on shards of that batch: 16 rows gain from four waves, 0.73 ->
+    // 0.76; 8 rows lose, 0.73 -> 0.60 -- too little work per CTA)
+    const int Zt = (4 * n_req <= slots && n_req < 16)
         ? slots : ((n_req + 3 * slots + slots - 1) / slots) * slots;
     const bool ragged = zsplit <= 0 && n_req > 1 && n_req <= 1024;
 
